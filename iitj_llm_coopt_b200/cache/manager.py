@@ -1,0 +1,303 @@
+"""The cache manager: paged keys and values with a block table per request, and slots for
+per-request state of fixed size.
+
+Bookkeeping follows the reference's BlockManager (engine/block_manager.py:26-110: a pool of
+fixed-size pages, free ids in a FIFO, a table of page ids per sequence, token p at slot
+table[p // page] * page + p % page, `ensure` that raises before it allocates anything,
+`free` at the end of a request).  What is added here:
+
+* Groups.  Layers (cache entries) whose `CacheNeed` is equal share one group.  Each paged
+  group has its own pool of pages, its own table per request and its own rule for giving
+  pages back: a group that keeps every token returns pages when the request ends; a
+  group with a window also returns, after each step, the pages that every later query's
+  window has passed (their table entry becomes -1 and is never read again).
+  One page id addresses the same page in every cache entry of its group, as in the
+  reference (engine/model.py:148-155: one K and V tensor per layer, same block ids).
+* State slots.  Every admitted request holds one slot id in [0, max_requests); groups of
+  kind "state" keep a [entries, max_requests, *state_shape] buffer indexed by it.  The
+  slot exists even when no layer keeps state (Llama: zero bytes).
+
+Device storage of a paged group: [entries, pages, 2, kv_heads, page_size, head_dim]
+(K plane then V plane of a page; one head's rows of a page are contiguous).
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+import torch
+
+
+class OutOfPages(Exception):
+    """Raised by `ensure` when some group cannot provide the pages; nothing was allocated."""
+
+
+class CacheError(RuntimeError):
+    pass
+
+
+class PagePool:
+    """Free-list bookkeeping of one group's pages (host only)."""
+
+    def __init__(self, num_pages: int):
+        if num_pages <= 0:
+            raise ValueError("a page pool needs at least one page")
+        self.num_pages = num_pages
+        self.free: deque = deque(range(num_pages))   # FIFO reuse, as engine/block_manager.py:30, 63-66
+        self.held: set = set()
+
+    @property
+    def num_free(self) -> int:
+        return len(self.free)
+
+    def take(self) -> int:
+        if not self.free:
+            raise OutOfPages("no free page")
+        p = self.free.popleft()
+        self.held.add(p)
+        return p
+
+    def give(self, page: int) -> None:
+        if page not in self.held:
+            raise CacheError(f"page {page} is given back but is not held (freed twice?)")
+        self.held.remove(page)
+        self.free.append(page)
+
+
+@dataclass
+class PagedGroup:
+    need: object
+    entries: list                      # cache entry indices in this group, in order
+    pool: PagePool
+    page_size: int
+    tables: dict = field(default_factory=dict)      # request -> [page id or -1]
+    storage: torch.Tensor | None = None             # [entries, pages, 2, kv_heads, page_size, head_dim]
+
+    def pages_for(self, tokens: int) -> int:
+        return -(-tokens // self.page_size)
+
+    def extra_pages(self, request, total_tokens: int) -> int:
+        return max(0, self.pages_for(total_tokens) - len(self.tables.get(request, ())))
+
+    def first_needed_page(self, stored_tokens: int) -> int:
+        """Logical pages below this index hold no key that a query at position >= stored_tokens can see."""
+        w = self.need.window
+        if w <= 0:
+            return 0
+        return max(0, stored_tokens - w + 1) // self.page_size
+
+
+@dataclass
+class StateGroup:
+    need: object
+    entries: list
+    storage: torch.Tensor | None = None             # [entries, max_requests, *state_shape]
+
+
+class CacheManager:
+    def __init__(self, needs: list, page_size: int, num_pages: int, max_requests: int,
+                 dtype: torch.dtype = torch.bfloat16, device=None):
+        """needs[i] is the CacheNeed of cache entry i.  `device=None` keeps bookkeeping only
+        (no storage is allocated), which is all the scheduler and the CPU tests use."""
+        self.page_size, self.num_pages, self.max_requests = page_size, num_pages, max_requests
+        self.dtype, self.device = dtype, device
+        self.groups: list = []
+        self.entry_group: list = []       # entry -> (group index, index of the entry inside the group)
+        by_need: dict = {}
+        for entry, need in enumerate(needs):
+            if need.kind == "none":
+                self.entry_group.append((None, 0))
+                continue
+            if need not in by_need:
+                by_need[need] = len(self.groups)
+                if need.kind == "paged_kv":
+                    self.groups.append(PagedGroup(need, [], PagePool(num_pages), page_size))
+                elif need.kind == "state":
+                    self.groups.append(StateGroup(need, []))
+                else:
+                    raise ValueError(f"unknown cache need kind {need.kind!r}")
+            g = by_need[need]
+            self.entry_group.append((g, len(self.groups[g].entries)))
+            self.groups[g].entries.append(entry)
+        self.paged = [i for i, g in enumerate(self.groups) if isinstance(g, PagedGroup)]
+        # per-request records
+        self.stored: dict = {}            # request -> tokens whose keys/values (or state) are in the cache
+        self.slot_of: dict = {}           # request -> state slot
+        self.free_slots: deque = deque(range(max_requests))
+        self._views: dict = {}
+        if device is not None:
+            self._allocate()
+
+    # ---- storage -------------------------------------------------------------------------
+    def _allocate(self) -> None:
+        for g in self.groups:
+            if isinstance(g, PagedGroup):
+                n = g.need
+                g.storage = torch.zeros((len(g.entries), self.num_pages, 2, n.kv_heads, self.page_size, n.head_dim),
+                                        dtype=self.dtype, device=self.device)
+            else:
+                dt = getattr(torch, g.need.state_dtype)
+                g.storage = torch.zeros((len(g.entries), self.max_requests) + tuple(g.need.state_shape),
+                                        dtype=dt, device=self.device)
+
+    @staticmethod
+    def bytes_per_page(needs: list, page_size: int, itemsize: int) -> int:
+        """Bytes one page id costs over all paged cache entries (to size the pool from memory)."""
+        return sum(2 * n.kv_heads * n.head_dim * page_size * itemsize for n in needs if n.kind == "paged_kv")
+
+    def view(self, entry: int):
+        """(group index, storage of that cache entry): [pages, 2, kv_heads, page, head_dim] or
+        [max_requests, *state_shape]."""
+        cached = self._views.get(entry)
+        if cached is not None:
+            return cached
+        g, local = self.entry_group[entry]
+        if g is None:
+            return None, None
+        storage = self.groups[g].storage
+        self._views[entry] = (g, storage[local] if storage is not None else None)
+        return self._views[entry]
+
+    # ---- requests ------------------------------------------------------------------------
+    def admit(self, request) -> int:
+        """Registers a request (no tokens stored yet) and gives it a state slot."""
+        if request in self.stored:
+            raise CacheError(f"request {request!r} is already admitted")
+        if not self.free_slots:
+            raise CacheError(f"all {self.max_requests} request slots are in use")
+        self.stored[request] = 0
+        self.slot_of[request] = self.free_slots.popleft()
+        for gi in self.paged:
+            self.groups[gi].tables[request] = []
+        return self.slot_of[request]
+
+    def has(self, request) -> bool:
+        return request in self.stored
+
+    def num_tokens(self, request) -> int:
+        return self.stored[request]
+
+    def release(self, request) -> int:
+        """Gives back everything the request holds; returns the number of pages returned."""
+        if request not in self.stored:
+            raise CacheError(f"request {request!r} is not admitted (released twice?)")
+        n = 0
+        for gi in self.paged:
+            g = self.groups[gi]
+            for p in g.tables.pop(request):
+                if p >= 0:
+                    g.pool.give(p)
+                    n += 1
+        self.free_slots.append(self.slot_of.pop(request))
+        del self.stored[request]
+        return n
+
+    # ---- capacity ------------------------------------------------------------------------
+    @property
+    def num_free(self) -> int:
+        """Free pages of the tightest paged group."""
+        return min((self.groups[gi].pool.num_free for gi in self.paged), default=self.num_pages)
+
+    @property
+    def usage(self) -> float:
+        return 1.0 - self.num_free / self.num_pages
+
+    @property
+    def capacity_tokens(self) -> int:
+        return self.num_pages * self.page_size
+
+    def extra_pages_needed(self, request, total_tokens: int) -> int:
+        """Largest number of new pages any group needs so the request can hold total_tokens."""
+        return max((self.groups[gi].extra_pages(request, total_tokens) for gi in self.paged), default=0)
+
+    def can_fit(self, request, total_tokens: int) -> bool:
+        return all(self.groups[gi].extra_pages(request, total_tokens) <= self.groups[gi].pool.num_free
+                   for gi in self.paged)
+
+    def ensure(self, request, total_tokens: int) -> None:
+        """Grow the request's tables so they can hold total_tokens tokens; all groups or none."""
+        if request not in self.stored:
+            raise CacheError(f"request {request!r} is not admitted")
+        for gi in self.paged:
+            g = self.groups[gi]
+            need = g.extra_pages(request, total_tokens)
+            if need > g.pool.num_free:
+                raise OutOfPages(f"request {request!r} needs {need} pages in group {gi}, {g.pool.num_free} free")
+        for gi in self.paged:
+            g = self.groups[gi]
+            table = g.tables[request]
+            for _ in range(g.extra_pages(request, total_tokens)):
+                table.append(g.pool.take())
+
+    def advance(self, request, total_tokens: int) -> None:
+        """Records that the cache now holds the request's first total_tokens tokens, and gives
+        back the pages that a window has passed."""
+        if total_tokens < self.stored[request]:
+            raise CacheError("advance cannot go backwards; use truncate")
+        for gi in self.paged:
+            g = self.groups[gi]
+            if g.pages_for(total_tokens) > len(g.tables[request]):
+                raise CacheError(f"request {request!r}: {total_tokens} tokens exceed its reserved pages")
+        self.stored[request] = total_tokens
+        for gi in self.paged:
+            g = self.groups[gi]
+            table = g.tables[request]
+            for lp in range(min(g.first_needed_page(total_tokens), len(table))):
+                if table[lp] >= 0:
+                    g.pool.give(table[lp])
+                    table[lp] = -1
+
+    def truncate(self, request, total_tokens: int) -> None:
+        """Forget tokens beyond total_tokens and give back the trailing pages
+        (engine/block_manager.py:95-103).  Not possible across pages a window already released."""
+        for gi in self.paged:
+            g = self.groups[gi]
+            table = g.tables[request]
+            keep = g.pages_for(total_tokens)
+            if any(p < 0 for p in table[g.first_needed_page(total_tokens):keep]):
+                raise CacheError("truncate would need pages that a window already gave back")
+            while len(table) > keep:
+                p = table.pop()
+                if p >= 0:
+                    g.pool.give(p)
+        self.stored[request] = min(self.stored[request], total_tokens)
+
+    # ---- what the step function needs ----------------------------------------------------
+    def table(self, group: int, request) -> list:
+        return self.groups[group].tables[request]
+
+    def slots(self, group: int, request, start: int, end: int) -> list:
+        """Cache slot (page * page_size + offset) of positions [start, end)."""
+        table, ps = self.groups[group].tables[request], self.page_size
+        out = []
+        for p in range(start, end):
+            page = table[p // ps]
+            if page < 0:
+                raise CacheError(f"request {request!r}: position {p} lies in a page already given back")
+            out.append(page * ps + p % ps)
+        return out
+
+    def state_slot(self, request) -> int:
+        return self.slot_of[request]
+
+    # ---- invariants (tests) --------------------------------------------------------------
+    def check(self) -> None:
+        """Every page is either free or in exactly one table; slots likewise."""
+        for gi in self.paged:
+            g = self.groups[gi]
+            in_tables = [p for t in g.tables.values() for p in t if p >= 0]
+            if len(in_tables) != len(set(in_tables)):
+                raise CacheError(f"group {gi}: a page is held twice")
+            if set(in_tables) != g.pool.held:
+                raise CacheError(f"group {gi}: tables and pool disagree about held pages")
+            free = list(g.pool.free)
+            if len(free) != len(set(free)) or set(free) & g.pool.held:
+                raise CacheError(f"group {gi}: free list is inconsistent")
+            if len(free) + len(in_tables) != g.pool.num_pages:
+                raise CacheError(f"group {gi}: {g.pool.num_pages - len(free) - len(in_tables)} pages are lost")
+            if set(g.tables) != set(self.stored):
+                raise CacheError(f"group {gi}: tables exist for other requests than the admitted ones")
+        used = list(self.slot_of.values())
+        if len(used) != len(set(used)) or set(used) & set(self.free_slots) or \
+                len(used) + len(self.free_slots) != self.max_requests:
+            raise CacheError("state slots are inconsistent")

@@ -1,0 +1,72 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions, error text.
+//
+// Every launcher is an `extern "C"` function that takes raw device pointers, explicit sizes
+// and a stream, launches on that stream, allocates nothing and returns 0 or a negative
+// code after leaving a message that `llm_last_error()` returns.  The Python side
+// (kernels/__init__.py) checks shapes, dtypes and contiguity before it calls in.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define LLM_API extern "C" __attribute__((visibility("default")))
+
+enum LlmDtype { LLM_F32 = 0, LLM_BF16 = 1 };
+
+// ---- error reporting (host) ------------------------------------------------------------
+char* llm_error_buffer();  // defined in runtime.cu; one buffer per process
+
+#define LLM_FAIL(code, ...)                                        \
+    do {                                                           \
+        snprintf(llm_error_buffer(), 512, __VA_ARGS__);            \
+        return (code);                                             \
+    } while (0)
+
+#define LLM_CHECK_LAUNCH(name)                                                       \
+    do {                                                                             \
+        cudaError_t e_ = cudaGetLastError();                                         \
+        if (e_ != cudaSuccess) LLM_FAIL(-2, "%s: %s", name, cudaGetErrorString(e_)); \
+    } while (0)
+
+// ---- element conversions (device) ------------------------------------------------------
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// ---- reductions ------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block whose size is a multiple of 32 (at most 1024).  The order of additions
+// depends only on blockDim, never on the data or on other blocks, so a row's result is
+// the same in whatever batch it is computed.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarp) ? scratch[lane] : 0.f;
+    return warp_sum(t);
+}
+
+template <typename F> static inline int llm_dispatch_dtype(int dtype, F&& f) {
+    if (dtype == LLM_F32) return f(float{});
+    if (dtype == LLM_BF16) return f(__nv_bfloat16{});
+    LLM_FAIL(-1, "unknown dtype code %d", dtype);
+}

@@ -1,0 +1,74 @@
+// Token sampling from float32 logits: greedy (argmax, the lowest index wins a tie) and
+// temperature sampling, mixed row by row in one launch.
+//
+// The reference samples with softmax(logits / T) followed by torch.multinomial
+// (engine/spec_decode.py:12-17).  Here a row with temperature T > 0 takes
+//     argmax_i ( logits[i] / T + g_i ),   g_i = -log(-log(u_i)),
+// which draws from exactly that softmax (the Gumbel-max identity) in one pass over the
+// row.  u_i comes from a counter-based generator keyed by a 64-bit value per row that the
+// host derives from (engine seed, request seed, index of the token in its request), so a
+// request's tokens do not depend on what else is in the batch.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {  // splitmix64 finaliser
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+__device__ __forceinline__ float gumbel(uint64_t key, uint32_t i) {
+    const uint64_t r = mix64(key + 0x9E3779B97F4A7C15ull * (uint64_t)(i + 1));
+    const float u = ((float)(uint32_t)(r >> 40) + 0.5f) * (1.0f / 16777216.0f);  // (0, 1)
+    return -logf(-logf(u));
+}
+
+__global__ void __launch_bounds__(1024)
+sample_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ temperature,
+              const unsigned long long* __restrict__ keys, int* __restrict__ out, int vocab) {
+    __shared__ float best_v[32];
+    __shared__ int best_i[32];
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    const float T = temperature ? temperature[r] : 0.f;
+    const uint64_t key = keys ? keys[r] : 0ull;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        float v = row[i];
+        if (T > 0.f) v = v / T + gumbel(key, (uint32_t)i);
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nwarp = blockDim.x >> 5;
+        bv = lane < nwarp ? best_v[lane] : -INFINITY;
+        bi = lane < nwarp ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) out[r] = bi == 0x7fffffff ? 0 : bi;  // a row of NaNs yields token 0
+    }
+}
+
+}  // namespace
+
+LLM_API int llm_sample(const float* logits, int ld, const float* temperature, const unsigned long long* keys,
+                       int* out, int rows, int vocab, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    sample_kernel<<<rows, 1024, 0, stream>>>(logits, ld, temperature, keys, out, vocab);
+    LLM_CHECK_LAUNCH("sample");
+    return 0;
+}

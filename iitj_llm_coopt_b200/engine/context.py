@@ -1,0 +1,76 @@
+"""What one step hands to the model: the flattened batch on the device.
+
+All index tensors are int32 views into one device buffer that was filled by a single
+host-to-device copy (engine/runner.py).  The reference's `Batch` (engine/model.py:54-65)
+carries the same fields; added here are `token_request` (which request of the step each
+token belongs to), `state_slots`, `first_portion`, and one block table and slot mapping
+per cache group.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+
+@dataclass
+class GroupMeta:
+    """Per cache group: where this step's tokens are stored and where earlier ones lie."""
+    block_table: torch.Tensor      # [B, W] int32, page ids (entries past a request's pages are 0)
+    slots: torch.Tensor            # [T] int32, page * page_size + offset of each new token
+    token_request: torch.Tensor    # [T] int32 (same tensor for all groups)
+    positions: torch.Tensor        # [T] int32
+    # host copies for kernels that plan their grid on the host
+    query_lens: list = field(default_factory=list)
+    seq_lens_host: list = field(default_factory=list)
+    cu_seqlens: torch.Tensor | None = None
+    seq_lens: torch.Tensor | None = None
+
+
+class Workspace:
+    """Named scratch tensors that live across steps, so a step allocates nothing once
+    every buffer has reached its largest size."""
+
+    def __init__(self, device):
+        self.device = device
+        self._flat: dict = {}
+
+    def get(self, name: str, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        flat = self._flat.get(key)
+        if flat is None or flat.numel() < n:
+            flat = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._flat[key] = flat
+        return flat[:n].view(*shape)
+
+
+@dataclass
+class StepContext:
+    num_tokens: int
+    num_requests: int
+    num_logits: int
+    token_ids: torch.Tensor        # [T]
+    positions: torch.Tensor        # [T]
+    token_request: torch.Tensor    # [T]
+    cu_seqlens: torch.Tensor       # [B+1] offsets of each request's new tokens
+    seq_lens: torch.Tensor         # [B] stored + new tokens
+    logit_rows: torch.Tensor       # [N] rows of the hidden states that want logits
+    state_slots: torch.Tensor      # [B]
+    first_portion: torch.Tensor    # [B] 1 where the request's tokens start at position 0
+    groups: dict                   # group index -> GroupMeta
+    cache: object                  # CacheManager
+    workspace: Workspace
+    # host-side copies, for parts that must loop over requests on the host
+    requests: list = field(default_factory=list)
+    query_lens: list = field(default_factory=list)
+    starts: list = field(default_factory=list)
+    slots_host: list = field(default_factory=list)
+
+    def buffer(self, name: str, shape, dtype) -> torch.Tensor:
+        return self.workspace.get(name, shape, dtype)
+
+    def group(self, index: int) -> GroupMeta:
+        return self.groups[index]

@@ -1,0 +1,169 @@
+"""The engine: scheduler above the step function, sampling, stop rules, counters.
+
+One `step()` is the reference's Engine.step (engine/engine.py:407-515) without its draft
+phase: plan, turn the plan into step entries (a prefill portion feeds
+tokens[num_computed:end]; a decode feeds the last token), run the step function, sample
+where a request reached the end of its tokens, append with the stop rules
+(engine/engine.py:293-308: max_tokens -> "length", EOS unless ignore_eos -> "stop",
+max_model_len -> "length"), finish and free.  Logits are asked for only at rows that are
+sampled: a prompt portion that does not reach the prompt's end wants none.
+"""
+from __future__ import annotations
+
+import time
+
+import torch
+
+from ..cache import OutOfPages
+from .policy import StaticPolicy
+from .runner import StepEntry
+from .scheduler import Plan, Scheduler, Sequence
+
+COUNTERS = ("prompt_tokens_total", "generation_tokens_total", "num_preemptions_total",
+            "request_success_total", "request_failure_total", "steps_total", "step_seconds_total")
+
+
+class Engine:
+    def __init__(self, runner, cache, sampler, policy=None, max_model_len: int = 32768, eos_ids=()):
+        self.runner, self.cache, self.sampler = runner, cache, sampler
+        self.policy = policy or StaticPolicy()
+        self.eos_ids = set(eos_ids)
+        self.max_model_len = max_model_len
+        self.kv_capacity_tokens = cache.capacity_tokens
+        if self.kv_capacity_tokens < self.max_model_len:
+            # as engine/engine.py:216-219: a lone sequence must always fit the pool
+            self.max_model_len = self.kv_capacity_tokens
+        if self.policy.max_num_seqs > cache.max_requests:
+            raise ValueError(f"max_num_seqs {self.policy.max_num_seqs} exceeds the cache's "
+                             f"{cache.max_requests} request slots")
+        self.counters = {k: 0 for k in COUNTERS}
+        self.gauges: dict = {}
+        self.scheduler = Scheduler(cache, self.policy, self.counters, engine=self)
+        self._next_id = 0
+
+    # ---- request lifecycle ---------------------------------------------------------------
+    def add_request(self, seq: Sequence) -> Sequence:
+        if not seq.tokens:
+            raise ValueError("a request needs at least one prompt token")
+        if len(seq.tokens) >= self.max_model_len:
+            raise ValueError(f"prompt of {len(seq.tokens)} tokens does not fit max_model_len {self.max_model_len}")
+        self.scheduler.waiting.append(seq)
+        return seq
+
+    def new_sequence(self, prompt, max_tokens, temperature=0.0, ignore_eos=False, seed=None, on_output=None):
+        seq = Sequence(seq_id=self._next_id, tokens=list(prompt), max_tokens=max_tokens, temperature=temperature,
+                       ignore_eos=ignore_eos, seed=seed, on_output=on_output)
+        self._next_id += 1
+        return self.add_request(seq)
+
+    def runner_forget(self, seq_id) -> None:
+        forget = getattr(self.runner, "forget", None)
+        if forget:
+            forget(seq_id)
+
+    def release(self, seq) -> None:
+        if self.cache.has(seq.seq_id):
+            self.cache.release(seq.seq_id)
+        self.runner_forget(seq.seq_id)
+
+    def _finish(self, seq, reason) -> None:
+        seq.finished, seq.finish_reason = True, reason
+        seq.finish_time = time.perf_counter()
+        if seq in self.scheduler.running:
+            self.scheduler.running.remove(seq)
+        self.release(seq)
+        key = "request_failure_total" if reason == "out_of_pages" else "request_success_total"
+        self.counters[key] += 1
+
+    def _append(self, seq, new_tokens) -> list:
+        """Append sampled tokens under the stop rules; returns those kept."""
+        kept = []
+        for t in new_tokens:
+            seq.tokens.append(t)
+            kept.append(t)
+            if seq.num_generated >= seq.max_tokens:
+                seq.finish_reason = "length"
+                break
+            if not seq.ignore_eos and t in self.eos_ids:
+                seq.finish_reason = "stop"
+                break
+            if len(seq.tokens) >= self.max_model_len:
+                seq.finish_reason = "length"
+                break
+        return kept
+
+    # ---- one step ------------------------------------------------------------------------
+    def step(self) -> bool:
+        try:
+            plan = self.scheduler.schedule()
+        except OutOfPages as e:
+            seq = getattr(e, "seq", None)
+            if seq is None:
+                raise
+            self._finish(seq, "out_of_pages")
+            if seq.on_output:
+                seq.on_output(seq, [], True)
+            return True
+        if not plan:
+            return False
+        t0 = time.perf_counter()
+        entries, sampled = [], []         # sampled: sequences whose last fed token wants logits
+        for s, end in plan.chunks:
+            toks = s.tokens[s.num_computed:end]
+            last = end == len(s.tokens)
+            entries.append(StepEntry(s.seq_id, toks, [len(toks) - 1] if last else []))
+            if last:
+                sampled.append(s)
+        for s in plan.decodes:
+            entries.append(StepEntry(s.seq_id, [s.tokens[-1]], [0]))
+            sampled.append(s)
+        n_tokens = sum(len(e.tokens) for e in entries)
+        logits = self.runner.step(entries)
+        new_tokens = []
+        if sampled:
+            rows = [(s.temperature, s.seq_id if s.seed is None else s.seed, s.num_generated) for s in sampled]
+            new_tokens = self.sampler.sample(logits, rows)
+
+        for s, end in plan.chunks:
+            self.counters["prompt_tokens_total"] += end - s.num_computed
+            s.num_computed = end
+        now = time.perf_counter()
+        for s, tok in zip(sampled, new_tokens):
+            kept = self._append(s, [tok])
+            s.num_computed = len(s.tokens) - 1      # everything but the newly sampled token is cached
+            self.counters["generation_tokens_total"] += len(kept)
+            if s.first_token_time is None:
+                s.first_token_time = now
+            done = s.finish_reason is not None
+            if done:
+                self._finish(s, s.finish_reason)
+            if s.on_output:
+                s.on_output(s, kept, done)
+
+        end_t = time.perf_counter()
+        self.counters["steps_total"] += 1
+        self.counters["step_seconds_total"] += end_t - t0
+        self.gauges = {
+            "num_requests_running": len(self.scheduler.running),
+            "num_requests_waiting": len(self.scheduler.waiting),
+            "kv_cache_usage_perc": self.cache.usage,
+            "kv_capacity_tokens": self.kv_capacity_tokens,
+            "step_time_s": end_t - t0,
+            "batch_tokens": n_tokens,
+            **self.policy.state(),
+        }
+        return True
+
+    def has_work(self) -> bool:
+        return bool(self.scheduler.running or self.scheduler.waiting)
+
+    def run_until_done(self, max_steps: int | None = None) -> int:
+        """The reference's worker loop (engine/worker.py:64-65) in-process."""
+        steps = 0
+        while self.has_work():
+            if not self.step():
+                raise RuntimeError("scheduler made no progress although requests are pending")
+            steps += 1
+            if max_steps is not None and steps >= max_steps:
+                break
+        return steps

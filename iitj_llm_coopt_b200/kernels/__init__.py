@@ -1,0 +1,245 @@
+"""The engine's kernel set: thin, checked wrappers around the sm_100a CUDA library.
+
+`load()` builds `csrc/` on first use, loads the shared library with ctypes and returns the
+one `Kernels` object the parts call into.  There is no other implementation: without a
+CUDA device of compute capability 10.x, or without a working build, `load()` raises.
+
+Every wrapper takes torch tensors that live on the GPU, checks dtype, shape and layout,
+and launches on torch's current stream.  Matrix products in float32 always run this
+library's FMA kernel; in bfloat16 they run cuBLAS through torch (`torch.mm`), the library
+the reference's engine uses for them (engine/model.py:194, F.linear).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import threading
+
+import torch
+
+from ..csrc import build as _build
+
+_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_SIGNATURES = {
+    # name: argtypes (all return int)
+    "llm_check_device": [],
+    "llm_abi_version": [],
+    "llm_embed": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "llm_add_rmsnorm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
+                        _c_float, _c_void_p],
+    "llm_rope_store": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_int, _c_int, _c_void_p],
+    "llm_silu_mul": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "llm_attention_generic": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "llm_gemm_f32": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                     _c_void_p],
+    "llm_sample": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+}
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _need(cond, msg):
+    if not cond:
+        raise KernelError(msg)
+
+
+def _check(t, name, dtype=None, dims=None):
+    _need(isinstance(t, torch.Tensor), f"{name}: expected a tensor")
+    _need(t.is_cuda, f"{name}: tensor is on {t.device}, the kernels run on the GPU only")
+    if dtype is not None:
+        ok = t.dtype in dtype if isinstance(dtype, (tuple, list)) else t.dtype == dtype
+        _need(ok, f"{name}: dtype {t.dtype} not accepted (want {dtype})")
+    if dims is not None:
+        _need(t.dim() == dims, f"{name}: expected {dims} dims, got shape {tuple(t.shape)}")
+    _need(t.is_contiguous(), f"{name}: tensor must be contiguous")
+
+
+class Kernels:
+    """Checked entry points of libllm_kernels.so.  One instance per process (see `load`)."""
+
+    def __init__(self, library_path: str):
+        self.library_path = library_path
+        self.lib = ctypes.CDLL(library_path)
+        self.lib.llm_last_error.restype = ctypes.c_char_p
+        for name, args in _SIGNATURES.items():
+            fn = getattr(self.lib, name)
+            fn.argtypes = args
+            fn.restype = _c_int
+        self.launches = 0  # kernels of this library launched so far (the bench reports it)
+
+    # ---- plumbing --------------------------------------------------------------------
+    def _call(self, name, *args):
+        rc = getattr(self.lib, name)(*args)
+        if rc != 0:
+            raise KernelError(f"{name} failed ({rc}): {self.lib.llm_last_error().decode()}")
+        self.launches += 1
+
+    @staticmethod
+    def _stream():
+        return torch.cuda.current_stream().cuda_stream
+
+    def check_device(self):
+        rc = self.lib.llm_check_device()
+        if rc != 0:
+            raise KernelError(self.lib.llm_last_error().decode())
+
+    # ---- row-wise kernels ------------------------------------------------------------
+    def embed(self, ids, table, out, scale: float = 1.0):
+        """out[t] = scale * table[ids[t]] as float32 (the residual stream)."""
+        _check(ids, "embed.ids", torch.int32, 1)
+        _check(table, "embed.table", tuple(DTYPE_CODE), 2)
+        _check(out, "embed.out", torch.float32, 2)
+        _need(out.shape == (ids.shape[0], table.shape[1]), "embed.out: wrong shape")
+        self._call("llm_embed", _ptr(ids), _ptr(table), DTYPE_CODE[table.dtype], _ptr(out), ids.shape[0],
+                   table.shape[1], table.shape[0], float(scale), self._stream())
+        return out
+
+    def add_rmsnorm(self, residual, delta, weight, eps: float, out, rows=None):
+        """residual += delta (when given, and rows is None); out = rmsnorm(residual[rows]) * weight."""
+        _check(residual, "add_rmsnorm.residual", torch.float32, 2)
+        width = residual.shape[1]
+        _check(out, "add_rmsnorm.out", tuple(DTYPE_CODE), 2)
+        _check(weight, "add_rmsnorm.weight", tuple(DTYPE_CODE), 1)
+        _need(weight.shape[0] == width and out.shape[1] == width, "add_rmsnorm: widths differ")
+        if delta is not None:
+            _check(delta, "add_rmsnorm.delta", out.dtype, 2)
+            _need(delta.shape == residual.shape, "add_rmsnorm.delta: shape differs from residual")
+        if rows is not None:
+            _check(rows, "add_rmsnorm.rows", torch.int32, 1)
+            _need(out.shape[0] == rows.shape[0], "add_rmsnorm.out: one row per entry of rows")
+        else:
+            _need(out.shape[0] == residual.shape[0], "add_rmsnorm.out: shape differs from residual")
+        self._call("llm_add_rmsnorm", _ptr(residual), _ptr(delta), _ptr(rows), _ptr(weight),
+                   DTYPE_CODE[weight.dtype], _ptr(out), DTYPE_CODE[out.dtype], out.shape[0], width, float(eps),
+                   self._stream())
+        return out
+
+    def rope_store(self, qkv, positions, inv_freq, slots, cache_layer, heads, kv_heads, head_dim, rotary_dim):
+        """Rotate q (in place) and k, store k and v of every token in its cache slot.
+
+        cache_layer: [pages, 2, kv_heads, page_size, head_dim]; slots may be None (rotate only)."""
+        _check(qkv, "rope_store.qkv", tuple(DTYPE_CODE), 2)
+        _check(positions, "rope_store.positions", torch.int32, 1)
+        tokens = qkv.shape[0]
+        _need(qkv.shape[1] == (heads + 2 * kv_heads) * head_dim, "rope_store.qkv: width is not (heads+2*kv_heads)*head_dim")
+        _need(positions.shape[0] == tokens, "rope_store.positions: one per token")
+        if rotary_dim:
+            _check(inv_freq, "rope_store.inv_freq", torch.float32, 1)
+            _need(inv_freq.shape[0] == rotary_dim // 2, "rope_store.inv_freq: rotary_dim/2 entries")
+        page_size = 1
+        if slots is not None:
+            _check(slots, "rope_store.slots", torch.int32, 1)
+            _need(slots.shape[0] == tokens, "rope_store.slots: one per token")
+            _check(cache_layer, "rope_store.cache", qkv.dtype, 5)
+            _need(cache_layer.shape[1] == 2 and cache_layer.shape[2] == kv_heads and cache_layer.shape[4] == head_dim,
+                  f"rope_store.cache: shape {tuple(cache_layer.shape)} does not fit kv_heads/head_dim")
+            page_size = cache_layer.shape[3]
+        self._call("llm_rope_store", _ptr(qkv), _ptr(positions), _ptr(inv_freq) if rotary_dim else None,
+                   _ptr(slots), _ptr(cache_layer) if slots is not None else None, DTYPE_CODE[qkv.dtype], tokens,
+                   heads, kv_heads, head_dim, rotary_dim, page_size, self._stream())
+
+    def silu_mul(self, gu, act):
+        _check(gu, "silu_mul.gu", tuple(DTYPE_CODE), 2)
+        _check(act, "silu_mul.act", gu.dtype, 2)
+        _need(gu.shape[1] == 2 * act.shape[1] and gu.shape[0] == act.shape[0], "silu_mul: shapes do not fit")
+        self._call("llm_silu_mul", _ptr(gu), _ptr(act), DTYPE_CODE[gu.dtype], act.shape[0], act.shape[1],
+                   self._stream())
+        return act
+
+    # ---- attention -------------------------------------------------------------------
+    def attention(self, qkv, cache_layer, meta, out, heads, kv_heads, head_dim, window: int = 0,
+                  scale: float = 0.0):
+        """Causal attention of every token in `qkv` (query heads first in each row) over the
+        paged keys and values of its request.  `meta` carries block_table [B, W],
+        token_request [T] and positions [T] as int32 device tensors."""
+        _check(qkv, "attention.qkv", tuple(DTYPE_CODE), 2)
+        _check(cache_layer, "attention.cache", qkv.dtype, 5)
+        _check(out, "attention.out", qkv.dtype, 2)
+        tokens = qkv.shape[0]
+        _need(qkv.shape[1] >= heads * head_dim, "attention.qkv: row too narrow")
+        _need(out.shape == (tokens, heads * head_dim), "attention.out: wrong shape")
+        _need(cache_layer.shape[1] == 2 and cache_layer.shape[2] == kv_heads and cache_layer.shape[4] == head_dim,
+              f"attention.cache: shape {tuple(cache_layer.shape)} does not fit kv_heads/head_dim")
+        _check(meta.block_table, "attention.block_table", torch.int32, 2)
+        _check(meta.token_request, "attention.token_request", torch.int32, 1)
+        _check(meta.positions, "attention.positions", torch.int32, 1)
+        _need(meta.token_request.shape[0] == tokens and meta.positions.shape[0] == tokens,
+              "attention: one token_request and one position per token")
+        if not scale:
+            scale = 1.0 / math.sqrt(head_dim)
+        self._call("llm_attention_generic", _ptr(qkv), qkv.shape[1], _ptr(cache_layer), _ptr(meta.block_table),
+                   meta.block_table.shape[1], _ptr(meta.token_request), _ptr(meta.positions), _ptr(out),
+                   out.shape[1], DTYPE_CODE[qkv.dtype], tokens, heads, kv_heads, head_dim, cache_layer.shape[3],
+                   int(window), float(scale), self._stream())
+        return out
+
+    # ---- matrix products -------------------------------------------------------------
+    def linear(self, x, weight, out, swiglu: bool = False):
+        """out = x . weight^T; with swiglu, weight holds gate rows then up rows and
+        out = silu(x . gate^T) * (x . up^T)."""
+        _check(x, "linear.x", tuple(DTYPE_CODE), 2)
+        _check(weight, "linear.weight", x.dtype, 2)
+        _check(out, "linear.out", (x.dtype, torch.float32), 2)
+        n = weight.shape[0] // 2 if swiglu else weight.shape[0]
+        _need(x.shape[1] == weight.shape[1], f"linear: x has {x.shape[1]} columns, weight {weight.shape[1]}")
+        _need(out.shape == (x.shape[0], n), f"linear.out: shape {tuple(out.shape)}, want {(x.shape[0], n)}")
+        if x.shape[0] == 0:
+            return out
+        if x.dtype == torch.float32:
+            self._call("llm_gemm_f32", _ptr(x), _ptr(weight), _ptr(out), x.shape[0], n, x.shape[1], x.shape[1],
+                       weight.shape[1], n, 1 if swiglu else 0, self._stream())
+            return out
+        # bfloat16: cuBLAS through torch, float32 accumulation
+        if swiglu:
+            gu = torch.mm(x, weight.t())
+            return self.silu_mul(gu, out)
+        if out.dtype == torch.float32:
+            torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+        else:
+            torch.mm(x, weight.t(), out=out)
+        return out
+
+    # ---- sampling --------------------------------------------------------------------
+    def sample(self, logits, temperature, keys, out):
+        """out[r] = argmax of row r (temperature[r] <= 0) or a draw from softmax(row / T)."""
+        _check(logits, "sample.logits", torch.float32, 2)
+        _check(out, "sample.out", torch.int32, 1)
+        rows = logits.shape[0]
+        _need(out.shape[0] == rows, "sample.out: one per row")
+        if temperature is not None:
+            _check(temperature, "sample.temperature", torch.float32, 1)
+            _check(keys, "sample.keys", torch.int64, 1)
+            _need(temperature.shape[0] == rows and keys.shape[0] == rows, "sample: one temperature and key per row")
+        self._call("llm_sample", _ptr(logits), logits.shape[1], _ptr(temperature), _ptr(keys), _ptr(out), rows,
+                   logits.shape[1], self._stream())
+        return out
+
+
+_lock = threading.Lock()
+_instance = None
+
+
+def load() -> Kernels:
+    """The process-wide kernel set; builds and loads the library on first call."""
+    global _instance
+    with _lock:
+        if _instance is None:
+            if not torch.cuda.is_available():
+                raise KernelError("no CUDA device is visible: this engine runs on the GPU only "
+                                  "(there is no CPU path)")
+            k = Kernels(_build.library_path())
+            k.check_device()
+            _instance = k
+        return _instance

@@ -1,0 +1,54 @@
+"""Token mixers.
+
+`PagedAttention`: grouped-query causal attention over a paged key/value cache.
+    qkv = x Wqkv^T (no bias; Wqkv = [Wq; Wk; Wv], engine/model.py:113-114, 194-198), position
+    encoding on q and k, keys/values of the new tokens stored in the cache
+    (engine/model.py:201-203), softmax(scale * q k^T) over the request's visible keys with
+    scale = 1/sqrt(head_dim) unless the spec gives one (engine/model.py:102, 204-207),
+    out = (P v) Wo^T (engine/model.py:208).
+The mixer reads whichever cache entry the run order hands it (`call.cache`) and stores its
+own keys and values there only if `call.write` is set, so a layer can read another
+layer's cache.
+"""
+from __future__ import annotations
+
+from ..config.specs import CacheNeed
+from .base import ParamSpec, Part
+
+
+class PagedAttention(Part):
+    def __init__(self, spec, kernels, dtype, position):
+        self.spec, self.k, self.dtype = spec, kernels, dtype
+        self.width, self.heads, self.kv_heads, self.head_dim = spec.width, spec.heads, spec.kv_heads, spec.head_dim
+        if self.heads % self.kv_heads:
+            raise ValueError(f"attention: heads {self.heads} is not a multiple of kv_heads {self.kv_heads}")
+        self.window, self.scale = spec.window, spec.softmax_scale
+        self.position = position
+        self.qkv_width = (self.heads + 2 * self.kv_heads) * self.head_dim
+        self.qkv = self.o = None
+
+    @classmethod
+    def parameters(cls, spec) -> dict:
+        q, kv = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim
+        return {
+            "qkv": ParamSpec((q + 2 * kv, spec.width), pieces=(("q", q), ("k", kv), ("v", kv))),
+            "o": ParamSpec((spec.width, q)),
+        }
+
+    @classmethod
+    def cache_need(cls, spec) -> CacheNeed:
+        return CacheNeed(kind="paged_kv", kv_heads=spec.kv_heads, head_dim=spec.head_dim, window=spec.window)
+
+    def forward(self, ctx, x, call):
+        t = x.shape[0]
+        group, view = ctx.cache.view(call.cache)
+        meta = ctx.group(group)
+        qkv = ctx.buffer("attn.qkv", (t, self.qkv_width), self.dtype)
+        self.k.linear(x, self.qkv, qkv)
+        self.position.encode_and_store(ctx, qkv, view, meta.slots if call.write else None,
+                                       self.heads, self.kv_heads)
+        attn = ctx.buffer("attn.ctx", (t, self.heads * self.head_dim), self.dtype)
+        self.k.attention(qkv, view, meta, attn, self.heads, self.kv_heads, self.head_dim,
+                         window=self.window, scale=self.scale)
+        out = ctx.buffer("attn.out", (t, self.width), self.dtype)
+        return self.k.linear(attn, self.o, out)
