@@ -1,0 +1,272 @@
+"""Each CUDA kernel alone against its plain-torch restatement (tests/torch_kernels.py), at
+sizes other than the engine's test models: widths and vocabularies that are no power of
+two, head sizes in steps of 16, odd numbers of heads and groups, several page sizes."""
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import torch_kernels as R
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 2e-5, torch.bfloat16: 1.6e-2}   # relative to the largest reference magnitude
+
+
+@pytest.fixture(scope="module")
+def K():
+    from iitj_llm_coopt_b200 import kernels
+    return kernels.load()
+
+
+def close(got, want, dtype, scale=1.0):
+    err = (got.float() - want.float()).abs().max().item()
+    ref = max(want.float().abs().max().item(), 1e-20)
+    assert err <= TOL[dtype] * scale * ref, (err, ref)
+
+
+def rnd(shape, dtype, seed, std=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda") * std).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,width,tokens", [(320, 96, 7), (1000, 200, 33)])
+def test_embed(K, dtype, vocab, width, tokens):
+    table = rnd((vocab, width), dtype, 1)
+    ids = torch.randint(0, vocab, (tokens,), device="cuda", dtype=torch.int32)
+    ids[0], ids[-1] = 0, vocab - 1
+    out = torch.empty(tokens, width, device="cuda")
+    K.embed(ids, table, out, 1.5)
+    assert torch.equal(out, R.ref_embed(ids, table, 1.5))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("wdtype", DTYPES)
+@pytest.mark.parametrize("rows,width,eps", [(5, 96, 1e-6), (19, 200, 1e-5), (3, 4104, 1e-5), (2, 13000, 1e-5)])
+def test_add_rmsnorm(K, dtype, wdtype, rows, width, eps):
+    res = rnd((rows, width), torch.float32, 2)
+    delta = rnd((rows, width), dtype, 3)
+    w = (1 + 0.1 * rnd((width,), torch.float32, 4)).to(wdtype)
+    # plain norm, no delta
+    out = torch.empty(rows, width, device="cuda", dtype=dtype)
+    before = res.clone()
+    K.add_rmsnorm(res, None, w, eps, out)
+    assert torch.equal(res, before)
+    close(out, R.ref_add_rmsnorm(before, None, w, eps)[1], dtype)
+    # residual += delta, then norm
+    K.add_rmsnorm(res, delta, w, eps, out)
+    v, y = R.ref_add_rmsnorm(before, delta, w, eps)
+    close(res, v, torch.float32)
+    close(out, y, dtype)
+    # gathered rows: the residual is left alone
+    idx = torch.tensor([rows - 1, 0, rows - 1], device="cuda", dtype=torch.int32)
+    out2 = torch.empty(3, width, device="cuda", dtype=dtype)
+    keep = res.clone()
+    K.add_rmsnorm(res, delta, w, eps, out2, rows=idx)
+    assert torch.equal(res, keep)
+    close(out2, R.ref_add_rmsnorm(keep, delta, w, eps, rows=idx)[1], dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary,page", [(3, 1, 32, 32, 8), (5, 5, 48, 48, 16), (6, 2, 80, 40, 4),
+                                                                (4, 2, 128, 128, 64), (2, 1, 16, 0, 16)])
+def test_rope_store(K, dtype, heads, kv_heads, head_dim, rotary, page):
+    tokens, pages = 23, 9
+    qkv = rnd((tokens, (heads + 2 * kv_heads) * head_dim), dtype, 5)
+    positions = torch.randint(0, 100000, (tokens,), device="cuda", dtype=torch.int32)
+    positions[0] = 0
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, rotary, 2).float() / max(rotary, 1)))).cuda() if rotary else None
+    perm = torch.randperm(pages * page, device="cuda")[:tokens].to(torch.int32)
+    perm[3] = -1                                   # "do not store" for one token
+    cache = torch.full((pages, 2, kv_heads, page, head_dim), 7.0, device="cuda", dtype=dtype)
+    want_cache = cache.clone()
+    want = R.ref_rope(qkv, positions, inv_freq, heads, kv_heads, head_dim, rotary)
+    R.ref_store(want_cache, want.to(dtype), perm, heads, kv_heads, head_dim)
+    got = qkv.clone()
+    K.rope_store(got, positions, inv_freq, perm, cache, heads, kv_heads, head_dim, rotary)
+    q = heads * head_dim
+    close(got[:, :q], want[:, :q], dtype)
+    close(cache, want_cache, dtype)
+    assert torch.equal(cache == 7.0, want_cache == 7.0)          # nothing else was touched
+    # rotate only (no slots): the cache is not needed
+    got2 = qkv.clone()
+    K.rope_store(got2, positions, inv_freq, None, None, heads, kv_heads, head_dim, rotary)
+    close(got2[:, :q], want[:, :q], dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(K, dtype):
+    gu = rnd((11, 2 * 176), dtype, 6, 3.0)
+    act = torch.empty(11, 176, device="cuda", dtype=dtype)
+    K.silu_mul(gu, act)
+    close(act, R.ref_silu_mul(gu), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 320, 96), (7, 130, 176), (65, 64, 64), (130, 200, 264), (3, 1000, 4104)])
+def test_linear(K, dtype, m, n, k):
+    x, w = rnd((m, k), dtype, 7), rnd((n, k), dtype, 8, 0.05)
+    out = torch.empty(m, n, device="cuda", dtype=dtype)
+    K.linear(x, w, out)
+    close(out, R.ref_linear(x, w), dtype)
+    out32 = torch.empty(m, n, device="cuda", dtype=torch.float32)
+    K.linear(x, w, out32)
+    close(out32, R.ref_linear(x, w), torch.float32 if dtype == torch.float32 else dtype, 0.1 if dtype == torch.bfloat16 else 1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 176, 64), (9, 344, 96), (70, 100, 200)])
+def test_linear_swiglu(K, dtype, m, n, k):
+    x, w = rnd((m, k), dtype, 9), rnd((2 * n, k), dtype, 10, 0.2)
+    out = torch.empty(m, n, device="cuda", dtype=dtype)
+    K.linear(x, w, out, swiglu=True)
+    close(out, R.ref_linear(x, w, swiglu=True), dtype)
+
+
+def test_linear_row_does_not_depend_on_batch(K):
+    """float32: a row's product is the same alone and among 100 others, bit for bit."""
+    x, w = rnd((101, 264), torch.float32, 11), rnd((200, 264), torch.float32, 12)
+    full = torch.empty(101, 200, device="cuda")
+    one = torch.empty(1, 200, device="cuda")
+    K.linear(x, w, full)
+    K.linear(x[77:78].contiguous(), w, one)
+    assert torch.equal(full[77:78], one)
+
+
+def _paged_case(dtype, heads, kv_heads, head_dim, page, lens, qlens, seed, pages_extra=3):
+    """Random paged cache for requests with total lengths `lens`, the last qlens[b] tokens being queries."""
+    B = len(lens)
+    need = [-(-n // page) for n in lens]
+    total_pages = sum(need) + pages_extra
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    width = max(need)
+    table = torch.zeros(B, width, dtype=torch.int32)
+    it = iter(perm)
+    for b in range(B):
+        for j in range(need[b]):
+            table[b, j] = next(it)
+    cache = rnd((total_pages, 2, kv_heads, page, head_dim), dtype, seed + 1)
+    T = sum(qlens)
+    q = rnd((T, (heads + 2 * kv_heads) * head_dim), dtype, seed + 2)
+    token_request = torch.cat([torch.full((n,), b, dtype=torch.int32) for b, n in enumerate(qlens)])
+    positions = torch.cat([torch.arange(L - n, L, dtype=torch.int32) for L, n in zip(lens, qlens)])
+    meta = SimpleNamespace(block_table=table.cuda(), token_request=token_request.cuda(), positions=positions.cuda(),
+                           query_lens=list(qlens), seq_lens_host=list(lens))
+    return q, cache, meta
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,window", [
+    (3, 1, 32, 8, 0), (4, 2, 16, 16, 0), (6, 2, 64, 16, 0), (4, 1, 128, 16, 0), (5, 5, 48, 4, 0),
+    (2, 1, 80, 32, 0), (8, 2, 256, 16, 0), (4, 2, 64, 16, 20), (3, 1, 32, 8, 7)])
+def test_attention_mixed_batch(K, dtype, heads, kv_heads, head_dim, page, window):
+    lens, qlens = [70, 33, 150, 1, 17], [70, 1, 13, 1, 2]          # whole prompt, decode, portion, first token, two tokens
+    q, cache, meta = _paged_case(dtype, heads, kv_heads, head_dim, page, lens, qlens, 20)
+    out = torch.empty(q.shape[0], heads * head_dim, device="cuda", dtype=dtype)
+    K.attention(q, cache, meta, out, heads, kv_heads, head_dim, window=window)
+    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads,
+                                 head_dim, window)
+    close(out, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("head_dim,page", [(64, 16), (128, 16), (32, 8)])
+@pytest.mark.parametrize("far", [0, 15, 16, 17, 255, 256, 700, 1022])
+def test_attention_finds_a_far_key(K, dtype, head_dim, page, far):
+    """One key among a thousand is made to stand out; the output must be that key's value.
+    Positions are chosen on and beside page edges and tile edges."""
+    heads, kv_heads, L = 4, 2, 1023
+    q, cache, meta = _paged_case(dtype, heads, kv_heads, head_dim, page, [L], [1], 30 + far)
+    cache.mul_(0.1)
+    pg, off = int(meta.block_table[0, far // page]), far % page
+    marker = rnd((kv_heads, head_dim), torch.float32, 99)
+    for h in range(heads):
+        hk = h // (heads // kv_heads)
+        qv = q[0, h * head_dim:(h + 1) * head_dim].float()
+        cache[pg, 0, hk, off] = (qv / qv.norm() * 60.0 / (qv.norm() / math.sqrt(head_dim))).to(dtype) \
+            if h % (heads // kv_heads) == 0 else cache[pg, 0, hk, off]
+    cache[pg, 1, :, off] = marker.to(dtype)
+    out = torch.empty(1, heads * head_dim, device="cuda", dtype=dtype)
+    K.attention(q, cache, meta, out, heads, kv_heads, head_dim)
+    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, head_dim)
+    close(out, want, dtype)
+    first = out[0, :head_dim].float()                      # head 0 looks straight at the far key
+    assert (first - marker[0].to(dtype).float()).abs().max() < 0.05 * marker.abs().max()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_window_edge(K, dtype):
+    """A key just outside the window must not be seen, the one just inside must."""
+    heads, kv_heads, head_dim, page, window, L = 2, 1, 64, 16, 37, 200
+    q, cache, meta = _paged_case(dtype, heads, kv_heads, head_dim, page, [L], [1], 41)
+    cache.mul_(0.1)
+    inside, outside = L - window, L - window - 1
+    qv = q[0, :head_dim].float()
+    big = (qv / qv.norm() * 60.0 / (qv.norm() / math.sqrt(head_dim))).to(dtype)
+    for pos, val in ((inside, 1.0), (outside, -1.0)):
+        pg, off = int(meta.block_table[0, pos // page]), pos % page
+        cache[pg, 0, 0, off] = big
+        cache[pg, 1, 0, off] = val
+    out = torch.empty(1, heads * head_dim, device="cuda", dtype=dtype)
+    K.attention(q, cache, meta, out, heads, kv_heads, head_dim, window=window)
+    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads,
+                                 head_dim, window)
+    close(out, want, dtype)
+    assert out[0, :head_dim].float().mean() > 0.9
+
+
+def test_attention_refuses_odd_head_size(K):
+    from iitj_llm_coopt_b200.kernels import KernelError
+    q, cache, meta = _paged_case(torch.float32, 2, 1, 24, 16, [5], [5], 50)
+    out = torch.empty(5, 48, device="cuda")
+    with pytest.raises(KernelError):
+        K.attention(q, cache, meta, out, 2, 1, 24)
+
+
+@pytest.mark.parametrize("vocab", [320, 1000, 128256])
+def test_sample_greedy_and_ties(K, vocab):
+    logits = rnd((6, vocab), torch.float32, 60)
+    logits[2, 5] = logits[2, vocab - 3] = 50.0                # a tie: the lowest index wins
+    logits[3, vocab - 1] = 60.0
+    out = torch.empty(6, device="cuda", dtype=torch.int32)
+    K.sample(logits, None, None, out)
+    assert out.tolist() == logits.argmax(-1).tolist()
+    assert out[2].item() == 5 and out[3].item() == vocab - 1
+
+
+def test_sample_temperature_matches_reference_stream(K):
+    from iitj_llm_coopt_b200.sampling import row_key
+    vocab, rows = 1000, 64
+    logits = rnd((rows, vocab), torch.float32, 61, 2.0)
+    temps = torch.tensor([0.0 if r % 4 == 0 else 0.5 + 0.01 * r for r in range(rows)])
+    keys = [row_key(7, r, 3 * r) for r in range(rows)]
+    keys_t = torch.tensor([k - (1 << 64) if k >= (1 << 63) else k for k in keys], dtype=torch.int64)
+    out = torch.empty(rows, device="cuda", dtype=torch.int32)
+    K.sample(logits, temps.cuda(), keys_t.cuda(), out)
+    want, perturbed = R.ref_sample(logits.cpu(), temps, keys)
+    top2 = perturbed.topk(2, dim=-1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 1e-3                  # skip near-ties of the perturbed rows
+    assert clear.sum() > rows // 2
+    assert torch.equal(out.cpu()[clear], want[clear])
+    # the same key gives the same token whatever else is in the batch
+    out1 = torch.empty(1, device="cuda", dtype=torch.int32)
+    K.sample(logits[5:6].contiguous(), temps[5:6].cuda(), keys_t[5:6].cuda(), out1)
+    assert out1.item() == out[5].item()
+
+
+def test_sample_temperature_follows_softmax(K):
+    """Frequencies of 20000 draws from a 5-token distribution against softmax(logits / T)."""
+    from iitj_llm_coopt_b200.sampling import row_key
+    logits = torch.tensor([[1.0, 2.0, 0.0, 3.0, -1.0]]).repeat(20000, 1).cuda()
+    T = 0.8
+    keys = [row_key(1, 2, i) for i in range(20000)]
+    keys_t = torch.tensor([k - (1 << 64) if k >= (1 << 63) else k for k in keys], dtype=torch.int64).cuda()
+    out = torch.empty(20000, device="cuda", dtype=torch.int32)
+    K.sample(logits, torch.full((20000,), T).cuda(), keys_t, out)
+    freq = torch.bincount(out.long().cpu(), minlength=5).float() / 20000
+    want = torch.softmax(logits[0].cpu() / T, -1)
+    assert (freq - want).abs().max() < 0.015, (freq, want)
