@@ -1,0 +1,293 @@
+#!/usr/bin/env python3
+"""Headline benchmark: decode tokens/s and prefill tokens/s of the Llama 3.1 8B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 8192] [--layers L]
+
+Prints ONE JSON line.  `value` is decoded tokens per second at the given batch (default 8)
+with `context` tokens per request already in the cache, timed on the device with CUDA
+events around each decode step (model step + sampling kernel).  `e2e` is the same metric
+through the Python entry point (`LLM.generate`: host token ids in, host token ids out,
+prefill included in the run but not in the decode rate, which is counted from the first
+to the last generated token).  `prefill` is one 2,048-token prompt in one step; `roofline`
+relates the decode step's mandatory HBM reads to its time; `points` holds decode at batch
+1 and 64.  Weights are random (seeded, drawn on the device), token ids are random.
+
+The reference arm (`--impl reference`) is unavailable: the reference is a folder of
+scripts without setup.py or pyproject.toml, so the offline install cannot build it.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Llama 3.1 8B: the sizes of the benchmark configuration (random weights, no checkpoint)
+LLAMA_8B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": False, "max_position_embeddings": 131072, "eos_token_id": 128001,
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                raw = json.load(f)
+            peaks = {k: float(raw[k]) for k in FALLBACK_PEAKS if k in raw}
+            if "hbm_gbs" in peaks and "bf16_tflops" in peaks:
+                peaks.setdefault("bf16_tflops_sustained", peaks["bf16_tflops"])
+                return peaks, "measured"
+        except (OSError, ValueError, KeyError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi in the background: SM clock and throttle reasons during the timed region."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc, self.lines = None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag == "Active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def matmul_weight_bytes(cfg, itemsize=2):
+    """Bytes of every matrix a decode step reads once: the layers' four projections and the head."""
+    h, inter, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    H, Hkv, D, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["vocab_size"]
+    per_layer = (H + 2 * Hkv) * D * h + h * H * D + 2 * inter * h + h * inter
+    return (L * per_layer + V * h) * itemsize
+
+
+def prefill_flops(cfg, T, rows=1):
+    h, inter, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    H, Hkv, D, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["vocab_size"]
+    linear = 2 * T * ((H + 2 * Hkv) * D * h + h * H * D + 2 * inter * h + h * inter)
+    attention = 4 * (T * (T + 1) // 2) * H * D
+    return L * (linear + attention) + 2 * rows * h * V
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (reported)")
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-points", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference has no setup.py or pyproject.toml: 'pip install --no-index ... /root/reference' "
+                          "fails with 'not installable'; its engine also needs vLLM's CUDA ops and a downloaded checkpoint"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (only --gpus 1)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from iitj_llm_coopt_b200 import EngineConfig, LlamaConfig, SamplingParams, StepEntry, build_engine
+    from iitj_llm_coopt_b200.engine.llm import LLM
+
+    peaks, peak_source = load_peaks()
+    cfg = dict(LLAMA_8B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    typed = LlamaConfig.from_dict(cfg)
+    B, C, K, W = args.batch, args.context, args.steps, args.warmup
+    page = 16
+    biggest = max(B, 1 if args.no_points else 64)
+    pool_tokens = biggest * (C + K + W + 2 * page) + args.prefill_tokens + 4 * page
+    ec = EngineConfig(dtype="bfloat16", page_size=page, num_pages=-(-pool_tokens // page), max_num_seqs=max(biggest, 8),
+                      max_num_batched_tokens=max(args.prefill_tokens, biggest), max_model_len=C + K + W + 64, seed=0)
+    t_build = time.time()
+    engine = build_engine(None, ec, config=typed, random_seed=2)
+    runner, cache, sampler, kernels = engine.runner, engine.cache, engine.sampler, engine.sampler.k
+    for g in cache.groups:                      # contexts "already in the cache": random keys and values
+        if g.storage is not None:
+            g.storage.normal_(0.0, 0.5)
+    torch.cuda.synchronize()
+    build_s = time.time() - t_build
+    gen = torch.Generator().manual_seed(0)
+
+    def decode_run(batch, steps, warmup):
+        """Device-timed decode steps at `batch` with C tokens per request in the cache."""
+        ids = [f"d{batch}_{i}" for i in range(batch)]
+        for r in ids:
+            cache.admit(r)
+            cache.ensure(r, C)
+            cache.advance(r, C)
+        toks = torch.randint(0, typed.vocab_size, (batch,), generator=gen).tolist()
+        rows = [(0.0, 0, 0)] * batch
+        times, launches = [], 0
+        for it in range(warmup + steps):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            entries = [StepEntry(r, [t], [0]) for r, t in zip(ids, toks)]
+            l0 = kernels.launches
+            torch.cuda.synchronize()
+            start.record()
+            logits = runner.step(entries)
+            out, host = sampler._buffers(batch)
+            kernels.sample(logits, None, None, out)
+            end.record()
+            torch.cuda.synchronize()
+            toks = out.tolist()
+            if it >= warmup:
+                times.append(start.elapsed_time(end))
+                launches += kernels.launches - l0
+        for r in ids:
+            cache.release(r)
+            runner.forget(r)
+        return times, launches
+
+    def prefill_run(T, reps, warmup):
+        times = []
+        for it in range(warmup + reps):
+            cache.admit("p")
+            toks = torch.randint(0, typed.vocab_size, (T,), generator=gen).tolist()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            runner.step([StepEntry("p", toks, [T - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            cache.release("p")
+            runner.forget("p")
+            if it >= warmup:
+                times.append(start.elapsed_time(end))
+        return times
+
+    clocks = ClockSampler()
+    clocks.start()
+    times, launches = decode_run(B, K, W)
+    clock_rec = clocks.stop()
+    ms = sum(times) / len(times)
+    value = B / (ms / 1e3)
+
+    weight_bytes = matmul_weight_bytes(cfg)
+    kv_bytes = B * (C + W + K / 2) * typed.kv_bytes_per_token(2)
+    achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
+
+    p_times = prefill_run(args.prefill_tokens, 5, 3)
+    p_ms = statistics.median(p_times)
+    p_flops = prefill_flops(cfg, args.prefill_tokens)
+    prefill = {"value": args.prefill_tokens / (p_ms / 1e3), "tokens": args.prefill_tokens, "ms": p_ms,
+               "frac": p_flops / (p_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), "peak": f"of {peak_source}"}
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            t, _ = decode_run(b, max(8, K // 2), 3)
+            points[f"decode_b{b}"] = b / (sum(t) / len(t) / 1e3)
+
+    e2e = None
+    if not args.no_e2e:
+        # through the public entry point: host token ids in, host token ids out
+        llm = LLM.__new__(LLM)
+        llm.engine = engine
+        prompts = [torch.randint(0, typed.vocab_size, (C,), generator=gen).tolist() for _ in range(B)]
+        stamps = []
+        first = {}
+
+        def on_out(seq, new, fin):
+            now = time.perf_counter()
+            first.setdefault(seq.seq_id, now)
+            stamps.append(now)
+
+        seqs = [engine.new_sequence(p, K + 1, 0.0, True, None, on_out) for p in prompts]
+        engine.run_until_done()
+        torch.cuda.synchronize()
+        t_first, t_last = max(first.values()), max(stamps)
+        decoded = sum(len(s.tokens) - s.prompt_len - 1 for s in seqs)
+        h2d = (4 * B + (B + 1) + 4 * B + B * (-(-(C + K) // page))) * 4     # ids, positions, maps, lengths, block table
+        e2e = {"value": decoded / (t_last - t_first), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": 4 * B}
+
+    line = {
+        "metric": "decode tok/s at batch 8 (Llama 3.1 8B shape, 8192-token contexts); prefill and batch 1/64 alongside",
+        "value": value, "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "llama-3.1-8b-shape-random", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": B, "seq_len": C, "page_size": page, "parallelism": "single-gpu",
+                   "l2": "inputs larger than L2 (a step reads >15 GB of weights)", "weights": "random seed 2"},
+        "clocks": clock_rec,
+        "e2e": e2e,
+        "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "peak_source": f"of {peak_source}"},
+        "points": points,
+        "build_seconds": build_s,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
