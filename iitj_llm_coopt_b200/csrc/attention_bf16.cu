@@ -1,0 +1,465 @@
+// bfloat16 paged attention on the tensor cores (mma.sync m16n8k16, float32 accumulation),
+// head sizes 64 and 128, groups of up to 16 query heads per key/value head.
+//
+//   attn_prefill_kernel  prompt portions: one CTA = 64 queries of one request x one query head;
+//                        keys/values walk through shared memory in tiles of 64 keys fetched
+//                        page by page with cp.async (any page size); online softmax in float32;
+//                        causal mask by position, optional sliding window.
+//   attn_decode_kernel   single decoded tokens: one CTA = one request x one key/value head x one
+//                        range of keys ("split"); the group's query heads are the rows of the
+//                        16-row MMA tile, so a key/value tile is read once for the whole group.
+//                        With more than one split the partial (max, sum, output) go to scratch
+//                        memory and attn_merge_kernel combines them.
+//
+// Replaces flash_attn_varlen_func with block_table (engine/model.py:204-207, 244-247).
+// Softmax statistics, the running output and all sums are float32; P is rounded to bfloat16
+// only as the operand of P.V.  Tiles start at multiples of 64 of the key position, so a
+// query's result does not depend on the batch it is computed in.
+#include "common.cuh"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int kTile = 64;       // keys per shared-memory tile
+constexpr int kThreads = 128;   // 4 warps
+constexpr int kStages = 3;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Element offset of 16-byte chunk `c` of row `r` in a [rows][D] bf16 tile whose chunks are
+// XOR-swizzled by the row, so that the 8 rows an ldmatrix reads fall into different banks.
+template <int D> __device__ __forceinline__ int tile_off(int r, int c) { return r * D + ((c ^ (r & 7)) << 3); }
+
+// Fetch keys [key0, key0 + 64) of one key/value head into a tile; rows past `key_last` repeat
+// that key (their scores are masked by the caller), so no page beyond the request's is touched.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* __restrict__ plane, const int* __restrict__ table,
+                                             int key0, int key_last, int page_size, size_t page_stride) {
+    constexpr int CH = D / 8;
+    for (int i = threadIdx.x; i < kTile * CH; i += kThreads) {
+        const int r = i / CH, c = i % CH;
+        const int key = min(key0 + r, key_last);
+        const int page = table[key / page_size], off = key % page_size;
+        const bf16* src = plane + (size_t)page * page_stride + (size_t)off * D + c * 8;
+        cp_async16(smem_u32(tile + tile_off<D>(r, c)), src);
+    }
+}
+
+// S[16 x 16 keys] for one warp: rows = the A fragments `qa`, keys = tile rows [r0, r0 + 16).
+template <int D>
+__device__ __forceinline__ void qk_16keys(float (&s0)[4], float (&s1)[4], const uint32_t (&qa)[D / 16][4],
+                                          const bf16* ktile, int r0, int lane) {
+#pragma unroll
+    for (int kt = 0; kt < D / 16; ++kt) {
+        uint32_t b[4];
+        const int row = r0 + ((lane >> 4) << 3) + (lane & 7);
+        const int chunk = 2 * kt + ((lane >> 3) & 1);
+        ldmatrix_x4(b, smem_u32(ktile + tile_off<D>(row, chunk)));
+        mma_bf16(s0, qa[kt], b[0], b[1]);
+        mma_bf16(s1, qa[kt], b[2], b[3]);
+    }
+}
+
+// O[16 x D] += P[16 x 16 keys] . V[16 keys x D], V rows = tile rows [r0, r0 + 16).
+template <int D>
+__device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (&pa)[4], const bf16* vtile, int r0, int lane) {
+#pragma unroll
+    for (int n2 = 0; n2 < D / 16; ++n2) {
+        uint32_t b[4];
+        const int row = r0 + (((lane >> 3) & 1) << 3) + (lane & 7);
+        const int chunk = 2 * n2 + (lane >> 4);
+        ldmatrix_x4_trans(b, smem_u32(vtile + tile_off<D>(row, chunk)));
+        mma_bf16(o[2 * n2], pa, b[0], b[1]);
+        mma_bf16(o[2 * n2 + 1], pa, b[2], b[3]);
+    }
+}
+
+// One online-softmax update for the two rows (g, g + 8) a thread holds, over 16 keys
+// (s0: keys 0-7, s1: keys 8-15 of the slice).  Scores arrive raw; `sl` = scale * log2(e).
+// Returns the bf16 A fragment of P and rescales `o`.
+template <int D>
+__device__ __forceinline__ void softmax_16keys(float (&s0)[4], float (&s1)[4], float (&m)[2], float (&l)[2],
+                                               float (&o)[D / 8][4], uint32_t (&pa)[4], float sl) {
+    float mx0 = fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]));
+    float mx1 = fmaxf(fmaxf(s0[2], s0[3]), fmaxf(s1[2], s1[3]));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m[0], mx0 * sl), mn1 = fmaxf(m[1], mx1 * sl);
+    const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;  // nothing visible yet
+    const float c0 = exp2f(m[0] - mu0), c1 = exp2f(m[1] - mu1);
+    m[0] = mn0;
+    m[1] = mn1;
+    float p00 = exp2f(s0[0] * sl - mu0), p01 = exp2f(s0[1] * sl - mu0), p02 = exp2f(s0[2] * sl - mu1), p03 = exp2f(s0[3] * sl - mu1);
+    float p10 = exp2f(s1[0] * sl - mu0), p11 = exp2f(s1[1] * sl - mu0), p12 = exp2f(s1[2] * sl - mu1), p13 = exp2f(s1[3] * sl - mu1);
+    l[0] = l[0] * c0 + (p00 + p01 + p10 + p11);
+    l[1] = l[1] * c1 + (p02 + p03 + p12 + p13);
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+        o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1;
+    }
+    pa[0] = pack_bf16(p00, p01);
+    pa[1] = pack_bf16(p02, p03);
+    pa[2] = pack_bf16(p10, p11);
+    pa[3] = pack_bf16(p12, p13);
+}
+
+// ---------------------------------------------------------------------------------------
+// prompt portions
+// ---------------------------------------------------------------------------------------
+// tiles[i] = {first token row, rows (<= 64), position of the first row, request}
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
+                    const int* __restrict__ block_table, int table_width, const int4* __restrict__ tiles,
+                    bf16* __restrict__ out, int out_stride, int heads, int kv_heads, int page_size, int window,
+                    float sl) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* qtile = reinterpret_cast<bf16*>(smem_raw);              // [64][D]
+    bf16* kv = qtile + kTile * D;                                 // [2 stages][K,V][64][D]
+    const int4 td = tiles[blockIdx.x];
+    const int tok0 = td.x, rows = td.y, pos0 = td.z, req = td.w;
+    const int h = blockIdx.y, hk = h / (heads / kv_heads);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int* table = block_table + (size_t)req * table_width;
+    const size_t plane = (size_t)kv_heads * page_size * D;
+    const bf16* kplane = cache + (size_t)hk * page_size * D;
+    const bf16* vplane = kplane + plane;
+    const int pos_last = pos0 + rows - 1;
+    const int lo0 = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int k_begin = lo0 & ~(kTile - 1);
+    const int n_tiles = (pos_last - k_begin) / kTile + 1;
+
+    // Q tile (rows past `rows` are zero)
+    constexpr int CH = D / 8;
+    for (int i = threadIdx.x; i < kTile * CH; i += kThreads) {
+        const int r = i / CH, c = i % CH;
+        bf16* dst = qtile + tile_off<D>(r, c);
+        if (r < rows)
+            cp_async16(smem_u32(dst), q + (size_t)(tok0 + r) * q_stride + (size_t)h * D + c * 8);
+        else
+            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    auto stage_k = [&](int s) { return kv + (size_t)s * 2 * kTile * D; };
+    auto stage_v = [&](int s) { return kv + (size_t)s * 2 * kTile * D + kTile * D; };
+    load_kv_tile<D>(stage_k(0), kplane, table, k_begin, pos_last, page_size, 2 * plane);
+    load_kv_tile<D>(stage_v(0), vplane, table, k_begin, pos_last, page_size, 2 * plane);
+    cp_async_commit();
+
+    uint32_t qa[D / 16][4];
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int row_pos0 = pos0 + warp * 16 + g, row_pos1 = row_pos0 + 8;  // positions of this thread's two rows
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int k0 = k_begin + it * kTile;
+        if (it + 1 < n_tiles) {
+            load_kv_tile<D>(stage_k((it + 1) & 1), kplane, table, k0 + kTile, pos_last, page_size, 2 * plane);
+            load_kv_tile<D>(stage_v((it + 1) & 1), vplane, table, k0 + kTile, pos_last, page_size, 2 * plane);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (it == 0) {
+#pragma unroll
+            for (int kt = 0; kt < D / 16; ++kt) {
+                const int row = warp * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+                ldmatrix_x4(qa[kt], smem_u32(qtile + tile_off<D>(row, 2 * kt + (lane >> 4))));
+            }
+        }
+        const bf16* kt_s = stage_k(it & 1);
+        const bf16* vt_s = stage_v(it & 1);
+        const bool need_mask = (k0 + kTile - 1 > pos0) || (window > 0 && k0 < pos_last - window + 1);
+#pragma unroll
+        for (int ks = 0; ks < kTile / 16; ++ks) {       // 16 keys at a time
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            qk_16keys<D>(s0, s1, qa, kt_s, ks * 16, lane);
+            if (need_mask) {
+                const int kb = k0 + ks * 16 + 2 * t4;
+                const int lo_a = window > 0 ? row_pos0 - window + 1 : 0, lo_b = window > 0 ? row_pos1 - window + 1 : 0;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    if (kb + e > row_pos0 || kb + e < lo_a) s0[e] = -INFINITY;
+                    if (kb + e > row_pos1 || kb + e < lo_b) s0[2 + e] = -INFINITY;
+                    if (kb + 8 + e > row_pos0 || kb + 8 + e < lo_a) s1[e] = -INFINITY;
+                    if (kb + 8 + e > row_pos1 || kb + 8 + e < lo_b) s1[2 + e] = -INFINITY;
+                }
+            }
+            uint32_t pa[4];
+            softmax_16keys<D>(s0, s1, m, l, o, pa, sl);
+            pv_16keys<D>(o, pa, vt_s, ks * 16, lane);
+        }
+        __syncthreads();   // the stage is refilled two iterations later
+    }
+    // row sums live in 4 lanes each
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    const int r0 = warp * 16 + g, r1 = r0 + 8;
+    const float i0 = 1.f / l[0], i1 = 1.f / l[1];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+        const int col = h * D + n * 8 + 2 * t4;
+        if (r0 < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t)(tok0 + r0) * out_stride + col) = pack_bf16(o[n][0] * i0, o[n][1] * i0);
+        if (r1 < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t)(tok0 + r1) * out_stride + col) = pack_bf16(o[n][2] * i1, o[n][3] * i1);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// decoded tokens (one query per request), keys split over CTAs
+// ---------------------------------------------------------------------------------------
+// part_o [items, heads, max_splits, D] float32 (unnormalised, relative to the split's max),
+// part_ml [items, heads, max_splits, 2] float32 (max in the log2 domain, sum).
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
+                   const int* __restrict__ block_table, int table_width, const int* __restrict__ items,
+                   const int* __restrict__ token_request, const int* __restrict__ positions,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out, int out_stride,
+                   int heads, int kv_heads, int page_size, int window, float sl, int keys_per_split, int max_splits) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* kv = reinterpret_cast<bf16*>(smem_raw);                 // [kStages][K,V][64][D]
+    const int split = blockIdx.x, hk = blockIdx.y, item = blockIdx.z;
+    const int tok = items[item];
+    const int pos = positions[tok];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int k_begin = lo & ~(kTile - 1);
+    const int n_splits = (pos - k_begin) / keys_per_split + 1;
+    if (split >= n_splits) return;
+    const int c0 = k_begin + split * keys_per_split;
+    const int c1 = min(c0 + keys_per_split, pos + 1);             // keys [c0, c1)
+    const int n_tiles = (c1 - c0 + kTile - 1) / kTile;
+    const int G = heads / kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int* table = block_table + (size_t)token_request[tok] * table_width;
+    const size_t plane = (size_t)kv_heads * page_size * D;
+    const bf16* kplane = cache + (size_t)hk * page_size * D;
+    const bf16* vplane = kplane + plane;
+    auto stage_k = [&](int s) { return kv + (size_t)s * 2 * kTile * D; };
+    auto stage_v = [&](int s) { return kv + (size_t)s * 2 * kTile * D + kTile * D; };
+
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) {
+        if (s < n_tiles) {
+            load_kv_tile<D>(stage_k(s), kplane, table, c0 + s * kTile, pos, page_size, 2 * plane);
+            load_kv_tile<D>(stage_v(s), vplane, table, c0 + s * kTile, pos, page_size, 2 * plane);
+        }
+        cp_async_commit();
+    }
+    // the group's query heads are rows 0 .. G-1 of the MMA tile; the other rows are zero
+    uint32_t qa[D / 16][4];
+    const bf16* qrow0 = q + (size_t)tok * q_stride + (size_t)(hk * G + g) * D;
+    const bf16* qrow1 = qrow0 + 8 * D;
+#pragma unroll
+    for (int kt = 0; kt < D / 16; ++kt) {
+        qa[kt][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + kt * 16 + 2 * t4) : 0u;
+        qa[kt][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + kt * 16 + 2 * t4) : 0u;
+        qa[kt][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + kt * 16 + 8 + 2 * t4) : 0u;
+        qa[kt][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + kt * 16 + 8 + 2 * t4) : 0u;
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int nxt = it + kStages - 1;
+        cp_async_wait<kStages - 2>();
+        __syncthreads();                      // tile `it` has landed; stage (it-1)%S is free again
+        if (nxt < n_tiles) {
+            load_kv_tile<D>(stage_k(nxt % kStages), kplane, table, c0 + nxt * kTile, pos, page_size, 2 * plane);
+            load_kv_tile<D>(stage_v(nxt % kStages), vplane, table, c0 + nxt * kTile, pos, page_size, 2 * plane);
+        }
+        cp_async_commit();
+        const int k0 = c0 + it * kTile + warp * 16;               // this warp's 16 keys of the tile
+        if (k0 < c1) {
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            qk_16keys<D>(s0, s1, qa, stage_k(it % kStages), warp * 16, lane);
+            if (k0 + 16 > c1 || k0 < lo) {
+                const int kb = k0 + 2 * t4;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    if (kb + e >= c1 || kb + e < lo) s0[e] = s0[2 + e] = -INFINITY;
+                    if (kb + 8 + e >= c1 || kb + 8 + e < lo) s1[e] = s1[2 + e] = -INFINITY;
+                }
+            }
+            uint32_t pa[4];
+            softmax_16keys<D>(s0, s1, m, l, o, pa, sl);
+            pv_16keys<D>(o, pa, stage_v(it % kStages), warp * 16, lane);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    // merge the four warps (each saw other keys) through shared memory: rows < G only
+    float* sm_o = reinterpret_cast<float*>(smem_raw);             // [4][16][D]
+    float* sm_m = sm_o + 4 * 16 * D;                              // [4][16]
+    float* sm_l = sm_m + 4 * 16;                                  // [4][16]
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+        const int col = n * 8 + 2 * t4;
+        if (g < G) { sm_o[(warp * 16 + g) * D + col] = o[n][0]; sm_o[(warp * 16 + g) * D + col + 1] = o[n][1]; }
+        if (g + 8 < G) { sm_o[(warp * 16 + g + 8) * D + col] = o[n][2]; sm_o[(warp * 16 + g + 8) * D + col + 1] = o[n][3]; }
+    }
+    if (t4 == 0) {
+        sm_m[warp * 16 + g] = m[0]; sm_l[warp * 16 + g] = l[0];
+        sm_m[warp * 16 + g + 8] = m[1]; sm_l[warp * 16 + g + 8] = l[1];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * D; i += kThreads) {
+        const int r = i / D, d = i % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + r]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sm_m[w * 16 + r];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            L += sm_l[w * 16 + r] * f;
+            O += sm_o[(w * 16 + r) * D + d] * f;
+        }
+        const int head = hk * G + r;
+        if (n_splits == 1) {
+            out[(size_t)tok * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(O / L);
+        } else {
+            const size_t base = ((size_t)item * heads + head) * max_splits + split;
+            part_o[base * D + d] = O;
+            if (d == 0) { part_ml[base * 2] = M; part_ml[base * 2 + 1] = L; }
+        }
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(D)
+attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ items,
+                  const int* __restrict__ positions, bf16* __restrict__ out, int out_stride, int heads, int window,
+                  int keys_per_split, int max_splits) {
+    const int item = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    const int tok = items[item];
+    const int pos = positions[tok];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int n_splits = (pos - (lo & ~(kTile - 1))) / keys_per_split + 1;
+    if (n_splits == 1) return;                                    // the decode kernel wrote the result itself
+    const size_t base = ((size_t)item * heads + head) * max_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    float L = 0.f, O = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float f = exp2f(part_ml[(base + s) * 2] - M);
+        L += part_ml[(base + s) * 2 + 1] * f;
+        O += part_o[(base + s) * D + d] * f;
+    }
+    out[(size_t)tok * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(O / L);
+}
+
+template <typename K> int set_smem(K kernel, size_t bytes, const char* name) {
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) LLM_FAIL(-2, "%s: %s", name, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+}  // namespace
+
+// 1 if the tensor-core kernels take this shape, else 0 (the caller then uses the general kernel).
+LLM_API int llm_attention_bf16_supported(int heads, int kv_heads, int head_dim) {
+    return (head_dim == 64 || head_dim == 128) && kv_heads > 0 && heads % kv_heads == 0 && heads / kv_heads <= 16;
+}
+
+// tiles: [n_tiles] int4 {first token row, rows, position of the first row, request}
+LLM_API int llm_attention_prefill_bf16(const void* q, int q_stride, const void* cache, const int* block_table,
+                                       int table_width, const int* tiles, int n_tiles, void* out, int out_stride,
+                                       int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
+                                       cudaStream_t stream) {
+    if (n_tiles == 0) return 0;
+    if (!llm_attention_bf16_supported(heads, kv_heads, head_dim))
+        LLM_FAIL(-1, "attention_prefill_bf16: heads %d / kv_heads %d / head_dim %d not supported", heads, kv_heads, head_dim);
+    if (heads > 65535) LLM_FAIL(-1, "attention_prefill_bf16: too many heads");
+    const float sl = scale * 1.4426950408889634f;
+    dim3 grid(n_tiles, heads);
+    auto launch = [&](auto kern, int D) {
+        const size_t smem = (size_t)(kTile * D + 2 * 2 * kTile * D) * sizeof(bf16);
+        if (set_smem(kern, smem, "attention_prefill_bf16")) return -2;
+        kern<<<grid, kThreads, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, block_table, table_width,
+                                               (const int4*)tiles, (bf16*)out, out_stride, heads, kv_heads, page_size,
+                                               window, sl);
+        LLM_CHECK_LAUNCH("attention_prefill_bf16");
+        return 0;
+    };
+    return head_dim == 64 ? launch(attn_prefill_kernel<64>, 64) : launch(attn_prefill_kernel<128>, 128);
+}
+
+// items: [n_items] token rows of the decoded tokens.  part_o needs n_items*heads*max_splits*head_dim floats,
+// part_ml n_items*heads*max_splits*2 floats (both unused when max_splits == 1).
+LLM_API int llm_attention_decode_bf16(const void* q, int q_stride, const void* cache, const int* block_table,
+                                      int table_width, const int* items, int n_items, const int* token_request,
+                                      const int* positions, float* part_o, float* part_ml, void* out, int out_stride,
+                                      int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
+                                      int keys_per_split, int max_splits, cudaStream_t stream) {
+    if (n_items == 0) return 0;
+    if (!llm_attention_bf16_supported(heads, kv_heads, head_dim))
+        LLM_FAIL(-1, "attention_decode_bf16: heads %d / kv_heads %d / head_dim %d not supported", heads, kv_heads, head_dim);
+    if (keys_per_split <= 0 || keys_per_split % kTile) LLM_FAIL(-1, "attention_decode_bf16: keys_per_split must be a multiple of 64");
+    if (max_splits < 1 || kv_heads > 65535 || n_items > 65535) LLM_FAIL(-1, "attention_decode_bf16: grid out of range");
+    if (max_splits > 1 && (!part_o || !part_ml)) LLM_FAIL(-1, "attention_decode_bf16: scratch is missing");
+    const float sl = scale * 1.4426950408889634f;
+    dim3 grid(max_splits, kv_heads, n_items);
+    auto launch = [&](auto kern, auto merge, int D) {
+        size_t smem = (size_t)kStages * 2 * kTile * D * sizeof(bf16);
+        const size_t merge_smem = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
+        if (merge_smem > smem) smem = merge_smem;
+        if (set_smem(kern, smem, "attention_decode_bf16")) return -2;
+        kern<<<grid, kThreads, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, block_table, table_width, items,
+                                               token_request, positions, part_o, part_ml, (bf16*)out, out_stride, heads,
+                                               kv_heads, page_size, window, sl, keys_per_split, max_splits);
+        LLM_CHECK_LAUNCH("attention_decode_bf16");
+        if (max_splits > 1) {
+            merge<<<dim3(n_items, heads), D, 0, stream>>>(part_o, part_ml, items, positions, (bf16*)out, out_stride, heads,
+                                                          window, keys_per_split, max_splits);
+            LLM_CHECK_LAUNCH("attention_merge");
+        }
+        return 0;
+    };
+    return head_dim == 64 ? launch(attn_decode_kernel<64>, attn_merge_kernel<64>, 64)
+                          : launch(attn_decode_kernel<128>, attn_merge_kernel<128>, 128);
+}

@@ -40,6 +40,12 @@ _SIGNATURES = {
     "llm_silu_mul": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "llm_attention_generic": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "llm_attention_bf16_supported": [_c_int, _c_int, _c_int],
+    "llm_attention_prefill_bf16": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int,
+                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "llm_attention_decode_bf16": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                  _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                  _c_float, _c_int, _c_int, _c_void_p],
     "llm_gemm_f32": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                      _c_void_p],
     "llm_sample": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
@@ -66,6 +72,58 @@ def _check(t, name, dtype=None, dims=None):
     _need(t.is_contiguous(), f"{name}: tensor must be contiguous")
 
 
+class AttentionPlan:
+    """How one step's tokens are handed to the tensor-core attention kernels: requests that
+    bring one token go to the split-key decode kernel (`items`: their token rows), the rest
+    are cut into tiles of 64 queries for the prefill kernel (`tiles`: first token row, rows,
+    position of the first row, request)."""
+
+    TILE = 64
+
+    def __init__(self, query_lens, seq_lens, device, items=None, tiles=None):
+        self.decode_pos = []
+        item_rows, tile_rows, row = [], [], 0
+        for b, (n, total) in enumerate(zip(query_lens, seq_lens)):
+            if n == 1:
+                item_rows.append(row)
+                self.decode_pos.append(total - 1)
+            else:
+                for s in range(0, n, self.TILE):
+                    tile_rows.append((row + s, min(self.TILE, n - s), total - n + s, b))
+            row += n
+        self.n_items, self.n_tiles = len(item_rows), len(tile_rows)
+        self.items, self.tiles = items, tiles
+        if self.items is None and item_rows:
+            self.items = torch.tensor(item_rows, dtype=torch.int32).to(device)
+        if self.tiles is None and tile_rows:
+            self.tiles = torch.tensor(tile_rows, dtype=torch.int32).to(device)
+        self.item_rows, self.tile_rows = item_rows, tile_rows
+        self._splits: dict = {}
+
+    def split(self, kv_heads: int, window: int, sm_count: int):
+        """(keys per split, most splits of any item): enough CTAs to fill the GPU about four
+        times over, but no split shorter than 256 keys."""
+        key = (kv_heads, window)
+        if key not in self._splits:
+            spans = []
+            for pos in self.decode_pos:
+                lo = max(0, pos - window + 1) if window > 0 else 0
+                spans.append(pos - (lo // self.TILE) * self.TILE + 1)
+            longest = max(spans)
+            want = max(1, -(-4 * sm_count // (self.n_items * kv_heads)))
+            kps = max(256, -(-(-(-longest // want)) // self.TILE) * self.TILE)
+            self._splits[key] = (kps, max((s - 1) // kps + 1 for s in spans))
+        return self._splits[key]
+
+
+def attention_plan(meta, device) -> AttentionPlan:
+    plan = getattr(meta, "attention_plan", None)
+    if plan is None:
+        plan = AttentionPlan(meta.query_lens, meta.seq_lens_host, device)
+        meta.attention_plan = plan
+    return plan
+
+
 class Kernels:
     """Checked entry points of libllm_kernels.so.  One instance per process (see `load`)."""
 
@@ -78,6 +136,22 @@ class Kernels:
             fn.argtypes = args
             fn.restype = _c_int
         self.launches = 0  # kernels of this library launched so far (the bench reports it)
+        self._scratch_bufs: dict = {}
+        self._sm_count = None
+
+    @property
+    def sm_count(self) -> int:
+        if self._sm_count is None:
+            self._sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        return self._sm_count
+
+    def _scratch(self, name, floats, device):
+        """Grow-only float32 scratch (split-attention partials); contents never outlive a call."""
+        buf = self._scratch_bufs.get((name, device))
+        if buf is None or buf.numel() < floats:
+            buf = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=device)
+            self._scratch_bufs[(name, device)] = buf
+        return buf
 
     # ---- plumbing --------------------------------------------------------------------
     def _call(self, name, *args):
@@ -179,9 +253,30 @@ class Kernels:
               "attention: one token_request and one position per token")
         if not scale:
             scale = 1.0 / math.sqrt(head_dim)
+        page_size = cache_layer.shape[3]
+        if qkv.dtype == torch.bfloat16 and self.lib.llm_attention_bf16_supported(heads, kv_heads, head_dim):
+            plan = attention_plan(meta, qkv.device)
+            if plan.n_tiles:
+                self._call("llm_attention_prefill_bf16", _ptr(qkv), qkv.shape[1], _ptr(cache_layer),
+                           _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.tiles), plan.n_tiles, _ptr(out),
+                           out.shape[1], heads, kv_heads, head_dim, page_size, int(window), float(scale), self._stream())
+            if plan.n_items:
+                kps, splits = plan.split(kv_heads, int(window), self.sm_count)
+                part_o = part_ml = None
+                if splits > 1:
+                    part_o = self._scratch("attn.part_o", plan.n_items * heads * splits * head_dim, qkv.device)
+                    part_ml = self._scratch("attn.part_ml", plan.n_items * heads * splits * 2, qkv.device)
+                self._call("llm_attention_decode_bf16", _ptr(qkv), qkv.shape[1], _ptr(cache_layer),
+                           _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.items), plan.n_items,
+                           _ptr(meta.token_request), _ptr(meta.positions), _ptr(part_o), _ptr(part_ml), _ptr(out),
+                           out.shape[1], heads, kv_heads, head_dim, page_size, int(window), float(scale), kps, splits,
+                           self._stream())
+                if splits > 1:
+                    self.launches += 1      # the merge kernel
+            return out
         self._call("llm_attention_generic", _ptr(qkv), qkv.shape[1], _ptr(cache_layer), _ptr(meta.block_table),
                    meta.block_table.shape[1], _ptr(meta.token_request), _ptr(meta.positions), _ptr(out),
-                   out.shape[1], DTYPE_CODE[qkv.dtype], tokens, heads, kv_heads, head_dim, cache_layer.shape[3],
+                   out.shape[1], DTYPE_CODE[qkv.dtype], tokens, heads, kv_heads, head_dim, page_size,
                    int(window), float(scale), self._stream())
         return out
 

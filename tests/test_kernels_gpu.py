@@ -270,3 +270,44 @@ def test_sample_temperature_follows_softmax(K):
     freq = torch.bincount(out.long().cpu(), minlength=5).float() / 20000
     want = torch.softmax(logits[0].cpu() / T, -1)
     assert (freq - want).abs().max() < 0.015, (freq, want)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,window", [
+    (8, 2, 128, 16, 0), (32, 8, 128, 16, 0), (16, 1, 64, 16, 0), (6, 2, 64, 8, 0), (4, 4, 128, 32, 0),
+    (8, 2, 128, 16, 300), (3, 1, 64, 4, 0)])
+def test_attention_bf16_decode_splits(K, heads, kv_heads, head_dim, page, window):
+    """Only single-token requests, contexts long enough to be cut into several splits."""
+    lens = [700, 300, 1000, 257, 64, 65, 1, 1500]
+    q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lens, [1] * len(lens), 70)
+    out = torch.empty(q.shape[0], heads * head_dim, device="cuda", dtype=torch.bfloat16)
+    K.attention(q, cache, meta, out, heads, kv_heads, head_dim, window=window)
+    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads,
+                                 head_dim, window)
+    close(out, want, torch.bfloat16)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,window", [
+    (8, 2, 128, 16, 0), (4, 1, 64, 16, 0), (6, 2, 64, 8, 0), (2, 2, 128, 64, 0), (4, 2, 128, 16, 100), (4, 2, 64, 16, 64)])
+def test_attention_bf16_prefill_tiles(K, heads, kv_heads, head_dim, page, window):
+    """Portions longer than one 64-query tile, starting at positions that are no multiple of 64."""
+    lens, qlens = [700, 130, 391, 64], [200, 130, 65, 64]
+    q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lens, qlens, 80)
+    out = torch.empty(q.shape[0], heads * head_dim, device="cuda", dtype=torch.bfloat16)
+    K.attention(q, cache, meta, out, heads, kv_heads, head_dim, window=window)
+    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads,
+                                 head_dim, window)
+    close(out, want, torch.bfloat16)
+
+
+def test_attention_bf16_same_result_in_any_batch(K):
+    """A decoded token's output is bitwise the same alone and beside other requests."""
+    heads, kv_heads, head_dim, page = 8, 2, 128, 16
+    lens, qlens = [500, 130, 77], [1, 40, 1]
+    q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lens, qlens, 90)
+    out = torch.empty(q.shape[0], heads * head_dim, device="cuda", dtype=torch.bfloat16)
+    K.attention(q, cache, meta, out, heads, kv_heads, head_dim)
+    solo = SimpleNamespace(block_table=meta.block_table[2:3].contiguous(), token_request=torch.zeros(1, dtype=torch.int32, device="cuda"),
+                           positions=meta.positions[41:42].contiguous(), query_lens=[1], seq_lens_host=[77])
+    out1 = torch.empty(1, heads * head_dim, device="cuda", dtype=torch.bfloat16)
+    K.attention(q[41:42].contiguous(), cache, solo, out1, heads, kv_heads, head_dim)
+    assert torch.equal(out1[0], out[41])
