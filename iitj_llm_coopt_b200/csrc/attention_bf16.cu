@@ -463,3 +463,64 @@ LLM_API int llm_attention_decode_bf16(const void* q, int q_stride, const void* c
     return head_dim == 64 ? launch(attn_decode_kernel<64>, attn_merge_kernel<64>, 64)
                           : launch(attn_decode_kernel<128>, attn_merge_kernel<128>, 128);
 }
+
+// ---------------------------------------------------------------------------------------
+// The same decode attention with its scratch inside the library (see llm_no_alloc.h).
+// ---------------------------------------------------------------------------------------
+#include "llm_no_alloc.h"
+
+#include <mutex>
+
+namespace {
+
+// Partials of the split-key decode kernel for callers without an allocator.  In host code
+// this name is only a handle for cudaGetSymbolAddress; the kernels get the device address.
+static __device__ __align__(256) float g_static_scratch[LLM_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_ptr[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the array on the current device; looked up once per device.
+int static_scratch_address(float** ptr) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) LLM_FAIL(-2, "attention_decode_bf16_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) LLM_FAIL(-1, "attention_decode_bf16_static: device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            LLM_FAIL(-2, "attention_decode_bf16_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_static_scratch_ptr[dev] = static_cast<float*>(p);
+    }
+    *ptr = g_static_scratch_ptr[dev];
+    return 0;
+}
+
+}  // namespace
+
+LLM_API int llm_attention_decode_bf16_static(const void* q, int q_stride, const void* cache, const int* block_table,
+                                             int table_width, const int* items, int n_items, const int* token_request,
+                                             const int* positions, void* out, int out_stride, int heads, int kv_heads,
+                                             int head_dim, int page_size, int window, float scale, int keys_per_split,
+                                             int max_splits, cudaStream_t stream) {
+    if (n_items <= 0) return 0;
+    if (heads <= 0 || head_dim <= 0 || max_splits < 1)
+        LLM_FAIL(-1, "attention_decode_bf16_static: heads, head_dim and max_splits must be positive");
+    const unsigned long long rows = (unsigned long long)n_items * heads * max_splits;
+    const unsigned long long need = rows * (unsigned long long)(head_dim + 2);
+    if (need > LLM_STATIC_SCRATCH_FLOATS)
+        LLM_FAIL(-1, "attention_decode_bf16_static: %d items x %d heads x %d splits x head_dim %d need %llu floats of "
+                     "scratch, the built-in array holds %u; use fewer items or splits per call, or "
+                     "llm_attention_decode_bf16 with your own scratch",
+                 n_items, heads, max_splits, head_dim, need, LLM_STATIC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    float* part_o = scratch;                        // rows * head_dim floats
+    float* part_ml = scratch + rows * head_dim;     // rows * 2 floats
+    return llm_attention_decode_bf16(q, q_stride, cache, block_table, table_width, items, n_items, token_request,
+                                     positions, part_o, part_ml, out, out_stride, heads, kv_heads, head_dim, page_size,
+                                     window, scale, keys_per_split, max_splits, stream);
+}
