@@ -1,0 +1,141 @@
+"""Greedy generation through the Python entry point and the command line, and the replay
+program run as a user would run it, against the plain implementation."""
+import json
+import os
+import struct
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+import replay_cases as cases
+from configs import CONFIGS
+from iitj_llm_coopt_b200 import LLM, SamplingParams
+from iitj_llm_coopt_b200.weights import write_model_dir
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lively_dirs(tmp_path_factory):
+    """The tiny models with a larger weight scale, so that greedy continuations vary."""
+    out = {}
+    for name, (cfg, seed, _page) in CONFIGS.items():
+        d = str(tmp_path_factory.mktemp(f"lively_{name}"))
+        write_model_dir(cfg, d, seed, std=0.08)
+        out[name] = d
+    return out
+
+
+PROMPT_LENS = {"A": [5, 17, 33], "B": [1, 9, 40, 64, 130], "C": [3, 50, 90], "D": [2, 70]}
+
+
+def margins_ok(cfg, w, prompt, got, min_margin):
+    """True if `got` equals the plain greedy continuation, allowing a different token only where the
+    plain implementation's top two logits are closer than min_margin (then stop comparing)."""
+    toks = list(prompt)
+    for t in got:
+        logits = plain.forward(cfg, w, toks)[-1]
+        top = logits.topk(2)
+        if t != int(top.indices[0]):
+            return float(top.values[0] - top.values[1]) < min_margin and t == int(top.indices[1])
+        toks.append(t)
+    return True
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_greedy_generation_through_the_entry_point(lively_dirs, dtype, name):
+    cfg_d, seed, page = CONFIGS[name]
+    cfg, w = plain.read_model_dir(lively_dirs[name], torch.float32)
+    prompts = list(cases.requests_for(cfg_d["vocab_size"], PROMPT_LENS[name], seed + 30).values())
+    n_new = 16 if name == "A" else 24
+    for budget, pages in ((2048, 256), (16, 40)):                 # roomy, then tight: portions and preemption
+        llm = LLM(lively_dirs[name], dtype=dtype, page_size=page, num_pages=pages, max_num_seqs=4,
+                  max_num_batched_tokens=budget)
+        outs = llm.generate(prompts, SamplingParams(max_tokens=n_new, ignore_eos=True))
+        for p, o in zip(prompts, outs):
+            assert o.finish_reason == "length" and len(o.token_ids) == n_new
+            if dtype == "float32":
+                assert o.token_ids == plain.greedy_generate(cfg, w, p, n_new), (name, budget)
+            else:
+                assert margins_ok(cfg, w, p, o.token_ids, 0.05), (name, budget)
+        llm.engine.cache.check()
+        assert llm.engine.cache.num_free == pages
+        del llm
+
+
+def test_temperature_is_reproducible_per_request_and_mixes_with_greedy(lively_dirs):
+    cfg_d, seed, page = CONFIGS["B"]
+    prompts = list(cases.requests_for(cfg_d["vocab_size"], PROMPT_LENS["B"], seed + 31).values())
+    params = [SamplingParams(max_tokens=24, temperature=0.8 if i % 2 == 0 else 0.0, ignore_eos=True, seed=100 + i)
+              for i in range(len(prompts))]
+    runs = []
+    for budget, pages, seqs in ((2048, 256, 8), (24, 64, 2)):
+        llm = LLM(lively_dirs["B"], dtype="float32", page_size=page, num_pages=pages, max_num_seqs=seqs,
+                  max_num_batched_tokens=budget, seed=5)
+        runs.append([o.token_ids for o in llm.generate(prompts, params)])
+        del llm
+    assert runs[0] == runs[1]                                     # same seeds, other batching: same tokens
+    cfg, w = plain.read_model_dir(lively_dirs["B"], torch.float32)
+    for i, p in enumerate(prompts):
+        if i % 2 == 1:
+            assert runs[0][i] == plain.greedy_generate(cfg, w, p, 24)
+    llm = LLM(lively_dirs["B"], dtype="float32", page_size=page, num_pages=256, seed=6)
+    other = [o.token_ids for o in llm.generate(prompts, params)]
+    assert other[0] != runs[0][0]                                 # another engine seed, another draw
+
+
+def test_eos_stops_generation(lively_dirs):
+    cfg_d, seed, page = CONFIGS["C"]
+    cfg, w = plain.read_model_dir(lively_dirs["C"], torch.float32)
+    prompt = cases.requests_for(cfg_d["vocab_size"], [20], 77)["r0"]
+    full = plain.greedy_generate(cfg, w, prompt, 12)
+    import shutil, tempfile
+    d = tempfile.mkdtemp()
+    try:
+        shutil.copy(os.path.join(lively_dirs["C"], "model.safetensors"), d)
+        raw = json.load(open(os.path.join(lively_dirs["C"], "config.json")))
+        raw["eos_token_id"] = full[4]
+        json.dump(raw, open(os.path.join(d, "config.json"), "w"))
+        llm = LLM(d, dtype="float32", num_pages=32)
+        out = llm.generate([prompt], SamplingParams(max_tokens=12))[0]
+        assert out.finish_reason == "stop" and out.token_ids == full[:full.index(full[4]) + 1]
+    finally:
+        shutil.rmtree(d)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_trace_run_program(model_dirs, tmp_path, dtype, name):
+    """bin/trace_run as a subprocess: mixed trace over a pool sized by --max-tokens."""
+    cfg_d, seed, page = CONFIGS[name]
+    reqs = cases.requests_for(cfg_d["vocab_size"], [40, 75, 33, 130, 64, 20], seed + 40)
+    steps, peak = cases.mixed(reqs, live=4, seed=3)
+    lines = cases.as_jsonl(steps)
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dirs[name],
+                           "--dtype", dtype, "--out", str(out), "--max-tokens", str(peak), "--page-size", str(page)],
+                          input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(len(steps))]
+    cfg, w = plain.read_model_dir(model_dirs[name], torch.float32)
+    ref = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    consumed = {rid: 0 for rid in reqs}
+    worst = 0.0
+    V = cfg_d["vocab_size"]
+    for i, (entries, _ends) in enumerate(steps):
+        wanted = sum(len(want) for _, _, want in entries)
+        data = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(wanted, V)
+        r = 0
+        for rid, toks, want in entries:
+            for wpos in want:
+                want_row = ref[rid][consumed[rid] + wpos].numpy()
+                worst = max(worst, float(np.abs(data[r] - want_row).max() / np.abs(want_row).max()))
+                r += 1
+            consumed[rid] += len(toks)
+    assert worst <= (1e-4 if dtype == "float32" else 2e-2), worst
