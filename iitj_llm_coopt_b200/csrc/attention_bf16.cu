@@ -55,18 +55,40 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // XOR-swizzled by the row, so that the 8 rows an ldmatrix reads fall into different banks.
 template <int D> __device__ __forceinline__ int tile_off(int r, int c) { return r * D + ((c ^ (r & 7)) << 3); }
 
-// Fetch keys [key0, key0 + 64) of one key/value head into a tile; rows past `key_last` repeat
-// that key (their scores are masked by the caller), so no page beyond the request's is touched.
+// Page ids of the rows of tile [key0, key0 + 64) that this thread copies (rows past `key_last`
+// repeat that key: their scores are masked by the caller, and no page beyond the request's
+// is touched).  Thread t copies chunk t % CH of rows t / CH, t / CH + RPI, ...
+template <int D> struct TileMap {
+    static constexpr int CH = D / 8;              // 16-byte chunks per row
+    static constexpr int RPI = kThreads / CH;     // rows covered per pass of the CTA
+    static constexpr int ITERS = kTile / RPI;
+};
+
 template <int D>
-__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* __restrict__ plane, const int* __restrict__ table,
-                                             int key0, int key_last, int page_size, size_t page_stride) {
-    constexpr int CH = D / 8;
-    for (int i = threadIdx.x; i < kTile * CH; i += kThreads) {
-        const int r = i / CH, c = i % CH;
+__device__ __forceinline__ void tile_pages(int (&pg)[TileMap<D>::ITERS], const int* __restrict__ table, int key0,
+                                           int key_last, int page_size, int page_shift) {
+    const int r0 = threadIdx.x / TileMap<D>::CH;
+#pragma unroll
+    for (int j = 0; j < TileMap<D>::ITERS; ++j) {
+        const int key = min(key0 + r0 + j * TileMap<D>::RPI, key_last);
+        pg[j] = table[page_shift >= 0 ? key >> page_shift : key / page_size];
+    }
+}
+
+// Issue the copies of one K tile and one V tile (same pages, V plane `v_off` elements after K).
+template <int D>
+__device__ __forceinline__ void load_kv_tiles(bf16* ktile, bf16* vtile, const bf16* __restrict__ kplane, size_t v_off,
+                                              const int (&pg)[TileMap<D>::ITERS], int key0, int key_last, int page_size,
+                                              int page_shift, size_t page_stride) {
+    const int c = threadIdx.x % TileMap<D>::CH, r0 = threadIdx.x / TileMap<D>::CH;
+#pragma unroll
+    for (int j = 0; j < TileMap<D>::ITERS; ++j) {
+        const int r = r0 + j * TileMap<D>::RPI;
         const int key = min(key0 + r, key_last);
-        const int page = table[key / page_size], off = key % page_size;
-        const bf16* src = plane + (size_t)page * page_stride + (size_t)off * D + c * 8;
-        cp_async16(smem_u32(tile + tile_off<D>(r, c)), src);
+        const int off = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+        const bf16* src = kplane + (size_t)pg[j] * page_stride + (size_t)off * D + c * 8;
+        cp_async16(smem_u32(ktile + tile_off<D>(r, c)), src);
+        cp_async16(smem_u32(vtile + tile_off<D>(r, c)), src + v_off);
     }
 }
 
@@ -138,8 +160,8 @@ template <int D>
 __global__ void __launch_bounds__(kThreads)
 attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
                     const int* __restrict__ block_table, int table_width, const int4* __restrict__ tiles,
-                    bf16* __restrict__ out, int out_stride, int heads, int kv_heads, int page_size, int window,
-                    float sl) {
+                    bf16* __restrict__ out, int out_stride, int heads, int kv_heads, int page_size, int page_shift,
+                    int window, float sl) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* qtile = reinterpret_cast<bf16*>(smem_raw);              // [64][D]
     bf16* kv = qtile + kTile * D;                                 // [2 stages][K,V][64][D]
@@ -150,7 +172,6 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     const int* table = block_table + (size_t)req * table_width;
     const size_t plane = (size_t)kv_heads * page_size * D;
     const bf16* kplane = cache + (size_t)hk * page_size * D;
-    const bf16* vplane = kplane + plane;
     const int pos_last = pos0 + rows - 1;
     const int lo0 = window > 0 ? max(0, pos0 - window + 1) : 0;
     const int k_begin = lo0 & ~(kTile - 1);
@@ -168,9 +189,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     }
     auto stage_k = [&](int s) { return kv + (size_t)s * 2 * kTile * D; };
     auto stage_v = [&](int s) { return kv + (size_t)s * 2 * kTile * D + kTile * D; };
-    load_kv_tile<D>(stage_k(0), kplane, table, k_begin, pos_last, page_size, 2 * plane);
-    load_kv_tile<D>(stage_v(0), vplane, table, k_begin, pos_last, page_size, 2 * plane);
+    int pg[TileMap<D>::ITERS];
+    tile_pages<D>(pg, table, k_begin, pos_last, page_size, page_shift);
+    load_kv_tiles<D>(stage_k(0), stage_v(0), kplane, plane, pg, k_begin, pos_last, page_size, page_shift, 2 * plane);
     cp_async_commit();
+    if (n_tiles > 1) tile_pages<D>(pg, table, k_begin + kTile, pos_last, page_size, page_shift);
 
     uint32_t qa[D / 16][4];
     float o[D / 8][4];
@@ -182,9 +205,10 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     for (int it = 0; it < n_tiles; ++it) {
         const int k0 = k_begin + it * kTile;
         if (it + 1 < n_tiles) {
-            load_kv_tile<D>(stage_k((it + 1) & 1), kplane, table, k0 + kTile, pos_last, page_size, 2 * plane);
-            load_kv_tile<D>(stage_v((it + 1) & 1), vplane, table, k0 + kTile, pos_last, page_size, 2 * plane);
+            load_kv_tiles<D>(stage_k((it + 1) & 1), stage_v((it + 1) & 1), kplane, plane, pg, k0 + kTile, pos_last,
+                             page_size, page_shift, 2 * plane);
             cp_async_commit();
+            if (it + 2 < n_tiles) tile_pages<D>(pg, table, k0 + 2 * kTile, pos_last, page_size, page_shift);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -199,26 +223,60 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
         }
         const bf16* kt_s = stage_k(it & 1);
         const bf16* vt_s = stage_v(it & 1);
-        const bool need_mask = (k0 + kTile - 1 > pos0) || (window > 0 && k0 < pos_last - window + 1);
+        // S = Q K^T for the 64 keys of the tile: 8 column blocks of 8 keys
+        float sc[kTile / 8][4];
 #pragma unroll
-        for (int ks = 0; ks < kTile / 16; ++ks) {       // 16 keys at a time
-            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-            qk_16keys<D>(s0, s1, qa, kt_s, ks * 16, lane);
-            if (need_mask) {
-                const int kb = k0 + ks * 16 + 2 * t4;
-                const int lo_a = window > 0 ? row_pos0 - window + 1 : 0, lo_b = window > 0 ? row_pos1 - window + 1 : 0;
+        for (int n = 0; n < kTile / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < kTile / 16; ++ks) qk_16keys<D>(sc[2 * ks], sc[2 * ks + 1], qa, kt_s, ks * 16, lane);
+        const bool need_mask = (k0 + kTile - 1 > pos0) || (window > 0 && k0 < pos_last - window + 1);
+        if (need_mask) {
+            const int lo_a = window > 0 ? row_pos0 - window + 1 : 0, lo_b = window > 0 ? row_pos1 - window + 1 : 0;
+#pragma unroll
+            for (int n = 0; n < kTile / 8; ++n) {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    if (kb + e > row_pos0 || kb + e < lo_a) s0[e] = -INFINITY;
-                    if (kb + e > row_pos1 || kb + e < lo_b) s0[2 + e] = -INFINITY;
-                    if (kb + 8 + e > row_pos0 || kb + 8 + e < lo_a) s1[e] = -INFINITY;
-                    if (kb + 8 + e > row_pos1 || kb + 8 + e < lo_b) s1[2 + e] = -INFINITY;
+                    const int key = k0 + n * 8 + 2 * t4 + e;
+                    if (key > row_pos0 || key < lo_a) sc[n][e] = -INFINITY;
+                    if (key > row_pos1 || key < lo_b) sc[n][2 + e] = -INFINITY;
                 }
             }
-            uint32_t pa[4];
-            softmax_16keys<D>(s0, s1, m, l, o, pa, sl);
-            pv_16keys<D>(o, pa, vt_s, ks * 16, lane);
         }
+        // one online-softmax update per tile
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < kTile / 8; ++n) {
+            mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
+            mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m[0], mx0 * sl), mn1 = fmaxf(m[1], mx1 * sl);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float c0 = exp2f(m[0] - mu0), c1 = exp2f(m[1] - mu1);
+        m[0] = mn0;
+        m[1] = mn1;
+        float sum0 = 0.f, sum1 = 0.f;
+        uint32_t pa[kTile / 16][4];
+#pragma unroll
+        for (int n = 0; n < kTile / 8; ++n) {
+            const float p0 = exp2f(sc[n][0] * sl - mu0), p1 = exp2f(sc[n][1] * sl - mu0);
+            const float p2 = exp2f(sc[n][2] * sl - mu1), p3 = exp2f(sc[n][3] * sl - mu1);
+            sum0 += p0 + p1;
+            sum1 += p2 + p3;
+            pa[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+            pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        l[0] = l[0] * c0 + sum0;
+        l[1] = l[1] * c1 + sum1;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1;
+        }
+#pragma unroll
+        for (int ks = 0; ks < kTile / 16; ++ks) pv_16keys<D>(o, pa[ks], vt_s, ks * 16, lane);
         __syncthreads();   // the stage is refilled two iterations later
     }
     // row sums live in 4 lanes each
@@ -250,7 +308,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ block_table, int table_width, const int* __restrict__ items,
                    const int* __restrict__ token_request, const int* __restrict__ positions,
                    float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out, int out_stride,
-                   int heads, int kv_heads, int page_size, int window, float sl, int keys_per_split, int max_splits) {
+                   int heads, int kv_heads, int page_size, int page_shift, int window, float sl, int keys_per_split,
+                   int max_splits) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* kv = reinterpret_cast<bf16*>(smem_raw);                 // [kStages][K,V][64][D]
     const int split = blockIdx.x, hk = blockIdx.y, item = blockIdx.z;
@@ -268,18 +327,20 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     const int* table = block_table + (size_t)token_request[tok] * table_width;
     const size_t plane = (size_t)kv_heads * page_size * D;
     const bf16* kplane = cache + (size_t)hk * page_size * D;
-    const bf16* vplane = kplane + plane;
     auto stage_k = [&](int s) { return kv + (size_t)s * 2 * kTile * D; };
     auto stage_v = [&](int s) { return kv + (size_t)s * 2 * kTile * D + kTile * D; };
 
+    int pg[TileMap<D>::ITERS];
 #pragma unroll
     for (int s = 0; s < kStages - 1; ++s) {
         if (s < n_tiles) {
-            load_kv_tile<D>(stage_k(s), kplane, table, c0 + s * kTile, pos, page_size, 2 * plane);
-            load_kv_tile<D>(stage_v(s), vplane, table, c0 + s * kTile, pos, page_size, 2 * plane);
+            tile_pages<D>(pg, table, c0 + s * kTile, pos, page_size, page_shift);
+            load_kv_tiles<D>(stage_k(s), stage_v(s), kplane, plane, pg, c0 + s * kTile, pos, page_size, page_shift, 2 * plane);
         }
         cp_async_commit();
     }
+    // page ids of the tile that the first iteration will request, fetched one iteration ahead from here on
+    if (kStages - 1 < n_tiles) tile_pages<D>(pg, table, c0 + (kStages - 1) * kTile, pos, page_size, page_shift);
     // the group's query heads are rows 0 .. G-1 of the MMA tile; the other rows are zero
     uint32_t qa[D / 16][4];
     const bf16* qrow0 = q + (size_t)tok * q_stride + (size_t)(hk * G + g) * D;
@@ -300,11 +361,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
         const int nxt = it + kStages - 1;
         cp_async_wait<kStages - 2>();
         __syncthreads();                      // tile `it` has landed; stage (it-1)%S is free again
-        if (nxt < n_tiles) {
-            load_kv_tile<D>(stage_k(nxt % kStages), kplane, table, c0 + nxt * kTile, pos, page_size, 2 * plane);
-            load_kv_tile<D>(stage_v(nxt % kStages), vplane, table, c0 + nxt * kTile, pos, page_size, 2 * plane);
-        }
+        if (nxt < n_tiles)
+            load_kv_tiles<D>(stage_k(nxt % kStages), stage_v(nxt % kStages), kplane, plane, pg, c0 + nxt * kTile, pos,
+                             page_size, page_shift, 2 * plane);
         cp_async_commit();
+        if (nxt + 1 < n_tiles) tile_pages<D>(pg, table, c0 + (nxt + 1) * kTile, pos, page_size, page_shift);
         const int k0 = c0 + it * kTile + warp * 16;               // this warp's 16 keys of the tile
         if (k0 < c1) {
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -391,6 +452,13 @@ attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
     out[(size_t)tok * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(O / L);
 }
 
+// log2(page_size) if it is a power of two, else -1 (the kernels then divide)
+int page_shift_of(int page_size) {
+    int s = 0;
+    while ((1 << s) < page_size) ++s;
+    return (1 << s) == page_size ? s : -1;
+}
+
 template <typename K> int set_smem(K kernel, size_t bytes, const char* name) {
     if (bytes > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -416,13 +484,14 @@ LLM_API int llm_attention_prefill_bf16(const void* q, int q_stride, const void* 
         LLM_FAIL(-1, "attention_prefill_bf16: heads %d / kv_heads %d / head_dim %d not supported", heads, kv_heads, head_dim);
     if (heads > 65535) LLM_FAIL(-1, "attention_prefill_bf16: too many heads");
     const float sl = scale * 1.4426950408889634f;
+    const int page_shift = page_shift_of(page_size);
     dim3 grid(n_tiles, heads);
     auto launch = [&](auto kern, int D) {
         const size_t smem = (size_t)(kTile * D + 2 * 2 * kTile * D) * sizeof(bf16);
         if (set_smem(kern, smem, "attention_prefill_bf16")) return -2;
         kern<<<grid, kThreads, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, block_table, table_width,
                                                (const int4*)tiles, (bf16*)out, out_stride, heads, kv_heads, page_size,
-                                               window, sl);
+                                               page_shift, window, sl);
         LLM_CHECK_LAUNCH("attention_prefill_bf16");
         return 0;
     };
@@ -443,6 +512,7 @@ LLM_API int llm_attention_decode_bf16(const void* q, int q_stride, const void* c
     if (max_splits < 1 || kv_heads > 65535 || n_items > 65535) LLM_FAIL(-1, "attention_decode_bf16: grid out of range");
     if (max_splits > 1 && (!part_o || !part_ml)) LLM_FAIL(-1, "attention_decode_bf16: scratch is missing");
     const float sl = scale * 1.4426950408889634f;
+    const int page_shift = page_shift_of(page_size);
     dim3 grid(max_splits, kv_heads, n_items);
     auto launch = [&](auto kern, auto merge, int D) {
         size_t smem = (size_t)kStages * 2 * kTile * D * sizeof(bf16);
@@ -451,7 +521,7 @@ LLM_API int llm_attention_decode_bf16(const void* q, int q_stride, const void* c
         if (set_smem(kern, smem, "attention_decode_bf16")) return -2;
         kern<<<grid, kThreads, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, block_table, table_width, items,
                                                token_request, positions, part_o, part_ml, (bf16*)out, out_stride, heads,
-                                               kv_heads, page_size, window, sl, keys_per_split, max_splits);
+                                               kv_heads, page_size, page_shift, window, sl, keys_per_split, max_splits);
         LLM_CHECK_LAUNCH("attention_decode_bf16");
         if (max_splits > 1) {
             merge<<<dim3(n_items, heads), D, 0, stream>>>(part_o, part_ml, items, positions, (bf16*)out, out_stride, heads,

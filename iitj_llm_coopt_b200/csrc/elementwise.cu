@@ -65,6 +65,72 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
         o[i] = from_f32<TD>(row_buf[i] * inv * to_f32(weight[i]));
 }
 
+// Four elements per thread and step (width % 4 == 0): all of a thread's loads are in flight at once.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename TD, typename TW, int PER_THREAD>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                       const int* __restrict__ rows, const TW* __restrict__ weight,
+                                       TD* __restrict__ out, int width, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+    float* res = residual + s * width;
+    const TD* dl = delta ? delta + s * width : nullptr;
+    float4 v[PER_THREAD];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER_THREAD; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < width) {
+            v[j] = Vec4<float>::load(res + i);
+            if (dl) {
+                const float4 d = Vec4<TD>::load(dl + i);
+                v[j].x += d.x; v[j].y += d.y; v[j].z += d.z; v[j].w += d.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < PER_THREAD; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        if (i < width) {
+            if (dl && !rows) Vec4<float>::store(res + i, v[j]);
+            ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+        }
+    }
+    const float total = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+    TD* o = out + (size_t)r * width;
+#pragma unroll
+    for (int j = 0; j < PER_THREAD; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        if (i < width) {
+            const float4 w = Vec4<TW>::load(weight + i);
+            Vec4<TD>::store(o + i, make_float4(v[j].x * inv * w.x, v[j].y * inv * w.y, v[j].z * inv * w.z, v[j].w * inv * w.w));
+        }
+    }
+}
+
 LLM_API int llm_add_rmsnorm(float* residual, const void* delta, const int* rows, const void* weight,
                             int weight_dtype, void* out, int dtype, int out_rows, int width, float eps,
                             cudaStream_t stream) {
@@ -75,6 +141,22 @@ LLM_API int llm_add_rmsnorm(float* residual, const void* delta, const int* rows,
         using TD = decltype(tag);
         return llm_dispatch_dtype(weight_dtype, [&](auto wtag) {
             using TW = decltype(wtag);
+            if (width % 4 == 0 && width <= 4 * 512 * 8) {
+                // up to 512 threads, up to 8 float4 per thread
+                const int vecs = width / 4;
+                int threads = (vecs + 31) / 32 * 32;
+                if (threads > 512) threads = 512;
+                const int per = (vecs + threads - 1) / threads;
+                auto go = [&](auto kern) {
+                    kern<<<out_rows, threads, 0, stream>>>(residual, (const TD*)delta, rows, (const TW*)weight, (TD*)out, width, eps);
+                };
+                if (per <= 1) go(add_rmsnorm_vec_kernel<TD, TW, 1>);
+                else if (per <= 2) go(add_rmsnorm_vec_kernel<TD, TW, 2>);
+                else if (per <= 4) go(add_rmsnorm_vec_kernel<TD, TW, 4>);
+                else go(add_rmsnorm_vec_kernel<TD, TW, 8>);
+                LLM_CHECK_LAUNCH("add_rmsnorm");
+                return 0;
+            }
             auto kern = add_rmsnorm_kernel<TD, TW>;
             if (smem > 48 * 1024) {
                 cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -105,6 +187,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   const float* __restrict__ inv_freq, const int* __restrict__ slots,
                                   T* __restrict__ cache, int heads, int kv_heads, int head_dim,
                                   int rotary_dim, int page_size) {
+    __shared__ float cs[128], sn[128];              // rotary_dim / 2 <= 128 (head_dim <= 256)
     const int t = blockIdx.x;
     const int half = rotary_dim / 2;
     const int row_width = (heads + 2 * kv_heads) * head_dim;
@@ -118,25 +201,23 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
         kbase = (size_t)page * 2 * plane + (size_t)off * head_dim;
     }
     const size_t head_stride = (size_t)page_size * head_dim;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &sn[i], &cs[i]);
+    __syncthreads();
 
-    // rotated pairs of query and key heads
+    // rotated pairs of query and key heads, two neighbouring pairs per step (half is even: head sizes are multiples of 16)
     const int rot_heads = heads + kv_heads;
-    for (int w = threadIdx.x; w < rot_heads * half; w += blockDim.x) {
-        const int h = w / half, i = w % half;
-        const float angle = pos * inv_freq[i];
-        float s, c;
-        sincosf(angle, &s, &c);
+    const int hp = half / 2;
+    for (int w = threadIdx.x; w < rot_heads * hp; w += blockDim.x) {
+        const int h = w / hp, i = (w % hp) * 2;
         T* x = row + (size_t)h * head_dim;
-        const float x1 = to_f32(x[i]), x2 = to_f32(x[i + half]);
-        const T o1 = from_f32<T>(x1 * c - x2 * s);
-        const T o2 = from_f32<T>(x2 * c + x1 * s);
-        if (h < heads) {
-            x[i] = o1;
-            x[i + half] = o2;
-        } else if (slot >= 0) {
-            T* dst = cache + kbase + (size_t)(h - heads) * head_stride;
-            dst[i] = o1;
-            dst[i + half] = o2;
+        const float a0 = to_f32(x[i]), a1 = to_f32(x[i + 1]), b0 = to_f32(x[i + half]), b1 = to_f32(x[i + half + 1]);
+        const T o0 = from_f32<T>(a0 * cs[i] - b0 * sn[i]), o1 = from_f32<T>(a1 * cs[i + 1] - b1 * sn[i + 1]);
+        const T p0 = from_f32<T>(b0 * cs[i] + a0 * sn[i]), p1 = from_f32<T>(b1 * cs[i + 1] + a1 * sn[i + 1]);
+        T* dst = nullptr;
+        if (h < heads) dst = x;
+        else if (slot >= 0) dst = cache + kbase + (size_t)(h - heads) * head_stride;
+        if (dst) {
+            dst[i] = o0; dst[i + 1] = o1; dst[i + half] = p0; dst[i + half + 1] = p1;
         }
     }
     if (slot < 0) return;
@@ -146,11 +227,14 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
         const int h = w / pass, i = rotary_dim + w % pass;
         cache[kbase + (size_t)h * head_stride + i] = row[(size_t)(heads + h) * head_dim + i];
     }
-    // values
+    // values, 16 bytes at a time (head_dim is a multiple of 16 elements)
+    constexpr int V16 = 16 / sizeof(T);
     const T* v = row + (size_t)(heads + kv_heads) * head_dim;
-    for (int w = threadIdx.x; w < kv_heads * head_dim; w += blockDim.x) {
-        const int h = w / head_dim, i = w % head_dim;
-        cache[kbase + plane + (size_t)h * head_stride + i] = v[(size_t)h * head_dim + i];
+    const int per_head = head_dim / V16;
+    for (int w = threadIdx.x; w < kv_heads * per_head; w += blockDim.x) {
+        const int h = w / per_head, i = (w % per_head) * V16;
+        *reinterpret_cast<uint4*>(cache + kbase + plane + (size_t)h * head_stride + i) =
+            *reinterpret_cast<const uint4*>(v + (size_t)h * head_dim + i);
     }
 }
 
@@ -158,8 +242,9 @@ LLM_API int llm_rope_store(void* qkv, const int* positions, const float* inv_fre
                            void* cache, int dtype, int tokens, int heads, int kv_heads, int head_dim,
                            int rotary_dim, int page_size, cudaStream_t stream) {
     if (tokens == 0) return 0;
-    if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
-        LLM_FAIL(-1, "rope_store: rotary_dim %d must be even and at most head_dim %d", rotary_dim, head_dim);
+    if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 3) || head_dim % 16 || head_dim > 256)
+        LLM_FAIL(-1, "rope_store: rotary_dim %d must be a multiple of 4 and at most head_dim %d (a multiple of 16 up to 256)",
+                 rotary_dim, head_dim);
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
         rope_store_kernel<T><<<tokens, 256, 0, stream>>>((T*)qkv, positions, inv_freq, slots, (T*)cache,
@@ -183,13 +268,34 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, i
     }
 }
 
+// inner % 4 == 0: four elements per thread and step
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t total4) {
+    const int inner4 = inner / 4;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / inner4, i = (idx % inner4) * 4;
+        const float4 g = Vec4<T>::load(gu + t * 2 * inner + i);
+        const float4 u = Vec4<T>::load(gu + t * 2 * inner + inner + i);
+        Vec4<T>::store(act + t * inner + i,
+                       make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
+                                   g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
+    }
+}
+
 LLM_API int llm_silu_mul(const void* gu, void* act, int dtype, int tokens, int inner, cudaStream_t stream) {
     const size_t total = (size_t)tokens * inner;
     if (total == 0) return 0;
-    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
-        silu_mul_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gu, (T*)act, inner, total);
+        if (inner % 4 == 0) {
+            const size_t total4 = total / 4;
+            const int blocks = (int)((total4 + 255) / 256 < 148 * 32 ? (total4 + 255) / 256 : 148 * 32);
+            silu_mul_vec_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gu, (T*)act, inner, total4);
+        } else {
+            const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+            silu_mul_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gu, (T*)act, inner, total);
+        }
         LLM_CHECK_LAUNCH("silu_mul");
         return 0;
     });

@@ -100,19 +100,35 @@ class AttentionPlan:
         self.item_rows, self.tile_rows = item_rows, tile_rows
         self._splits: dict = {}
 
-    def split(self, kv_heads: int, window: int, sm_count: int):
-        """(keys per split, most splits of any item): enough CTAs to fill the GPU about four
-        times over, but no split shorter than 256 keys."""
-        key = (kv_heads, window)
+    def split(self, kv_heads: int, window: int, sm_count: int, head_dim: int = 128, bound: int | None = None):
+        """(keys per split, most splits of any item).
+
+        The decode kernel runs `items * kv_heads * splits` CTAs, `slots` of them at a time
+        (2 per SM at head size 128, 4 at 64).  Candidates are scored by waves * (keys per
+        split + a fixed per-CTA cost), which favours split counts that fill whole waves.
+        `bound` replaces the longest context by an upper bound (captured graphs use one so
+        that the choice stays the same while contexts grow)."""
+        key = (kv_heads, window, head_dim, bound)
         if key not in self._splits:
             spans = []
             for pos in self.decode_pos:
                 lo = max(0, pos - window + 1) if window > 0 else 0
                 spans.append(pos - (lo // self.TILE) * self.TILE + 1)
-            longest = max(spans)
-            want = max(1, -(-4 * sm_count // (self.n_items * kv_heads)))
-            kps = max(256, -(-(-(-longest // want)) // self.TILE) * self.TILE)
-            self._splits[key] = (kps, max((s - 1) // kps + 1 for s in spans))
+            longest = max(spans) if bound is None else max(bound, max(spans))
+            slots = sm_count * (2 if head_dim > 64 else 4)
+            pairs = self.n_items * kv_heads
+            best = None
+            for n in range(1, 65):
+                kps = -(-(-(-longest // n)) // self.TILE) * self.TILE
+                if n > 1 and kps < 256:
+                    break
+                real = -(-longest // kps)
+                waves = -(-pairs * real // slots)
+                cost = waves * (kps + 192)
+                if best is None or cost < best[0]:
+                    best = (cost, kps, real)
+            kps = best[1]
+            self._splits[key] = (kps, max((s - 1) // kps + 1 for s in ([longest] if bound is not None else spans)))
         return self._splits[key]
 
 
@@ -261,7 +277,7 @@ class Kernels:
                            _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.tiles), plan.n_tiles, _ptr(out),
                            out.shape[1], heads, kv_heads, head_dim, page_size, int(window), float(scale), self._stream())
             if plan.n_items:
-                kps, splits = plan.split(kv_heads, int(window), self.sm_count)
+                kps, splits = plan.split(kv_heads, int(window), self.sm_count, head_dim, getattr(plan, 'context_bound', None))
                 part_o = part_ml = None
                 if splits > 1:
                     part_o = self._scratch("attn.part_o", plan.n_items * heads * splits * head_dim, qkv.device)
