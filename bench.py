@@ -257,12 +257,15 @@ def main() -> int:
             first.setdefault(seq.seq_id, now)
             stamps.append(now)
 
+        budget = engine.policy.max_batched_tokens
+        engine.policy.max_batched_tokens = B * C          # all prompts in one prefill step, then decode steps only
         seqs = [engine.new_sequence(p, K + 1, 0.0, True, None, on_out) for p in prompts]
         engine.run_until_done()
         torch.cuda.synchronize()
+        engine.policy.max_batched_tokens = budget
         t_first, t_last = max(first.values()), max(stamps)
         decoded = sum(len(s.tokens) - s.prompt_len - 1 for s in seqs)
-        h2d = (4 * B + (B + 1) + 4 * B + B * (-(-(C + K) // page))) * 4     # ids, positions, maps, lengths, block table
+        h2d = (4 * B + (B + 1) + 4 * B + B * max(16, 1 << ((-(-(C + K) // page)) - 1).bit_length())) * 4
         e2e = {"value": decoded / (t_last - t_first), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": 4 * B}
 

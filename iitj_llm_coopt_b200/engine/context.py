@@ -25,6 +25,7 @@ class GroupMeta:
     seq_lens_host: list = field(default_factory=list)
     cu_seqlens: torch.Tensor | None = None
     seq_lens: torch.Tensor | None = None
+    attention_plan: object = None  # kernels.AttentionPlan: decode items and prefill tiles of this step
 
 
 class Workspace:
@@ -34,6 +35,7 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._flat: dict = {}
+        self.generation = 0      # bumped whenever a buffer is (re)allocated: captured graphs then hold stale addresses
 
     def get(self, name: str, shape, dtype) -> torch.Tensor:
         n = 1
@@ -44,6 +46,7 @@ class Workspace:
         if flat is None or flat.numel() < n:
             flat = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._flat[key] = flat
+            self.generation += 1
         return flat[:n].view(*shape)
 
 

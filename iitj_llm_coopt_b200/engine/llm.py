@@ -89,7 +89,7 @@ def build_engine(model: str | None = None, engine_config: EngineConfig | None = 
         if num_pages <= 0:
             raise RuntimeError("no memory left for the key/value cache")
         cache = CacheManager(needs, ec.page_size, num_pages, max_requests=ec.max_num_seqs, dtype=dtype, device=device)
-        runner = ModelRunner(net, cache, device)
+        runner = ModelRunner(net, cache, device, cuda_graphs=ec.cuda_graphs)
         sampler = Sampler(kernels, ec.seed, device)
     pol = policy or StaticPolicy(max_num_seqs=ec.max_num_seqs, max_batched_tokens=ec.max_num_batched_tokens,
                                  watermark=ec.watermark)
@@ -111,11 +111,12 @@ class LLM:
     def __init__(self, model: str | None = None, dtype: str = "bfloat16", *, config=None, random_seed=None,
                  page_size: int = 16, num_pages: int | None = None, kv_gb: float | None = None,
                  gpu_memory_utilization: float = 0.9, max_model_len: int = 32768, max_num_seqs: int = 256,
-                 max_num_batched_tokens: int = 2048, seed: int = 0, device: str = "cuda:0", kernels=None):
+                 max_num_batched_tokens: int = 2048, seed: int = 0, device: str = "cuda:0", kernels=None,
+                 cuda_graphs: bool = True):
         ec = EngineConfig(dtype=dtype, page_size=page_size, num_pages=num_pages, kv_gb=kv_gb,
                           gpu_memory_utilization=gpu_memory_utilization, max_model_len=max_model_len,
                           max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens, seed=seed,
-                          device=device)
+                          device=device, cuda_graphs=cuda_graphs)
         self.engine = build_engine(model, ec, config=config, random_seed=random_seed, kernels=kernels)
 
     def generate(self, prompt_token_ids, sampling_params=None) -> list:

@@ -20,6 +20,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
+from ..kernels import AttentionPlan
 from .context import GroupMeta, StepContext, Workspace
 
 
@@ -31,8 +32,13 @@ class StepEntry:
 
 
 class ModelRunner:
-    def __init__(self, model, cache, device="cuda"):
+    def __init__(self, model, cache, device="cuda", cuda_graphs: bool = False):
         self.model, self.cache, self.device = model, cache, device
+        self.use_graphs = bool(cuda_graphs) and str(device).startswith("cuda") and \
+            bool(getattr(model, "graph_safe", False))
+        self._graphs: dict = {}      # key -> captured decode step
+        self._graph_seen: dict = {}  # key -> eager runs so far
+        self.graph_replays = 0
         self.vocab = model.spec.vocab
         self.workspace = Workspace(device)
         self._pinned = None          # int32 staging buffer (host, pinned)
@@ -79,6 +85,43 @@ class ModelRunner:
             self._meta = torch.empty(cap, dtype=torch.int32, device=self.device)
         return self._pinned.numpy()
 
+    # ---- captured decode steps --------------------------------------------------------
+    def _generation(self):
+        k = getattr(self.model, "k", None)
+        return (self.workspace.generation, getattr(k, "scratch_generation", 0), self._meta.data_ptr())
+
+    def _forward_graphed(self, key, ctx):
+        """Runs a decode-shaped step: eagerly the first time its shape is seen (which also
+        brings every scratch buffer to size), captured into a CUDA graph the second time,
+        replayed from then on.  The index arrays were copied to their fixed places before."""
+        rec = self._graphs.get(key)
+        if rec is not None and rec["generation"] == self._generation():
+            rec["graph"].replay()
+            self.graph_replays += 1
+            k = getattr(self.model, "k", None)
+            if k is not None:
+                k.launches += rec["launches"]
+            return rec["logits"]
+        if self._graph_seen.get(key, 0) < 1:
+            self._graph_seen[key] = self._graph_seen.get(key, 0) + 1
+            return self.model.forward(ctx)
+        if len(self._graphs) >= 64:
+            self._graphs.pop(next(iter(self._graphs)))
+        k = getattr(self.model, "k", None)
+        before = k.launches if k is not None else 0
+        generation = self._generation()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx)
+        launches = (k.launches - before) if k is not None else 0
+        if generation != self._generation():     # a buffer grew while capturing: do not keep the graph
+            self._graph_seen[key] = 0
+            return self.model.forward(ctx)
+        self._graphs[key] = {"graph": graph, "logits": logits, "generation": generation, "launches": launches}
+        graph.replay()
+        self.graph_replays += 1
+        return logits
+
     # ---- the step --------------------------------------------------------------------
     def step(self, entries: list):
         if not entries:
@@ -107,6 +150,17 @@ class ModelRunner:
         groups = cache.paged
         rows = {g: [self._table_row(g, e.request) for e in entries] for g in groups}
         widths = {g: max(1, max(r.shape[0] for r in rows[g])) for g in groups}
+        # A step of single tokens that all want logits has the same shape every time: it can be
+        # replayed from a captured graph if the index arrays keep their places, so the block
+        # tables are padded to a power of two of pages.
+        graphable = self.use_graphs and T == B and N == B and all(e.want == [0] for e in entries)
+        if graphable:
+            widths = {g: max(16, 1 << (w - 1).bit_length()) for g, w in widths.items()}
+        plan = AttentionPlan(qlens, seqlens, self.device, items=False, tiles=False)
+        if graphable:
+            # the split choice of decode attention is frozen into a graph: fix it by an upper bound of
+            # the contexts, in steps of 512 tokens, and capture anew when the batch outgrows the bound
+            plan.context_bound = -(-max(seqlens) // 512) * 512
 
         # layout of the one int32 buffer
         layout, off = {}, 0
@@ -121,7 +175,12 @@ class ModelRunner:
         for g in groups:
             place(f"slots{g}", T)
             place(f"table{g}", B * widths[g])
+        place("attn_items", plan.n_items)
+        place("attn_tiles", 4 * plan.n_tiles)
+        old_meta = self._meta
         host = self._stage(off)
+        if self._meta is not old_meta:
+            self._graphs.clear()           # the index arrays moved: captured graphs point at the old buffer
 
         def put(name, values):
             o, n = layout[name]
@@ -140,6 +199,10 @@ class ModelRunner:
         put("logit_rows", [int(cu[b]) + w for b, e in enumerate(entries) for w in e.want])
         put("state_slots", slots_b)
         put("first_portion", [1 if s == 0 else 0 for s in starts])
+        if plan.n_items:
+            put("attn_items", plan.item_rows)
+        if plan.n_tiles:
+            put("attn_tiles", np.asarray(plan.tile_rows, dtype=np.int64).reshape(-1))
         ps = cache.page_size
         slots_host = {}
         for g in groups:
@@ -163,6 +226,8 @@ class ModelRunner:
             o, n = layout[name]
             return self._meta[o:o + n]
 
+        plan.items = dev("attn_items") if plan.n_items else None
+        plan.tiles = dev("attn_tiles").view(-1, 4) if plan.n_tiles else None
         token_request, positions = dev("token_request"), dev("positions")
         cu_dev, seq_dev = dev("cu_seqlens"), dev("seq_lens")
         metas = {}
@@ -170,14 +235,18 @@ class ModelRunner:
             o, _ = layout[f"table{g}"]
             metas[g] = GroupMeta(block_table=self._meta[o:o + B * widths[g]].view(B, widths[g]),
                                  slots=dev(f"slots{g}"), token_request=token_request, positions=positions,
-                                 query_lens=qlens, seq_lens_host=seqlens, cu_seqlens=cu_dev, seq_lens=seq_dev)
+                                 query_lens=qlens, seq_lens_host=seqlens, cu_seqlens=cu_dev, seq_lens=seq_dev,
+                                 attention_plan=plan)
         ctx = StepContext(num_tokens=T, num_requests=B, num_logits=N, token_ids=dev("token_ids"),
                           positions=positions, token_request=token_request, cu_seqlens=cu_dev, seq_lens=seq_dev,
                           logit_rows=dev("logit_rows"), state_slots=dev("state_slots"),
                           first_portion=dev("first_portion"), groups=metas, cache=cache,
                           workspace=self.workspace, requests=[e.request for e in entries],
                           query_lens=qlens, starts=starts, slots_host=slots_b)
-        logits = self.model.forward(ctx)
+        if graphable:
+            logits = self._forward_graphed((B, tuple(sorted(widths.items())), plan.context_bound), ctx)
+        else:
+            logits = self.model.forward(ctx)
         for e, end in zip(entries, seqlens):
             cache.advance(e.request, end)
         self.steps += 1

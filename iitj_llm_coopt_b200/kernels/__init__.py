@@ -93,6 +93,7 @@ class AttentionPlan:
             row += n
         self.n_items, self.n_tiles = len(item_rows), len(tile_rows)
         self.items, self.tiles = items, tiles
+        self.context_bound = None     # an upper bound of the contexts that fixes the split choice (captured graphs)
         if self.items is None and item_rows:
             self.items = torch.tensor(item_rows, dtype=torch.int32).to(device)
         if self.tiles is None and tile_rows:
@@ -153,6 +154,7 @@ class Kernels:
             fn.restype = _c_int
         self.launches = 0  # kernels of this library launched so far (the bench reports it)
         self._scratch_bufs: dict = {}
+        self.scratch_generation = 0
         self._sm_count = None
 
     @property
@@ -167,6 +169,7 @@ class Kernels:
         if buf is None or buf.numel() < floats:
             buf = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=device)
             self._scratch_bufs[(name, device)] = buf
+            self.scratch_generation += 1
         return buf
 
     # ---- plumbing --------------------------------------------------------------------

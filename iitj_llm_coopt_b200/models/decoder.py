@@ -83,6 +83,14 @@ class DecoderModel:
         self.final_norm = _lookup(P.NORMS, spec.final_norm, "norm")(spec.final_norm, kernels, dtype)
         self.head = P.OutputHead(spec.vocab, spec.width, kernels, spec.logit_scale)
 
+    @property
+    def graph_safe(self) -> bool:
+        """True if every part only launches shape-determined work, so decode steps can be captured."""
+        mixers_ok = all(getattr(b.mixer.position, "graph_safe", True) for b in self.layers
+                        if getattr(b.mixer, "position", None) is not None)
+        return mixers_ok and all(getattr(b, "graph_safe", False) for b in self.layers) and \
+            self.embedding.graph_safe and self.final_norm.graph_safe and self.head.graph_safe
+
     # ---- parameters ----------------------------------------------------------------------
     def load_parameters(self, params: dict) -> None:
         """`params`: {path: tensor} for every path of model_parameter_specs(spec)."""

@@ -37,7 +37,15 @@ class ParamSpec:
 
 
 class Part:
-    """Base of all parts: parameter declaration and loading."""
+    """Base of all parts: parameter declaration and loading.
+
+    `graph_safe`: True if `forward` only launches work whose addresses and launch shapes
+    depend on the step's shape alone (everything that varies is read from the step's device
+    arrays).  Decode steps of a model whose parts are all graph-safe are replayed from
+    captured CUDA graphs; a part that decides anything on the host per step (loops over
+    requests, reads `ctx.starts`) must leave it False."""
+
+    graph_safe = False
 
     @classmethod
     def parameters(cls, spec) -> dict:

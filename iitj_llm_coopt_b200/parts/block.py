@@ -15,6 +15,10 @@ class PreNormBlock:
         self.mixer_norm, self.mixer = mixer_norm, mixer
         self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in self.parts().values())
+
     def parts(self) -> dict:
         return {"mixer_norm": self.mixer_norm, "mixer": self.mixer,
                 "feed_forward_norm": self.feed_forward_norm, "feed_forward": self.feed_forward}

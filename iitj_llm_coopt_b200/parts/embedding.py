@@ -12,6 +12,8 @@ from .base import ParamSpec, Part
 
 
 class Embedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab, width, kernels, scale=1.0):
         self.vocab, self.width, self.k, self.scale = vocab, width, kernels, scale
         self.weight = None
@@ -26,6 +28,8 @@ class Embedding(Part):
 
 
 class OutputHead(Part):
+    graph_safe = True
+
     def __init__(self, vocab, width, kernels, scale=1.0):
         self.vocab, self.width, self.k, self.scale = vocab, width, kernels, scale
         self.weight = None

@@ -9,6 +9,8 @@ from .base import ParamSpec, Part
 
 
 class SwiGLU(Part):
+    graph_safe = True
+
     def __init__(self, spec, kernels, dtype):
         if spec.activation != "silu":
             raise ValueError(f"SwiGLU: activation {spec.activation!r} is not supported")

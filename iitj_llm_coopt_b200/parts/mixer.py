@@ -17,6 +17,8 @@ from .base import ParamSpec, Part
 
 
 class PagedAttention(Part):
+    graph_safe = True
+
     def __init__(self, spec, kernels, dtype, position):
         self.spec, self.k, self.dtype = spec, kernels, dtype
         self.width, self.heads, self.kv_heads, self.head_dim = spec.width, spec.heads, spec.kv_heads, spec.head_dim

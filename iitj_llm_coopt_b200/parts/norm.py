@@ -10,6 +10,8 @@ from .base import ParamSpec, Part
 
 
 class RMSNorm(Part):
+    graph_safe = True
+
     def __init__(self, spec, kernels, dtype):
         self.spec, self.k, self.dtype = spec, kernels, dtype
         self.width, self.eps = spec.width, spec.eps

@@ -35,6 +35,8 @@ def rope_inverse_frequencies(rotary_dim: int, theta: float, scaling: dict | None
 
 
 class RotaryEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, spec, kernels, dtype, device="cuda"):
         self.spec, self.k = spec, kernels
         self.head_dim, self.rotary_dim = spec.head_dim, spec.rotary_dim
@@ -46,6 +48,8 @@ class RotaryEmbedding(Part):
 
 
 class NoPosition(Part):
+    graph_safe = True
+
     def __init__(self, spec, kernels, dtype, device="cuda"):
         self.spec, self.k, self.head_dim = spec, kernels, spec.head_dim
 
