@@ -1,0 +1,407 @@
+// bfloat16 matrix products on the fifth-generation tensor cores: y = x . W^T with x [T, K]
+// and W [N, K] row-major (F.linear of engine/model.py:194, 208, 210-211, 218), float32
+// accumulation in tensor memory.
+//
+// The weight rows are the 128-row side of the MMA tile ("swap-AB"): one CTA owns 128 output
+// features and a tile of 16..256 tokens, so a decode step with a handful of tokens still
+// streams full weight tiles.  Operands arrive by TMA (cp.async.bulk.tensor, 128-byte
+// swizzle, no multicast) into a ring of shared-memory stages; one thread issues
+// tcgen05.mma (kind::f16, M = 128, N = token tile, K = 16 per instruction) with shared-
+// memory descriptors; completion of a stage's MMAs frees the stage through tcgen05.commit;
+// four epilogue warps read the accumulator with tcgen05.ld and store the transposed tile.
+//
+// Variants:
+//   SWIGLU    W holds gate rows then up rows; the CTA keeps two accumulators (gate, up) for
+//             the same 128 features and writes silu(gate) * up (engine/model.py:210-211,
+//             251-252), so the [T, 2I] intermediate is never written.
+//   split-K   when a product has too few tiles to fill the GPU, the k range is split over
+//             CTAs; partial sums go to float32 scratch and llm_gemm_bf16_reduce adds them in
+//             split order (and applies SwiGLU, or rounds to bfloat16).
+//
+// Every wait on an mbarrier is bounded; a wait that runs out records a code in a status
+// word (llm_gemm_bf16_status), and the CTA falls through to its teardown (TMEM is freed).
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int kFeatTile = 128;                 // UMMA M
+constexpr int kBlockK = 64;                    // elements per k-block: 128 bytes = one swizzle row
+constexpr int kThreads = 192;                  // warp 0: TMA, warp 1: MMA + TMEM alloc, warps 2-5: epilogue
+constexpr int kMaxStages = 12;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ int g_status = 0;                   // 0 ok; else (code << 16) | block id of the first CTA that gave up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity to complete; false if it did not.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void give_up(int code) { atomicCAS(&g_status, 0, (code << 16) | (int)(blockIdx.x & 0xffff)); }
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile of rows of 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);          // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                                    // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                          // stride byte offset
+    d |= (uint64_t)1 << 46;                                    // version
+    d |= (uint64_t)2 << 61;                                    // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor of tcgen05.mma kind::f16: bf16 x bf16 -> f32, both operands K-major.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4)            // D format f32
+         | (1u << 7)            // A format bf16
+         | (1u << 10)           // B format bf16
+         | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+
+enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_PARTIAL = 2 };
+
+struct GemmArgs {
+    void* out;            // [tokens, ldc] bf16 or f32, or partials [splits, tokens, ldc] f32
+    int out_mode;
+    int n_feat;           // output features handled by the grid's feature tiles (I for SwiGLU, else N)
+    int up_row_offset;    // SwiGLU: row of W where the up rows start (= I); partial column offset likewise
+    int tokens;
+    int ldc;
+    int k_blocks;         // ceil(K / 64)
+    int splits;
+    int stages;
+};
+
+template <int N_TOK, bool SWIGLU>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs a) {
+    constexpr int kABytes = kFeatTile * kBlockK * 2;               // 16 KiB per weight tile
+    constexpr int kBBytes = N_TOK * kBlockK * 2;
+    constexpr int kStageBytes = (SWIGLU ? 2 : 1) * kABytes + kBBytes;
+    constexpr int kTmemCols = (SWIGLU ? 2 : 1) * N_TOK < 32 ? 32 : (SWIGLU ? 2 : 1) * N_TOK;
+    static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns must be a power of two up to 512");
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], accum_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int feat0 = blockIdx.x * kFeatTile, split = blockIdx.y, tok0 = blockIdx.z * N_TOK;
+    const int kb0 = (int)((long long)split * a.k_blocks / a.splits), kb1 = (int)((long long)(split + 1) * a.k_blocks / a.splits);
+    const int n_kb = kb1 - kb0;
+    const int stages = a.stages;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&accum_bar, 1);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: TMA loads into the ring --------------------------------------------
+        for (int i = 0; i < n_kb; ++i) {
+            const int s = i % stages;
+            if (i >= stages && !mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1)) { give_up(1); failed = 1; break; }
+            unsigned char* st = tiles + (size_t)s * kStageBytes;
+            mbar_expect_tx(&full_bar[s], kStageBytes);
+            const int k = (kb0 + i) * kBlockK;
+            tma_load_2d(st, &map_w, &full_bar[s], k, feat0);
+            if (SWIGLU) tma_load_2d(st + kABytes, &map_w, &full_bar[s], k, a.up_row_offset + feat0);
+            tma_load_2d(st + (SWIGLU ? 2 : 1) * kABytes, &map_x, &full_bar[s], k, tok0);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ---------------------------------------------------------------------
+        constexpr uint32_t idesc = umma_idesc(kFeatTile, N_TOK);
+        bool ok = true;
+        for (int i = 0; i < n_kb && ok; ++i) {
+            const int s = i % stages;
+            if (!mbar_wait(&full_bar[s], (i / stages) & 1)) { give_up(2); failed = 1; ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            unsigned char* st = tiles + (size_t)s * kStageBytes;
+            const uint64_t da = umma_desc(st), db = umma_desc(st + (SWIGLU ? 2 : 1) * kABytes);
+            const uint64_t da2 = SWIGLU ? umma_desc(st + kABytes) : 0;
+#pragma unroll
+            for (int k = 0; k < kBlockK / 16; ++k) {
+                const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);          // +32 bytes per K step of 16
+                if (SWIGLU) umma_f16(tmem_base + N_TOK, da2 + 2 * k, db + 2 * k, idesc, acc);
+            }
+            umma_commit(&empty_bar[s]);           // the stage is free once these MMAs have read it
+        }
+        umma_commit(&accum_bar);                  // the accumulator is complete (also on the give-up path)
+    } else if (warp >= 2) {
+        // ---- epilogue: TMEM -> registers -> global, transposed ------------------------------
+        const int quarter = warp & 3;             // a warp may only read TMEM lanes [32 * (warp % 4), +32)
+        const int feat = feat0 + quarter * 32 + lane;
+        if (n_kb > 0 && mbar_wait(&accum_bar, 0) && !failed) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < N_TOK; c0 += 16) {
+                uint32_t g[16], u[16];
+                tmem_ld16(lane_addr + c0, g);
+                if (SWIGLU) tmem_ld16(lane_addr + N_TOK + c0, u);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (feat < a.n_feat) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int tok = tok0 + c0 + c;
+                        if (tok >= a.tokens) break;
+                        const float gv = __uint_as_float(g[c]);
+                        if (a.out_mode == OUT_PARTIAL) {
+                            float* dst = (float*)a.out + ((size_t)split * a.tokens + tok) * a.ldc;
+                            dst[feat] = gv;
+                            if (SWIGLU) dst[a.up_row_offset + feat] = __uint_as_float(u[c]);
+                        } else {
+                            float v = gv;
+                            if (SWIGLU) v = gv / (1.0f + expf(-gv)) * __uint_as_float(u[c]);
+                            if (a.out_mode == OUT_F32) ((float*)a.out)[(size_t)tok * a.ldc + feat] = v;
+                            else ((bf16*)a.out)[(size_t)tok * a.ldc + feat] = __float2bfloat16_rn(v);
+                        }
+                    }
+                }
+            }
+        } else if (n_kb > 0 && !failed) {
+            give_up(3);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
+    }
+}
+
+// out[t, f] = sum over splits of part[s, t, f]  (SwiGLU: silu(sum gate) * sum up), four features per thread.
+template <bool SWIGLU, typename TO>
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, TO* __restrict__ out, int splits, int tokens,
+                                     int n_feat, int ld_part, int up_offset, int ldc) {
+    const int f4 = n_feat / 4;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < (size_t)tokens * f4;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / f4), f = (int)(idx % f4) * 4;
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+        for (int s = 0; s < splits; ++s) {
+            const float* row = part + ((size_t)s * tokens + t) * ld_part;
+            const float4 a = *reinterpret_cast<const float4*>(row + f);
+            g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+            if (SWIGLU) {
+                const float4 b = *reinterpret_cast<const float4*>(row + up_offset + f);
+                u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+            }
+        }
+        if (SWIGLU) {
+            g.x = g.x / (1.0f + expf(-g.x)) * u.x; g.y = g.y / (1.0f + expf(-g.y)) * u.y;
+            g.z = g.z / (1.0f + expf(-g.z)) * u.z; g.w = g.w / (1.0f + expf(-g.w)) * u.w;
+        }
+        TO* dst = out + (size_t)t * ldc + f;
+        dst[0] = from_f32<TO>(g.x); dst[1] = from_f32<TO>(g.y); dst[2] = from_f32<TO>(g.z); dst[3] = from_f32<TO>(g.w);
+    }
+}
+
+// ---- host: tensor maps ------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; int rows, cols, box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^ ((size_t)k.box_rows << 20);
+    }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+std::mutex g_maps_mutex;
+
+// Map of a row-major [rows, cols] bf16 matrix, box = 64 columns x box_rows rows, 128-byte swizzle, zero fill.
+int tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_maps_mutex);
+    const MapKey key{ptr, rows, cols, box_rows};
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) LLM_FAIL(-2, "gemm_bf16: cuTensorMapEncodeTiled is not available from this driver");
+    if (((uintptr_t)ptr & 15) || (cols % 8)) LLM_FAIL(-1, "gemm_bf16: matrices must be 16-byte aligned with K %% 8 == 0 (K = %d)", cols);
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) LLM_FAIL(-2, "gemm_bf16: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, m);
+    *out = m;
+    return 0;
+}
+
+template <int N_TOK, bool SWIGLU>
+int launch_tile(const CUtensorMap& mw, const CUtensorMap& mx, GemmArgs a, dim3 grid, cudaStream_t stream) {
+    constexpr int stage_bytes = (SWIGLU ? 2 : 1) * kFeatTile * kBlockK * 2 + N_TOK * kBlockK * 2;
+    int stages = (200 * 1024) / stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    a.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + 1024;
+    auto kern = gemm_tn_kernel<N_TOK, SWIGLU>;
+    static bool configured = false;            // one flag per instantiation
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LLM_FAIL(-2, "gemm_bf16: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    kern<<<grid, kThreads, smem, stream>>>(mw, mx, a);
+    LLM_CHECK_LAUNCH("gemm_bf16");
+    return 0;
+}
+
+}  // namespace
+
+// Token tile the kernel uses for `tokens` rows of x.
+LLM_API int llm_gemm_bf16_token_tile(int tokens) {
+    return tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : tokens <= 128 ? 128 : 256;
+}
+
+// out = x . w^T.   x [tokens, K] bf16, w [n (or 2n with swiglu), K] bf16.
+// out_f32 == 0: out is bf16 [tokens, ldc]; out_f32 != 0: float32 [tokens, ldc].
+// splits > 1 needs `scratch` with splits * tokens * (swiglu ? 2n : n) floats; the reduction runs right after.
+LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, int tokens, int n, int K, int ldc,
+                          int swiglu, int splits, float* scratch, cudaStream_t stream) {
+    if (tokens == 0 || n == 0) return 0;
+    if (K % 8) LLM_FAIL(-1, "gemm_bf16: K %d must be a multiple of 8", K);
+    if (swiglu && out_f32) LLM_FAIL(-1, "gemm_bf16: the SwiGLU variant writes bfloat16");
+    const int k_blocks = (K + kBlockK - 1) / kBlockK;
+    if (splits < 1) splits = 1;
+    if (splits > k_blocks) splits = k_blocks;
+    if (splits > 1 && !scratch) LLM_FAIL(-1, "gemm_bf16: split-K needs scratch");
+    if (splits > 1 && (n % 4)) LLM_FAIL(-1, "gemm_bf16: split-K needs n %% 4 == 0");
+    const int w_rows = swiglu ? 2 * n : n;
+    const int tile = llm_gemm_bf16_token_tile(tokens);
+    CUtensorMap mw, mx;
+    if (int rc = tensor_map(w, w_rows, K, kFeatTile, &mw)) return rc;
+    if (int rc = tensor_map(x, tokens, K, tile, &mx)) return rc;
+    GemmArgs a;
+    a.out = splits > 1 ? (void*)scratch : out;
+    a.out_mode = splits > 1 ? OUT_PARTIAL : (out_f32 ? OUT_F32 : OUT_BF16);
+    a.n_feat = n;
+    a.up_row_offset = swiglu ? n : 0;
+    a.tokens = tokens;
+    a.ldc = splits > 1 ? w_rows : ldc;
+    a.k_blocks = k_blocks;
+    a.splits = splits;
+    a.stages = 0;
+    dim3 grid((n + kFeatTile - 1) / kFeatTile, splits, (tokens + tile - 1) / tile);
+    if (grid.y > 65535 || grid.z > 65535) LLM_FAIL(-1, "gemm_bf16: grid out of range");
+    int rc;
+#define LLM_GEMM_CASE(T)                                                                       \
+    case T: rc = swiglu ? launch_tile<T, true>(mw, mx, a, grid, stream) : launch_tile<T, false>(mw, mx, a, grid, stream); break;
+    switch (tile) {
+        LLM_GEMM_CASE(16)
+        LLM_GEMM_CASE(32)
+        LLM_GEMM_CASE(64)
+        LLM_GEMM_CASE(128)
+        LLM_GEMM_CASE(256)
+        default: LLM_FAIL(-1, "gemm_bf16: no kernel for a token tile of %d", tile);
+    }
+#undef LLM_GEMM_CASE
+    if (rc) return rc;
+    if (splits > 1) {
+        const size_t work = (size_t)tokens * (n / 4);
+        const int blocks = (int)((work + 255) / 256 < 148 * 8 ? (work + 255) / 256 : 148 * 8);
+        if (swiglu)
+            splitk_reduce_kernel<true, bf16><<<blocks, 256, 0, stream>>>(scratch, (bf16*)out, splits, tokens, n, w_rows, n, ldc);
+        else if (out_f32)
+            splitk_reduce_kernel<false, float><<<blocks, 256, 0, stream>>>(scratch, (float*)out, splits, tokens, n, w_rows, 0, ldc);
+        else
+            splitk_reduce_kernel<false, bf16><<<blocks, 256, 0, stream>>>(scratch, (bf16*)out, splits, tokens, n, w_rows, 0, ldc);
+        LLM_CHECK_LAUNCH("gemm_bf16_reduce");
+    }
+    return 0;
+}
+
+// Reads and clears the status word: 0, or (code << 16 | block) of the first CTA whose wait ran out
+// (code 1: producer waiting for a free stage, 2: MMA issuer waiting for data, 3: epilogue waiting for the accumulator).
+LLM_API int llm_gemm_bf16_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    return v;
+}

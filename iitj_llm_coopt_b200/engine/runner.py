@@ -15,6 +15,7 @@ decode step does not rebuild them from Python lists.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -111,8 +112,17 @@ class ModelRunner:
         before = k.launches if k is not None else 0
         generation = self._generation()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            logits = self.model.forward(ctx)
+        # The garbage collector must not run inside the capture: collecting an older engine there would
+        # destroy its graphs, which CUDA forbids while a capture is open and which voids the capture.
+        gc_was_on = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                logits = self.model.forward(ctx)
+        finally:
+            if gc_was_on:
+                gc.enable()
         launches = (k.launches - before) if k is not None else 0
         if generation != self._generation():     # a buffer grew while capturing: do not keep the graph
             self._graph_seen[key] = 0

@@ -48,6 +48,10 @@ _SIGNATURES = {
                                   _c_float, _c_int, _c_int, _c_void_p],
     "llm_gemm_f32": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                      _c_void_p],
+    "llm_gemm_bf16_token_tile": [_c_int],
+    "llm_gemm_bf16": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                      _c_void_p],
+    "llm_gemm_bf16_status": [],
     "llm_sample": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
 }
 
@@ -315,7 +319,10 @@ class Kernels:
             self._call("llm_gemm_f32", _ptr(x), _ptr(weight), _ptr(out), x.shape[0], n, x.shape[1], x.shape[1],
                        weight.shape[1], n, 1 if swiglu else 0, self._stream())
             return out
-        # bfloat16: cuBLAS through torch, float32 accumulation
+        # bfloat16: this library's tcgen05 kernel where it is the faster one, else cuBLAS through torch
+        tokens, k = x.shape
+        if self.gemm_policy(tokens, n, k, swiglu) == "tcgen05":
+            return self.gemm_tcgen05(x, weight, out, swiglu, self.gemm_splits(tokens, n, k, swiglu))
         if swiglu:
             gu = torch.mm(x, weight.t())
             return self.silu_mul(gu, out)
@@ -324,6 +331,59 @@ class Kernels:
         else:
             torch.mm(x, weight.t(), out=out)
         return out
+
+    def gemm_tcgen05(self, x, weight, out, swiglu: bool = False, splits: int = 1):
+        """out = x . weight^T on this library's tcgen05 kernel (bfloat16 in, bfloat16 or float32 out)."""
+        _check(x, "gemm.x", torch.bfloat16, 2)
+        _check(weight, "gemm.weight", torch.bfloat16, 2)
+        _check(out, "gemm.out", (torch.bfloat16, torch.float32), 2)
+        tokens, k = x.shape
+        n = weight.shape[0] // 2 if swiglu else weight.shape[0]
+        _need(weight.shape[1] == k and out.shape == (tokens, n), "gemm: shapes do not fit")
+        splits = max(1, min(int(splits), -(-k // 64)))
+        scratch = None
+        if splits > 1:
+            scratch = self._scratch("gemm.partials", splits * tokens * weight.shape[0], x.device)
+        self._call("llm_gemm_bf16", _ptr(x), _ptr(weight), _ptr(out), 1 if out.dtype == torch.float32 else 0, tokens,
+                   n, k, out.shape[1], 1 if swiglu else 0, splits, _ptr(scratch), self._stream())
+        if splits > 1:
+            self.launches += 1
+        return out
+
+    # Which kernel multiplies: "tcgen05" (this library) or "cublas".  `gemm_backend` may force one.
+    gemm_backend = "auto"
+    gemm_small_tokens = 128
+
+    def gemm_policy(self, tokens, n, k, swiglu) -> str:
+        """Measured on B200 at the 8B shapes: the fused SwiGLU product of this library matches
+        cuBLAS + a separate SiLU kernel up to 128 tokens and saves a launch; the plain products
+        are left to cuBLAS."""
+        if k % 8:
+            return "cublas"
+        if self.gemm_backend != "auto":
+            return self.gemm_backend
+        return "tcgen05" if (swiglu and tokens <= self.gemm_small_tokens) else "cublas"
+
+    def gemm_splits(self, tokens, n, k, swiglu) -> int:
+        """Split the k range when the product has too few CTAs to fill the GPU: candidates are
+        scored by waves * (k-blocks per CTA + a fixed per-CTA cost), one CTA per SM."""
+        tile = self.lib.llm_gemm_bf16_token_tile(tokens)
+        ctas = -(-n // 128) * -(-tokens // tile)
+        k_blocks = -(-k // 64)
+        if tokens > 256 or ctas >= self.sm_count or n % 4:
+            return 1
+        best = (None, 1)
+        for s in range(1, min(16, max(1, k_blocks // 4)) + 1):
+            per = -(-k_blocks // s)
+            waves = -(-ctas * s // self.sm_count)
+            cost = waves * (per + 8)
+            if best[0] is None or cost < best[0]:
+                best = (cost, s)
+        return best[1]
+
+    def gemm_status(self) -> int:
+        """0, or a code if a tcgen05 GEMM gave up waiting on one of its barriers since the last call."""
+        return self.lib.llm_gemm_bf16_status()
 
     # ---- sampling --------------------------------------------------------------------
     def sample(self, logits, temperature, keys, out):

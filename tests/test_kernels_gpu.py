@@ -311,3 +311,45 @@ def test_attention_bf16_same_result_in_any_batch(K):
     out1 = torch.empty(1, heads * head_dim, device="cuda", dtype=torch.bfloat16)
     K.attention(q[41:42].contiguous(), cache, solo, out1, heads, kv_heads, head_dim)
     assert torch.equal(out1[0], out[41])
+
+
+# ---- the tcgen05 matrix product (bfloat16) ---------------------------------------------
+@pytest.mark.parametrize("tokens", [1, 7, 16, 17, 40, 100, 129, 300, 600])
+@pytest.mark.parametrize("n,k", [(128, 64), (200, 96), (320, 176), (1000, 264), (136, 4104)])
+def test_gemm_tcgen05_shapes(K, tokens, n, k):
+    x, w = rnd((tokens, k), torch.bfloat16, 100), rnd((n, k), torch.bfloat16, 101, 0.05)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.zeros(tokens, n, device="cuda", dtype=out_dtype)
+        K.gemm_tcgen05(x, w, out)
+        close(out, R.ref_linear(x, w), torch.bfloat16, 0.5 if out_dtype == torch.bfloat16 else 0.01)
+    assert K.gemm_status() == 0
+
+
+@pytest.mark.parametrize("tokens,n,k,splits", [(1, 128, 512, 2), (8, 320, 1024, 3), (33, 200, 4104, 9), (64, 136, 640, 16),
+                                               (5, 256, 64, 4), (200, 384, 256, 2)])
+def test_gemm_tcgen05_split_k(K, tokens, n, k, splits):
+    x, w = rnd((tokens, k), torch.bfloat16, 102), rnd((n, k), torch.bfloat16, 103, 0.05)
+    out = torch.zeros(tokens, n, device="cuda", dtype=torch.float32)
+    K.gemm_tcgen05(x, w, out, splits=splits)
+    close(out, R.ref_linear(x, w), torch.bfloat16, 0.01)
+    assert K.gemm_status() == 0
+
+
+@pytest.mark.parametrize("tokens,n,k,splits", [(1, 176, 64, 1), (9, 344, 96, 1), (70, 100, 200, 1), (8, 256, 1024, 4),
+                                               (130, 384, 192, 1), (300, 1000, 264, 1), (16, 176, 4104, 7)])
+def test_gemm_tcgen05_swiglu(K, tokens, n, k, splits):
+    x, w = rnd((tokens, k), torch.bfloat16, 104), rnd((2 * n, k), torch.bfloat16, 105, 0.2)
+    out = torch.zeros(tokens, n, device="cuda", dtype=torch.bfloat16)
+    K.gemm_tcgen05(x, w, out, swiglu=True, splits=splits)
+    close(out, R.ref_linear(x, w, swiglu=True), torch.bfloat16, 0.5)
+    assert K.gemm_status() == 0
+
+
+def test_gemm_tcgen05_row_does_not_depend_on_batch(K):
+    """With the same split count a token's row is bitwise the same alone and among others."""
+    x, w = rnd((50, 264), torch.bfloat16, 106), rnd((200, 264), torch.bfloat16, 107, 0.05)
+    full = torch.zeros(50, 200, device="cuda", dtype=torch.float32)
+    one = torch.zeros(1, 200, device="cuda", dtype=torch.float32)
+    K.gemm_tcgen05(x, w, full, splits=2)
+    K.gemm_tcgen05(x[31:32].contiguous(), w, one, splits=2)
+    assert torch.equal(full[31:32], one)
