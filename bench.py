@@ -133,6 +133,8 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step by itself (for profiling)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -160,9 +162,10 @@ def main() -> int:
     B, C, K, W = args.batch, args.context, args.steps, args.warmup
     page = 16
     biggest = max(B, 1 if args.no_points else 64)
-    pool_tokens = biggest * (C + K + W + 2 * page) + args.prefill_tokens + 4 * page
+    pool_tokens = biggest * (C + max(K, 96) + W + 2 * page) + args.prefill_tokens + 4 * page
     ec = EngineConfig(dtype="bfloat16", page_size=page, num_pages=-(-pool_tokens // page), max_num_seqs=max(biggest, 8),
-                      max_num_batched_tokens=max(args.prefill_tokens, biggest), max_model_len=C + K + W + 64, seed=0)
+                      max_num_batched_tokens=max(args.prefill_tokens, biggest), max_model_len=C + max(K, 96) + W + 64, seed=0,
+                      cuda_graphs=not args.no_graphs)
     t_build = time.time()
     engine = build_engine(None, ec, config=typed, random_seed=2)
     runner, cache, sampler, kernels = engine.runner, engine.cache, engine.sampler, engine.sampler.k
@@ -231,7 +234,7 @@ def main() -> int:
     kv_bytes = B * (C + W + K / 2) * typed.kv_bytes_per_token(2)
     achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
 
-    p_times = prefill_run(args.prefill_tokens, 5, 3)
+    p_times = prefill_run(args.prefill_tokens, 5, 3) if not args.no_prefill else [float("nan")]
     p_ms = statistics.median(p_times)
     p_flops = prefill_flops(cfg, args.prefill_tokens)
     prefill = {"value": args.prefill_tokens / (p_ms / 1e3), "tokens": args.prefill_tokens, "ms": p_ms,
@@ -259,7 +262,8 @@ def main() -> int:
 
         budget = engine.policy.max_batched_tokens
         engine.policy.max_batched_tokens = B * C          # all prompts in one prefill step, then decode steps only
-        seqs = [engine.new_sequence(p, K + 1, 0.0, True, None, on_out) for p in prompts]
+        KE = max(K, 96)                                    # enough steps to amortise the one-off graph capture
+        seqs = [engine.new_sequence(p, KE + 1, 0.0, True, None, on_out) for p in prompts]
         engine.run_until_done()
         torch.cuda.synchronize()
         engine.policy.max_batched_tokens = budget

@@ -162,6 +162,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
                     const int* __restrict__ block_table, int table_width, const int4* __restrict__ tiles,
                     bf16* __restrict__ out, int out_stride, int heads, int kv_heads, int page_size, int page_shift,
                     int window, float sl) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* qtile = reinterpret_cast<bf16*>(smem_raw);              // [64][D]
     bf16* kv = qtile + kTile * D;                                 // [2 stages][K,V][64][D]
@@ -310,6 +312,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out, int out_stride,
                    int heads, int kv_heads, int page_size, int page_shift, int window, float sl, int keys_per_split,
                    int max_splits) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* kv = reinterpret_cast<bf16*>(smem_raw);                 // [kStages][K,V][64][D]
     const int split = blockIdx.x, hk = blockIdx.y, item = blockIdx.z;
@@ -434,6 +438,8 @@ __global__ void __launch_bounds__(D)
 attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ items,
                   const int* __restrict__ positions, bf16* __restrict__ out, int out_stride, int heads, int window,
                   int keys_per_split, int max_splits) {
+    pdl_trigger();
+    pdl_wait();
     const int item = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
     const int tok = items[item];
     const int pos = positions[tok];
@@ -489,7 +495,7 @@ LLM_API int llm_attention_prefill_bf16(const void* q, int q_stride, const void* 
     auto launch = [&](auto kern, int D) {
         const size_t smem = (size_t)(kTile * D + 2 * 2 * kTile * D) * sizeof(bf16);
         if (set_smem(kern, smem, "attention_prefill_bf16")) return -2;
-        kern<<<grid, kThreads, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, block_table, table_width,
+        llm_launch(kern, grid, kThreads, smem, stream, (const bf16*)q, q_stride, (const bf16*)cache, block_table, table_width,
                                                (const int4*)tiles, (bf16*)out, out_stride, heads, kv_heads, page_size,
                                                page_shift, window, sl);
         LLM_CHECK_LAUNCH("attention_prefill_bf16");
@@ -519,12 +525,12 @@ LLM_API int llm_attention_decode_bf16(const void* q, int q_stride, const void* c
         const size_t merge_smem = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
         if (merge_smem > smem) smem = merge_smem;
         if (set_smem(kern, smem, "attention_decode_bf16")) return -2;
-        kern<<<grid, kThreads, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, block_table, table_width, items,
+        llm_launch(kern, grid, kThreads, smem, stream, (const bf16*)q, q_stride, (const bf16*)cache, block_table, table_width, items,
                                                token_request, positions, part_o, part_ml, (bf16*)out, out_stride, heads,
                                                kv_heads, page_size, page_shift, window, sl, keys_per_split, max_splits);
         LLM_CHECK_LAUNCH("attention_decode_bf16");
         if (max_splits > 1) {
-            merge<<<dim3(n_items, heads), D, 0, stream>>>(part_o, part_ml, items, positions, (bf16*)out, out_stride, heads,
+            llm_launch(merge, dim3(n_items, heads), D, 0, stream, part_o, part_ml, items, positions, (bf16*)out, out_stride, heads,
                                                           window, keys_per_split, max_splits);
             LLM_CHECK_LAUNCH("attention_merge");
         }

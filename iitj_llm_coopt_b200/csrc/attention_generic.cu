@@ -60,6 +60,8 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
                     const int* __restrict__ token_request, const int* __restrict__ positions,
                     T* __restrict__ out, int out_stride, int tokens, int heads, int kv_heads,
                     int head_dim, int page_size, int window, float scale) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ __align__(16) float q_smem[kWarps][kMaxHeadDim];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * kWarps + warp;
@@ -138,7 +140,7 @@ LLM_API int llm_attention_generic(const void* q, int q_stride, const void* cache
     if (blocks > 0x7fffffffLL) LLM_FAIL(-1, "attention: too many (token, head) pairs: %lld", items);
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
-        attn_generic_kernel<T><<<(unsigned)blocks, kWarps * 32, 0, stream>>>(
+        llm_launch(attn_generic_kernel<T>, (unsigned)blocks, kWarps * 32, 0, stream, 
             (const T*)q, q_stride, (const T*)cache, block_table, table_width, token_request, positions,
             (T*)out, out_stride, tokens, heads, kv_heads, head_dim, page_size, window, scale);
         LLM_CHECK_LAUNCH("attention_generic");

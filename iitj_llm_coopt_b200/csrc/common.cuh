@@ -65,6 +65,37 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
     return warp_sum(t);
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// Every kernel of this library is launched with the "programmatic stream serialization"
+// attribute (unless llm_set_pdl(0)): its CTAs may be scheduled while the kernel before it in
+// the stream is still running, do work that depends on nothing that kernel writes (barrier
+// set-up, tensor-memory allocation, weight prefetch), and then block in pdl_wait() until the
+// earlier kernel has completed and its writes are visible.  pdl_trigger() at a kernel's top
+// tells the scheduler that the next kernel may start as soon as resources allow.  Both are
+// no-ops in a launch without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool llm_pdl_enabled();  // runtime.cu
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t llm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (llm_pdl_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename F> static inline int llm_dispatch_dtype(int dtype, F&& f) {
     if (dtype == LLM_F32) return f(float{});
     if (dtype == LLM_BF16) return f(__nv_bfloat16{});

@@ -12,6 +12,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                              float* __restrict__ out, int width, int vocab, float scale) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;  // the host refuses such ids; never read out of range
@@ -25,7 +27,7 @@ LLM_API int llm_embed(const int* ids, const void* table, int table_dtype, float*
     if (tokens == 0) return 0;
     return llm_dispatch_dtype(table_dtype, [&](auto tag) {
         using TW = decltype(tag);
-        embed_kernel<TW><<<tokens, 256, 0, stream>>>(ids, (const TW*)table, out, width, vocab, scale);
+        llm_launch(embed_kernel<TW>, tokens, 256, 0, stream, ids, (const TW*)table, out, width, vocab, scale);
         LLM_CHECK_LAUNCH("embed");
         return 0;
     });
@@ -42,6 +44,8 @@ template <typename TD, typename TW>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                    const int* __restrict__ rows, const TW* __restrict__ weight,
                                    TD* __restrict__ out, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float row_buf[];  // width floats
     __shared__ float red[32];
     const int r = blockIdx.x;
@@ -91,6 +95,8 @@ template <typename TD, typename TW, int PER_THREAD>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                        const int* __restrict__ rows, const TW* __restrict__ weight,
                                        TD* __restrict__ out, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float red[32];
     const int r = blockIdx.x;
     const size_t s = rows ? (size_t)rows[r] : (size_t)r;
@@ -148,7 +154,7 @@ LLM_API int llm_add_rmsnorm(float* residual, const void* delta, const int* rows,
                 if (threads > 512) threads = 512;
                 const int per = (vecs + threads - 1) / threads;
                 auto go = [&](auto kern) {
-                    kern<<<out_rows, threads, 0, stream>>>(residual, (const TD*)delta, rows, (const TW*)weight, (TD*)out, width, eps);
+                    llm_launch(kern, out_rows, threads, 0, stream, residual, (const TD*)delta, rows, (const TW*)weight, (TD*)out, width, eps);
                 };
                 if (per <= 1) go(add_rmsnorm_vec_kernel<TD, TW, 1>);
                 else if (per <= 2) go(add_rmsnorm_vec_kernel<TD, TW, 2>);
@@ -162,7 +168,7 @@ LLM_API int llm_add_rmsnorm(float* residual, const void* delta, const int* rows,
                 cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 if (e != cudaSuccess) LLM_FAIL(-2, "add_rmsnorm: %s", cudaGetErrorString(e));
             }
-            kern<<<out_rows, 256, smem, stream>>>(residual, (const TD*)delta, rows, (const TW*)weight,
+            llm_launch(kern, out_rows, 256, smem, stream, residual, (const TD*)delta, rows, (const TW*)weight,
                                                   (TD*)out, width, eps);
             LLM_CHECK_LAUNCH("add_rmsnorm");
             return 0;
@@ -184,9 +190,12 @@ LLM_API int llm_add_rmsnorm(float* residual, const void* delta, const int* rows,
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
-                                  const float* __restrict__ inv_freq, const int* __restrict__ slots,
+                                  const float* __restrict__ inv_freq, const float* __restrict__ cos_table,
+                                  const float* __restrict__ sin_table, const int* __restrict__ slots,
                                   T* __restrict__ cache, int heads, int kv_heads, int head_dim,
                                   int rotary_dim, int page_size) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float cs[128], sn[128];              // rotary_dim / 2 <= 128 (head_dim <= 256)
     const int t = blockIdx.x;
     const int half = rotary_dim / 2;
@@ -201,7 +210,14 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
         kbase = (size_t)page * 2 * plane + (size_t)off * head_dim;
     }
     const size_t head_stride = (size_t)page_size * head_dim;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &sn[i], &cs[i]);
+    if (cos_table) {   // the step's table: one row of rotary_dim / 2 cosines and sines per token
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            cs[i] = cos_table[(size_t)t * half + i];
+            sn[i] = sin_table[(size_t)t * half + i];
+        }
+    } else {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &sn[i], &cs[i]);
+    }
     __syncthreads();
 
     // rotated pairs of query and key heads, two neighbouring pairs per step (half is even: head sizes are multiples of 16)
@@ -238,8 +254,29 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
     }
 }
 
-LLM_API int llm_rope_store(void* qkv, const int* positions, const float* inv_freq, const int* slots,
-                           void* cache, int dtype, int tokens, int heads, int kv_heads, int head_dim,
+// cos[t, i] = cos(positions[t] * inv_freq[i]), sin likewise: computed once per step and shared by all
+// layers with the same position encoding (float32 angles, float32 sincosf).
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float* __restrict__ cos_table, float* __restrict__ sin_table, int tokens, int half) {
+    pdl_trigger();
+    pdl_wait();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= tokens * half) return;
+    const int t = idx / half, i = idx % half;
+    sincosf((float)positions[t] * inv_freq[i], &sin_table[idx], &cos_table[idx]);
+}
+
+LLM_API int llm_rope_table(const int* positions, const float* inv_freq, float* cos_table, float* sin_table,
+                           int tokens, int half, cudaStream_t stream) {
+    if (tokens == 0 || half == 0) return 0;
+    const int total = tokens * half;
+    llm_launch(rope_table_kernel, (total + 255) / 256, 256, 0, stream, positions, inv_freq, cos_table, sin_table, tokens, half);
+    LLM_CHECK_LAUNCH("rope_table");
+    return 0;
+}
+
+LLM_API int llm_rope_store(void* qkv, const int* positions, const float* inv_freq, const float* cos_table,
+                           const float* sin_table, const int* slots, void* cache, int dtype, int tokens, int heads, int kv_heads, int head_dim,
                            int rotary_dim, int page_size, cudaStream_t stream) {
     if (tokens == 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 3) || head_dim % 16 || head_dim > 256)
@@ -247,7 +284,7 @@ LLM_API int llm_rope_store(void* qkv, const int* positions, const float* inv_fre
                  rotary_dim, head_dim);
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
-        rope_store_kernel<T><<<tokens, 256, 0, stream>>>((T*)qkv, positions, inv_freq, slots, (T*)cache,
+        llm_launch(rope_store_kernel<T>, tokens, 256, 0, stream, (T*)qkv, positions, inv_freq, cos_table, sin_table, slots, (T*)cache,
                                                          heads, kv_heads, head_dim, rotary_dim, page_size);
         LLM_CHECK_LAUNCH("rope_store");
         return 0;
@@ -259,6 +296,8 @@ LLM_API int llm_rope_store(void* qkv, const int* positions, const float* inv_fre
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t total) {
+    pdl_trigger();
+    pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / inner, i = idx % inner;
@@ -271,6 +310,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, i
 // inner % 4 == 0: four elements per thread and step
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t total4) {
+    pdl_trigger();
+    pdl_wait();
     const int inner4 = inner / 4;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -291,10 +332,10 @@ LLM_API int llm_silu_mul(const void* gu, void* act, int dtype, int tokens, int i
         if (inner % 4 == 0) {
             const size_t total4 = total / 4;
             const int blocks = (int)((total4 + 255) / 256 < 148 * 32 ? (total4 + 255) / 256 : 148 * 32);
-            silu_mul_vec_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gu, (T*)act, inner, total4);
+            llm_launch(silu_mul_vec_kernel<T>, blocks, 256, 0, stream, (const T*)gu, (T*)act, inner, total4);
         } else {
             const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-            silu_mul_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gu, (T*)act, inner, total);
+            llm_launch(silu_mul_kernel<T>, blocks, 256, 0, stream, (const T*)gu, (T*)act, inner, total);
         }
         LLM_CHECK_LAUNCH("silu_mul");
         return 0;

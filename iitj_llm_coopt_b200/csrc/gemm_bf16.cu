@@ -157,11 +157,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
 
+    pdl_trigger();
     if (warp == 0 && lane == 0) {
         // ---- producer: TMA loads into the ring --------------------------------------------
-        for (int i = 0; i < n_kb; ++i) {
+        // The weights depend on no earlier kernel: the first ring of weight tiles is requested before
+        // the wait for the previous kernel, the activation tiles (its output) after it.
+        const int pre = n_kb < stages ? n_kb : stages;
+        for (int i = 0; i < pre; ++i) {
+            unsigned char* st = tiles + (size_t)i * kStageBytes;
+            mbar_expect_tx(&full_bar[i], kStageBytes);
+            const int k = (kb0 + i) * kBlockK;
+            tma_load_2d(st, &map_w, &full_bar[i], k, feat0);
+            if (SWIGLU) tma_load_2d(st + kABytes, &map_w, &full_bar[i], k, a.up_row_offset + feat0);
+        }
+        pdl_wait();
+        for (int i = 0; i < pre; ++i)
+            tma_load_2d(tiles + (size_t)i * kStageBytes + (SWIGLU ? 2 : 1) * kABytes, &map_x, &full_bar[i],
+                        (kb0 + i) * kBlockK, tok0);
+        for (int i = pre; i < n_kb; ++i) {
             const int s = i % stages;
-            if (i >= stages && !mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1)) { give_up(1); failed = 1; break; }
+            if (!mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1)) { give_up(1); failed = 1; break; }
             unsigned char* st = tiles + (size_t)s * kStageBytes;
             mbar_expect_tx(&full_bar[s], kStageBytes);
             const int k = (kb0 + i) * kBlockK;
@@ -193,6 +208,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ---- epilogue: TMEM -> registers -> global, transposed ------------------------------
         const int quarter = warp & 3;             // a warp may only read TMEM lanes [32 * (warp % 4), +32)
         const int feat = feat0 + quarter * 32 + lane;
+        pdl_wait();                               // nothing is stored before the previous kernel has finished
         if (n_kb > 0 && mbar_wait(&accum_bar, 0) && !failed) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -237,6 +253,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 template <bool SWIGLU, typename TO>
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, TO* __restrict__ out, int splits, int tokens,
                                      int n_feat, int ld_part, int up_offset, int ldc) {
+    pdl_trigger();
+    pdl_wait();
     const int f4 = n_feat / 4;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < (size_t)tokens * f4;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -328,7 +346,7 @@ int launch_tile(const CUtensorMap& mw, const CUtensorMap& mx, GemmArgs a, dim3 g
         if (e != cudaSuccess) LLM_FAIL(-2, "gemm_bf16: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
         configured = true;
     }
-    kern<<<grid, kThreads, smem, stream>>>(mw, mx, a);
+    llm_launch(kern, grid, kThreads, smem, stream, mw, mx, a);
     LLM_CHECK_LAUNCH("gemm_bf16");
     return 0;
 }
@@ -387,11 +405,11 @@ LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, 
         const size_t work = (size_t)tokens * (n / 4);
         const int blocks = (int)((work + 255) / 256 < 148 * 8 ? (work + 255) / 256 : 148 * 8);
         if (swiglu)
-            splitk_reduce_kernel<true, bf16><<<blocks, 256, 0, stream>>>(scratch, (bf16*)out, splits, tokens, n, w_rows, n, ldc);
+            llm_launch(splitk_reduce_kernel<true, bf16>, blocks, 256, 0, stream, scratch, (bf16*)out, splits, tokens, n, w_rows, n, ldc);
         else if (out_f32)
-            splitk_reduce_kernel<false, float><<<blocks, 256, 0, stream>>>(scratch, (float*)out, splits, tokens, n, w_rows, 0, ldc);
+            llm_launch(splitk_reduce_kernel<false, float>, blocks, 256, 0, stream, scratch, (float*)out, splits, tokens, n, w_rows, 0, ldc);
         else
-            splitk_reduce_kernel<false, bf16><<<blocks, 256, 0, stream>>>(scratch, (bf16*)out, splits, tokens, n, w_rows, 0, ldc);
+            llm_launch(splitk_reduce_kernel<false, bf16>, blocks, 256, 0, stream, scratch, (bf16*)out, splits, tokens, n, w_rows, 0, ldc);
         LLM_CHECK_LAUNCH("gemm_bf16_reduce");
     }
     return 0;

@@ -16,6 +16,8 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(256)
 sgemm_tn_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
                 int M, int N, int K, int lda, int ldw, int ldc) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[SWIGLU ? 2 : 1][BK][BN + 4];
     const int tid = threadIdx.x;
@@ -90,9 +92,9 @@ LLM_API int llm_gemm_f32(const float* A, const float* W, float* C, int M, int N,
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) LLM_FAIL(-1, "gemm_f32: M %d is too large", M);
     if (swiglu)
-        sgemm_tn_kernel<true><<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+        llm_launch(sgemm_tn_kernel<true>, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
     else
-        sgemm_tn_kernel<false><<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+        llm_launch(sgemm_tn_kernel<false>, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
     LLM_CHECK_LAUNCH("gemm_f32");
     return 0;
 }

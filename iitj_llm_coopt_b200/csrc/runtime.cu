@@ -6,6 +6,17 @@ static char g_error[512] = "";
 
 char* llm_error_buffer() { return g_error; }
 
+static int g_pdl = 1;
+
+bool llm_pdl_enabled() { return g_pdl != 0; }
+
+// Switch programmatic dependent launch on (default) or off for all later launches; returns the old value.
+LLM_API int llm_set_pdl(int on) {
+    const int old = g_pdl;
+    g_pdl = on ? 1 : 0;
+    return old;
+}
+
 LLM_API const char* llm_last_error() { return g_error; }
 
 LLM_API int llm_abi_version() { return 1; }

@@ -27,6 +27,8 @@ __device__ __forceinline__ float gumbel(uint64_t key, uint32_t i) {
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ temperature,
               const unsigned long long* __restrict__ keys, int* __restrict__ out, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const int r = blockIdx.x;
@@ -63,12 +65,92 @@ sample_kernel(const float* __restrict__ logits, int ld, const float* __restrict_
     }
 }
 
+constexpr int kChunk = 2048;   // vocabulary entries per block of the two-stage form
+
+// Stage 1: the best (value, index) of one chunk of one row.
+__global__ void __launch_bounds__(256)
+sample_chunk_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ temperature,
+                    const unsigned long long* __restrict__ keys, float* __restrict__ part_v, int* __restrict__ part_i,
+                    int vocab, int chunks) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float best_v[8];
+    __shared__ int best_i[8];
+    const int c = blockIdx.x, r = blockIdx.y;
+    const float* row = logits + (size_t)r * ld;
+    const float T = temperature ? temperature[r] : 0.f;
+    const uint64_t key = keys ? keys[r] : 0ull;
+    const int end = min(vocab, (c + 1) * kChunk);
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = c * kChunk + threadIdx.x; i < end; i += 256) {
+        float v = row[i];
+        if (T > 0.f) v = v / T + gumbel(key, (uint32_t)i);
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
+        part_v[(size_t)r * chunks + c] = bv;
+        part_i[(size_t)r * chunks + c] = bi;
+    }
+}
+
+// Stage 2: the best over a row's chunks (one warp per row).
+__global__ void __launch_bounds__(32)
+sample_pick_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int* __restrict__ out, int chunks) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = threadIdx.x; c < chunks; c += 32) {
+        const float v = part_v[(size_t)r * chunks + c];
+        const int i = part_i[(size_t)r * chunks + c];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+}
+
 }  // namespace
 
+// Number of floats of scratch llm_sample wants for `rows` rows of `vocab` logits (0: none needed).
+LLM_API int llm_sample_scratch_floats(int rows, int vocab) {
+    const int chunks = (vocab + kChunk - 1) / kChunk;
+    return chunks > 1 ? 2 * rows * chunks : 0;
+}
+
+// scratch: llm_sample_scratch_floats(rows, vocab) floats, or null to scan each row with a single block.
 LLM_API int llm_sample(const float* logits, int ld, const float* temperature, const unsigned long long* keys,
-                       int* out, int rows, int vocab, cudaStream_t stream) {
+                       int* out, int rows, int vocab, float* scratch, cudaStream_t stream) {
     if (rows == 0) return 0;
-    sample_kernel<<<rows, 1024, 0, stream>>>(logits, ld, temperature, keys, out, vocab);
+    const int chunks = (vocab + kChunk - 1) / kChunk;
+    if (scratch && chunks > 1) {
+        if (rows > 65535) LLM_FAIL(-1, "sample: too many rows");
+        float* part_v = scratch;
+        int* part_i = reinterpret_cast<int*>(scratch + (size_t)rows * chunks);
+        llm_launch(sample_chunk_kernel, dim3(chunks, rows), 256, 0, stream, logits, ld, temperature, keys, part_v, part_i, vocab, chunks);
+        LLM_CHECK_LAUNCH("sample");
+        llm_launch(sample_pick_kernel, rows, 32, 0, stream, (const float*)part_v, (const int*)part_i, out, chunks);
+        LLM_CHECK_LAUNCH("sample_pick");
+        return 0;
+    }
+    llm_launch(sample_kernel, rows, 1024, 0, stream, logits, ld, temperature, keys, out, vocab);
     LLM_CHECK_LAUNCH("sample");
     return 0;
 }

@@ -71,6 +71,7 @@ class StepContext:
     query_lens: list = field(default_factory=list)
     starts: list = field(default_factory=list)
     slots_host: list = field(default_factory=list)
+    shared: dict = field(default_factory=dict)   # per-step results that several layers share (e.g. rotary tables)
 
     def buffer(self, name: str, shape, dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 import threading
 
 import torch
@@ -31,12 +32,14 @@ class KernelError(RuntimeError):
 _SIGNATURES = {
     # name: argtypes (all return int)
     "llm_check_device": [],
+    "llm_set_pdl": [_c_int],
     "llm_abi_version": [],
     "llm_embed": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "llm_add_rmsnorm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
                         _c_float, _c_void_p],
-    "llm_rope_store": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-                       _c_int, _c_int, _c_int, _c_void_p],
+    "llm_rope_table": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+    "llm_rope_store": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "llm_silu_mul": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "llm_attention_generic": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
@@ -52,7 +55,8 @@ _SIGNATURES = {
     "llm_gemm_bf16": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                       _c_void_p],
     "llm_gemm_bf16_status": [],
-    "llm_sample": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+    "llm_sample_scratch_floats": [_c_int, _c_int],
+    "llm_sample": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
 }
 
 
@@ -157,6 +161,13 @@ class Kernels:
             fn.argtypes = args
             fn.restype = _c_int
         self.launches = 0  # kernels of this library launched so far (the bench reports it)
+        # IITJ_GEMM_BACKEND=cublas|tcgen05 forces one matrix-product path, IITJ_GEMM_SMALL_TOKENS moves the
+        # boundary, IITJ_PDL=0 switches programmatic dependent launch off (all three are for measurements)
+        self.gemm_backend = os.environ.get("IITJ_GEMM_BACKEND", "auto")
+        self.gemm_small_tokens = int(os.environ.get("IITJ_GEMM_SMALL_TOKENS", "128"))
+        self.gemm_all_small = os.environ.get("IITJ_GEMM_ALL_SMALL", "0") == "1"
+        if os.environ.get("IITJ_PDL", "1") == "0":
+            self.lib.llm_set_pdl(0)
         self._scratch_bufs: dict = {}
         self.scratch_generation = 0
         self._sm_count = None
@@ -186,6 +197,10 @@ class Kernels:
     @staticmethod
     def _stream():
         return torch.cuda.current_stream().cuda_stream
+
+    def set_pdl(self, on: bool) -> bool:
+        """Programmatic dependent launch for all later launches of this library; returns the old setting."""
+        return bool(self.lib.llm_set_pdl(1 if on else 0))
 
     def check_device(self):
         rc = self.lib.llm_check_device()
@@ -223,10 +238,23 @@ class Kernels:
                    self._stream())
         return out
 
-    def rope_store(self, qkv, positions, inv_freq, slots, cache_layer, heads, kv_heads, head_dim, rotary_dim):
+    def rope_tables(self, positions, inv_freq, cos, sin):
+        """cos[t, i] = cos(positions[t] * inv_freq[i]) and sin likewise, float32 [tokens, rotary_dim/2]."""
+        _check(positions, "rope_tables.positions", torch.int32, 1)
+        _check(inv_freq, "rope_tables.inv_freq", torch.float32, 1)
+        _check(cos, "rope_tables.cos", torch.float32, 2)
+        _check(sin, "rope_tables.sin", torch.float32, 2)
+        _need(cos.shape == (positions.shape[0], inv_freq.shape[0]) and sin.shape == cos.shape, "rope_tables: wrong table shape")
+        self._call("llm_rope_table", _ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), positions.shape[0],
+                   inv_freq.shape[0], self._stream())
+        return cos, sin
+
+    def rope_store(self, qkv, positions, inv_freq, slots, cache_layer, heads, kv_heads, head_dim, rotary_dim,
+                   tables=None):
         """Rotate q (in place) and k, store k and v of every token in its cache slot.
 
-        cache_layer: [pages, 2, kv_heads, page_size, head_dim]; slots may be None (rotate only)."""
+        cache_layer: [pages, 2, kv_heads, page_size, head_dim]; slots may be None (rotate only).
+        tables: (cos, sin) of `rope_tables` for these positions, else the angles are evaluated here."""
         _check(qkv, "rope_store.qkv", tuple(DTYPE_CODE), 2)
         _check(positions, "rope_store.positions", torch.int32, 1)
         tokens = qkv.shape[0]
@@ -243,7 +271,13 @@ class Kernels:
             _need(cache_layer.shape[1] == 2 and cache_layer.shape[2] == kv_heads and cache_layer.shape[4] == head_dim,
                   f"rope_store.cache: shape {tuple(cache_layer.shape)} does not fit kv_heads/head_dim")
             page_size = cache_layer.shape[3]
-        self._call("llm_rope_store", _ptr(qkv), _ptr(positions), _ptr(inv_freq) if rotary_dim else None,
+        cos = sin = None
+        if tables is not None and rotary_dim:
+            cos, sin = tables
+            _check(cos, "rope_store.cos", torch.float32, 2)
+            _check(sin, "rope_store.sin", torch.float32, 2)
+            _need(cos.shape == (tokens, rotary_dim // 2) and sin.shape == cos.shape, "rope_store: wrong table shape")
+        self._call("llm_rope_store", _ptr(qkv), _ptr(positions), _ptr(inv_freq) if rotary_dim else None, _ptr(cos), _ptr(sin),
                    _ptr(slots), _ptr(cache_layer) if slots is not None else None, DTYPE_CODE[qkv.dtype], tokens,
                    heads, kv_heads, head_dim, rotary_dim, page_size, self._stream())
 
@@ -351,9 +385,6 @@ class Kernels:
         return out
 
     # Which kernel multiplies: "tcgen05" (this library) or "cublas".  `gemm_backend` may force one.
-    gemm_backend = "auto"
-    gemm_small_tokens = 128
-
     def gemm_policy(self, tokens, n, k, swiglu) -> str:
         """Measured on B200 at the 8B shapes: the fused SwiGLU product of this library matches
         cuBLAS + a separate SiLU kernel up to 128 tokens and saves a launch; the plain products
@@ -362,7 +393,9 @@ class Kernels:
             return "cublas"
         if self.gemm_backend != "auto":
             return self.gemm_backend
-        return "tcgen05" if (swiglu and tokens <= self.gemm_small_tokens) else "cublas"
+        if tokens <= self.gemm_small_tokens and (swiglu or self.gemm_all_small):
+            return "tcgen05"
+        return "cublas"
 
     def gemm_splits(self, tokens, n, k, swiglu) -> int:
         """Split the k range when the product has too few CTAs to fill the GPU: candidates are
@@ -396,8 +429,10 @@ class Kernels:
             _check(temperature, "sample.temperature", torch.float32, 1)
             _check(keys, "sample.keys", torch.int64, 1)
             _need(temperature.shape[0] == rows and keys.shape[0] == rows, "sample: one temperature and key per row")
+        need = self.lib.llm_sample_scratch_floats(rows, logits.shape[1])
+        scratch = self._scratch("sample.part", need, logits.device) if need else None
         self._call("llm_sample", _ptr(logits), logits.shape[1], _ptr(temperature), _ptr(keys), _ptr(out), rows,
-                   logits.shape[1], self._stream())
+                   logits.shape[1], _ptr(scratch), self._stream())
         return out
 
 

@@ -42,9 +42,22 @@ class RotaryEmbedding(Part):
         self.head_dim, self.rotary_dim = spec.head_dim, spec.rotary_dim
         self.inv_freq = rope_inverse_frequencies(spec.rotary_dim, spec.theta, spec.scaling_dict()).to(device)
 
+    def tables(self, ctx):
+        """cos and sin of this step's positions, computed by the first layer that asks and shared by
+        every layer with the same position spec."""
+        key = ("rope", self.spec)
+        tabs = ctx.shared.get(key)
+        if tabs is None:
+            half = self.rotary_dim // 2
+            name = f"rope.{hash(self.spec) & 0xffffffff:x}"
+            cos = ctx.buffer(name + ".cos", (ctx.num_tokens, half), torch.float32)
+            sin = ctx.buffer(name + ".sin", (ctx.num_tokens, half), torch.float32)
+            tabs = ctx.shared[key] = self.k.rope_tables(ctx.positions, self.inv_freq, cos, sin)
+        return tabs
+
     def encode_and_store(self, ctx, qkv, cache_view, slots, heads, kv_heads):
         self.k.rope_store(qkv, ctx.positions, self.inv_freq, slots, cache_view, heads, kv_heads,
-                          self.head_dim, self.rotary_dim)
+                          self.head_dim, self.rotary_dim, tables=self.tables(ctx) if self.rotary_dim else None)
 
 
 class NoPosition(Part):

@@ -91,6 +91,14 @@ def test_rope_store(K, dtype, heads, kv_heads, head_dim, rotary, page):
     close(got[:, :q], want[:, :q], dtype)
     close(cache, want_cache, dtype)
     assert torch.equal(cache == 7.0, want_cache == 7.0)          # nothing else was touched
+    # with the step's table of cosines and sines
+    if rotary:
+        cos = torch.empty(tokens, rotary // 2, device="cuda")
+        sin = torch.empty_like(cos)
+        K.rope_tables(positions, inv_freq, cos, sin)
+        got3, cache3 = qkv.clone(), torch.full_like(cache, 7.0)
+        K.rope_store(got3, positions, inv_freq, perm, cache3, heads, kv_heads, head_dim, rotary, tables=(cos, sin))
+        assert torch.equal(got3, got) and torch.equal(cache3, cache)
     # rotate only (no slots): the cache is not needed
     got2 = qkv.clone()
     K.rope_store(got2, positions, inv_freq, None, None, heads, kv_heads, head_dim, rotary)

@@ -141,7 +141,13 @@ class TorchKernels:
         out.copy_(y)
         return out
 
-    def rope_store(self, qkv, positions, inv_freq, slots, cache_layer, heads, kv_heads, head_dim, rotary_dim):
+    def rope_tables(self, positions, inv_freq, cos, sin):
+        ang = positions.float().unsqueeze(1) * inv_freq.float().unsqueeze(0)
+        cos.copy_(ang.cos())
+        sin.copy_(ang.sin())
+        return cos, sin
+
+    def rope_store(self, qkv, positions, inv_freq, slots, cache_layer, heads, kv_heads, head_dim, rotary_dim, tables=None):
         rot = ref_rope(qkv, positions, inv_freq, heads, kv_heads, head_dim, rotary_dim).to(qkv.dtype)
         if slots is not None:
             ref_store(cache_layer, rot, slots, heads, kv_heads, head_dim)
