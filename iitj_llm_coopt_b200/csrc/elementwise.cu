@@ -147,11 +147,11 @@ LLM_API int llm_add_rmsnorm(float* residual, const void* delta, const int* rows,
         using TD = decltype(tag);
         return llm_dispatch_dtype(weight_dtype, [&](auto wtag) {
             using TW = decltype(wtag);
-            if (width % 4 == 0 && width <= 4 * 512 * 8) {
-                // up to 512 threads, up to 8 float4 per thread
+            if (width % 4 == 0 && width <= 4 * 256 * 16) {
+                // up to 256 threads, up to 16 float4 per thread: many independent loads in flight per thread
                 const int vecs = width / 4;
                 int threads = (vecs + 31) / 32 * 32;
-                if (threads > 512) threads = 512;
+                if (threads > 256) threads = 256;
                 const int per = (vecs + threads - 1) / threads;
                 auto go = [&](auto kern) {
                     llm_launch(kern, out_rows, threads, 0, stream, residual, (const TD*)delta, rows, (const TW*)weight, (TD*)out, width, eps);
@@ -159,7 +159,8 @@ LLM_API int llm_add_rmsnorm(float* residual, const void* delta, const int* rows,
                 if (per <= 1) go(add_rmsnorm_vec_kernel<TD, TW, 1>);
                 else if (per <= 2) go(add_rmsnorm_vec_kernel<TD, TW, 2>);
                 else if (per <= 4) go(add_rmsnorm_vec_kernel<TD, TW, 4>);
-                else go(add_rmsnorm_vec_kernel<TD, TW, 8>);
+                else if (per <= 8) go(add_rmsnorm_vec_kernel<TD, TW, 8>);
+                else go(add_rmsnorm_vec_kernel<TD, TW, 16>);
                 LLM_CHECK_LAUNCH("add_rmsnorm");
                 return 0;
             }
@@ -196,7 +197,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   int rotary_dim, int page_size) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float cs[128], sn[128];              // rotary_dim / 2 <= 128 (head_dim <= 256)
+    __shared__ __align__(16) float cs[128], sn[128];  // rotary_dim / 2 <= 128 (head_dim <= 256)
     const int t = blockIdx.x;
     const int half = rotary_dim / 2;
     const int row_width = (heads + 2 * kv_heads) * head_dim;
@@ -220,20 +221,39 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
     }
     __syncthreads();
 
-    // rotated pairs of query and key heads, two neighbouring pairs per step (half is even: head sizes are multiples of 16)
+    // rotated pairs of query and key heads, four neighbouring pairs per step where the size allows
     const int rot_heads = heads + kv_heads;
-    const int hp = half / 2;
-    for (int w = threadIdx.x; w < rot_heads * hp; w += blockDim.x) {
-        const int h = w / hp, i = (w % hp) * 2;
-        T* x = row + (size_t)h * head_dim;
-        const float a0 = to_f32(x[i]), a1 = to_f32(x[i + 1]), b0 = to_f32(x[i + half]), b1 = to_f32(x[i + half + 1]);
-        const T o0 = from_f32<T>(a0 * cs[i] - b0 * sn[i]), o1 = from_f32<T>(a1 * cs[i + 1] - b1 * sn[i + 1]);
-        const T p0 = from_f32<T>(b0 * cs[i] + a0 * sn[i]), p1 = from_f32<T>(b1 * cs[i + 1] + a1 * sn[i + 1]);
-        T* dst = nullptr;
-        if (h < heads) dst = x;
-        else if (slot >= 0) dst = cache + kbase + (size_t)(h - heads) * head_stride;
-        if (dst) {
-            dst[i] = o0; dst[i + 1] = o1; dst[i + half] = p0; dst[i + half + 1] = p1;
+    if (half % 4 == 0) {
+        const int hp = half / 4;
+        for (int w = threadIdx.x; w < rot_heads * hp; w += blockDim.x) {
+            const int h = w / hp, i = (w % hp) * 4;
+            T* x = row + (size_t)h * head_dim;
+            const float4 a = Vec4<T>::load(x + i), b = Vec4<T>::load(x + i + half);
+            const float4 c = *reinterpret_cast<const float4*>(cs + i), sg = *reinterpret_cast<const float4*>(sn + i);
+            const float4 lo4 = make_float4(a.x * c.x - b.x * sg.x, a.y * c.y - b.y * sg.y, a.z * c.z - b.z * sg.z, a.w * c.w - b.w * sg.w);
+            const float4 hi4 = make_float4(b.x * c.x + a.x * sg.x, b.y * c.y + a.y * sg.y, b.z * c.z + a.z * sg.z, b.w * c.w + a.w * sg.w);
+            T* dst = nullptr;
+            if (h < heads) dst = x;
+            else if (slot >= 0) dst = cache + kbase + (size_t)(h - heads) * head_stride;
+            if (dst) {
+                Vec4<T>::store(dst + i, lo4);
+                Vec4<T>::store(dst + i + half, hi4);
+            }
+        }
+    } else {
+        const int hp = half / 2;
+        for (int w = threadIdx.x; w < rot_heads * hp; w += blockDim.x) {
+            const int h = w / hp, i = (w % hp) * 2;
+            T* x = row + (size_t)h * head_dim;
+            const float a0 = to_f32(x[i]), a1 = to_f32(x[i + 1]), b0 = to_f32(x[i + half]), b1 = to_f32(x[i + half + 1]);
+            const T o0 = from_f32<T>(a0 * cs[i] - b0 * sn[i]), o1 = from_f32<T>(a1 * cs[i + 1] - b1 * sn[i + 1]);
+            const T p0 = from_f32<T>(b0 * cs[i] + a0 * sn[i]), p1 = from_f32<T>(b1 * cs[i + 1] + a1 * sn[i + 1]);
+            T* dst = nullptr;
+            if (h < heads) dst = x;
+            else if (slot >= 0) dst = cache + kbase + (size_t)(h - heads) * head_stride;
+            if (dst) {
+                dst[i] = o0; dst[i + 1] = o1; dst[i + half] = p0; dst[i + half + 1] = p1;
+            }
         }
     }
     if (slot < 0) return;
@@ -307,20 +327,23 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, i
     }
 }
 
-// inner % 4 == 0: four elements per thread and step
+// inner % 8 == 0: eight elements per thread and step (16-byte loads in bfloat16)
 template <typename T>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t total4) {
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t total8) {
     pdl_trigger();
     pdl_wait();
-    const int inner4 = inner / 4;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
+    const int inner8 = inner / 8;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
          idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = idx / inner4, i = (idx % inner4) * 4;
-        const float4 g = Vec4<T>::load(gu + t * 2 * inner + i);
-        const float4 u = Vec4<T>::load(gu + t * 2 * inner + inner + i);
-        Vec4<T>::store(act + t * inner + i,
-                       make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
-                                   g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
+        const size_t t = idx / inner8, i = (idx % inner8) * 8;
+        const T* gp = gu + t * 2 * inner + i;
+        const float4 g0 = Vec4<T>::load(gp), g1 = Vec4<T>::load(gp + 4);
+        const float4 u0 = Vec4<T>::load(gp + inner), u1 = Vec4<T>::load(gp + inner + 4);
+        T* dst = act + t * inner + i;
+        Vec4<T>::store(dst, make_float4(g0.x / (1.0f + expf(-g0.x)) * u0.x, g0.y / (1.0f + expf(-g0.y)) * u0.y,
+                                        g0.z / (1.0f + expf(-g0.z)) * u0.z, g0.w / (1.0f + expf(-g0.w)) * u0.w));
+        Vec4<T>::store(dst + 4, make_float4(g1.x / (1.0f + expf(-g1.x)) * u1.x, g1.y / (1.0f + expf(-g1.y)) * u1.y,
+                                            g1.z / (1.0f + expf(-g1.z)) * u1.z, g1.w / (1.0f + expf(-g1.w)) * u1.w));
     }
 }
 
@@ -329,10 +352,10 @@ LLM_API int llm_silu_mul(const void* gu, void* act, int dtype, int tokens, int i
     if (total == 0) return 0;
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
-        if (inner % 4 == 0) {
-            const size_t total4 = total / 4;
-            const int blocks = (int)((total4 + 255) / 256 < 148 * 32 ? (total4 + 255) / 256 : 148 * 32);
-            llm_launch(silu_mul_vec_kernel<T>, blocks, 256, 0, stream, (const T*)gu, (T*)act, inner, total4);
+        if (inner % 8 == 0) {
+            const size_t total8 = total / 8;
+            const int blocks = (int)((total8 + 255) / 256 < 148 * 32 ? (total8 + 255) / 256 : 148 * 32);
+            llm_launch(silu_mul_vec_kernel<T>, blocks, 256, 0, stream, (const T*)gu, (T*)act, inner, total8);
         } else {
             const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
             llm_launch(silu_mul_kernel<T>, blocks, 256, 0, stream, (const T*)gu, (T*)act, inner, total);
