@@ -134,6 +134,8 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one phase alone with few repetitions and print a short line (for profilers)")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step by itself (for profiling)")
     args = ap.parse_args()
 
@@ -147,6 +149,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.only:
+        args.no_points = args.no_e2e = True
 
     import torch
 
@@ -223,6 +227,14 @@ def main() -> int:
                 times.append(start.elapsed_time(end))
         return times
 
+    if args.only == "prefill":
+        t = prefill_run(args.prefill_tokens, 1, 1)
+        print(json.dumps({"only": "prefill", "tokens": args.prefill_tokens, "ms": t[0]}))
+        return 0
+    if args.only == "decode":
+        t, n = decode_run(B, max(1, K), 3)
+        print(json.dumps({"only": "decode", "batch": B, "ms": sum(t) / len(t), "launches_per_step": n / len(t)}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     times, launches = decode_run(B, K, W)

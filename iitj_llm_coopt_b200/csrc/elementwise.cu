@@ -148,10 +148,12 @@ LLM_API int llm_add_rmsnorm(float* residual, const void* delta, const int* rows,
         return llm_dispatch_dtype(weight_dtype, [&](auto wtag) {
             using TW = decltype(wtag);
             if (width % 4 == 0 && width <= 4 * 256 * 16) {
-                // up to 256 threads, up to 16 float4 per thread: many independent loads in flight per thread
+                // Many rows: 256 threads with up to 16 float4 each (bytes in flight per SM).  Few rows (decode):
+                // up to 1024 threads so that a row is one round of loads (latency).
                 const int vecs = width / 4;
                 int threads = (vecs + 31) / 32 * 32;
-                if (threads > 256) threads = 256;
+                const int cap = out_rows >= 512 ? 256 : 1024;
+                if (threads > cap) threads = cap;
                 const int per = (vecs + threads - 1) / threads;
                 auto go = [&](auto kern) {
                     llm_launch(kern, out_rows, threads, 0, stream, residual, (const TD*)delta, rows, (const TW*)weight, (TD*)out, width, eps);
