@@ -20,9 +20,7 @@
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in a status
 // word (llm_gemm_bf16_status), and the CTA falls through to its teardown (TMEM is freed).
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05_common.cuh"
 
 #include <mutex>
 #include <unordered_map>
@@ -35,77 +33,9 @@ constexpr int kFeatTile = 128;                 // UMMA M
 constexpr int kBlockK = 64;                    // elements per k-block: 128 bytes = one swizzle row
 constexpr int kThreads = 192;                  // warp 0: TMA, warp 1: MMA + TMEM alloc, warps 2-5: epilogue
 constexpr int kMaxStages = 12;
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ int g_status = 0;                   // 0 ok; else (code << 16) | block id of the first CTA that gave up
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity to complete; false if it did not.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
 __device__ __forceinline__ void give_up(int code) { atomicCAS(&g_status, 0, (code << 16) | (int)(blockIdx.x & 0xffff)); }
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major tile of rows of 128 bytes, 128-byte swizzle,
-// 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);          // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                                    // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                          // stride byte offset
-    d |= (uint64_t)1 << 46;                                    // version
-    d |= (uint64_t)2 << 61;                                    // SWIZZLE_128B
-    return d;
-}
-
-// Instruction descriptor of tcgen05.mma kind::f16: bf16 x bf16 -> f32, both operands K-major.
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
-    return (1u << 4)            // D format f32
-         | (1u << 7)            // A format bf16
-         | (1u << 10)           // B format bf16
-         | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-}
 
 enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_PARTIAL = 2 };
 
@@ -297,40 +227,47 @@ EncodeTiledFn encode_fn() {
 }
 
 struct MapKey {
-    const void* ptr; int rows, cols, box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+    const void* ptr; uint64_t rows, cols; uint32_t box_rows, box_cols;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols;
+    }
 };
 struct MapKeyHash {
     size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^ ((size_t)k.box_rows << 20);
+        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^
+               ((size_t)k.box_rows << 20) ^ ((size_t)k.box_cols << 40);
     }
 };
 std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 std::mutex g_maps_mutex;
 
-// Map of a row-major [rows, cols] bf16 matrix, box = 64 columns x box_rows rows, 128-byte swizzle, zero fill.
-int tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+}  // namespace
+
+int llm_tensor_map_2d(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols, CUtensorMap* out) {
     std::lock_guard<std::mutex> lock(g_maps_mutex);
-    const MapKey key{ptr, rows, cols, box_rows};
+    const MapKey key{ptr, rows, cols, box_rows, box_cols};
     auto it = g_maps.find(key);
     if (it != g_maps.end()) { *out = it->second; return 0; }
     EncodeTiledFn fn = encode_fn();
-    if (!fn) LLM_FAIL(-2, "gemm_bf16: cuTensorMapEncodeTiled is not available from this driver");
-    if (((uintptr_t)ptr & 15) || (cols % 8)) LLM_FAIL(-1, "gemm_bf16: matrices must be 16-byte aligned with K %% 8 == 0 (K = %d)", cols);
+    if (!fn) LLM_FAIL(-2, "tensor map: cuTensorMapEncodeTiled is not available from this driver");
+    if (((uintptr_t)ptr & 15) || (cols % 8)) LLM_FAIL(-1, "tensor map: matrices must be 16-byte aligned with a row length that is a multiple of 8 (got %llu)", (unsigned long long)cols);
+    if (box_cols * 2 > 128 || box_rows > 256) LLM_FAIL(-1, "tensor map: box %u x %u does not fit the 128-byte swizzle", box_cols, box_rows);
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     CUtensorMap m;
     CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) LLM_FAIL(-2, "gemm_bf16: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    if (r != CUDA_SUCCESS) LLM_FAIL(-2, "tensor map: cuTensorMapEncodeTiled failed with code %d", (int)r);
     if (g_maps.size() > 4096) g_maps.clear();
     g_maps.emplace(key, m);
     *out = m;
     return 0;
 }
+
+namespace {
 
 template <int N_TOK, bool SWIGLU>
 int launch_tile(const CUtensorMap& mw, const CUtensorMap& mx, GemmArgs a, dim3 grid, cudaStream_t stream) {
@@ -374,8 +311,8 @@ LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, 
     const int w_rows = swiglu ? 2 * n : n;
     const int tile = llm_gemm_bf16_token_tile(tokens);
     CUtensorMap mw, mx;
-    if (int rc = tensor_map(w, w_rows, K, kFeatTile, &mw)) return rc;
-    if (int rc = tensor_map(x, tokens, K, tile, &mx)) return rc;
+    if (int rc = llm_tensor_map_2d(w, w_rows, K, kFeatTile, kBlockK, &mw)) return rc;
+    if (int rc = llm_tensor_map_2d(x, tokens, K, tile, kBlockK, &mx)) return rc;
     GemmArgs a;
     a.out = splits > 1 ? (void*)scratch : out;
     a.out_mode = splits > 1 ? OUT_PARTIAL : (out_f32 ? OUT_F32 : OUT_BF16);

@@ -187,6 +187,7 @@ class ModelRunner:
             place(f"table{g}", B * widths[g])
         place("attn_items", plan.n_items)
         place("attn_tiles", 4 * plan.n_tiles)
+        place("attn_big_tiles", 4 * len(plan.big_rows))
         old_meta = self._meta
         host = self._stage(off)
         if self._meta is not old_meta:
@@ -213,6 +214,7 @@ class ModelRunner:
             put("attn_items", plan.item_rows)
         if plan.n_tiles:
             put("attn_tiles", np.asarray(plan.tile_rows, dtype=np.int64).reshape(-1))
+            put("attn_big_tiles", np.asarray(plan.big_rows, dtype=np.int64).reshape(-1))
         ps = cache.page_size
         slots_host = {}
         for g in groups:
@@ -238,6 +240,7 @@ class ModelRunner:
 
         plan.items = dev("attn_items") if plan.n_items else None
         plan.tiles = dev("attn_tiles").view(-1, 4) if plan.n_tiles else None
+        plan.big_tiles = dev("attn_big_tiles").view(-1, 4) if plan.n_tiles else None
         token_request, positions = dev("token_request"), dev("positions")
         cu_dev, seq_dev = dev("cu_seqlens"), dev("seq_lens")
         metas = {}

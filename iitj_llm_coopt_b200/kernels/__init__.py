@@ -49,6 +49,10 @@ _SIGNATURES = {
     "llm_attention_decode_bf16": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                   _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                   _c_float, _c_int, _c_int, _c_void_p],
+    "llm_attention_tcgen05_supported": [_c_int, _c_int, _c_int, _c_int],
+    "llm_attention_prefill_tcgen05": [_c_void_p, _c_int, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p,
+                                      _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "llm_attention_tcgen05_status": [],
     "llm_gemm_f32": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                      _c_void_p],
     "llm_gemm_bf16_token_tile": [_c_int],
@@ -90,7 +94,7 @@ class AttentionPlan:
 
     def __init__(self, query_lens, seq_lens, device, items=None, tiles=None):
         self.decode_pos = []
-        item_rows, tile_rows, row = [], [], 0
+        item_rows, tile_rows, big_rows, row = [], [], [], 0
         for b, (n, total) in enumerate(zip(query_lens, seq_lens)):
             if n == 1:
                 item_rows.append(row)
@@ -98,7 +102,10 @@ class AttentionPlan:
             else:
                 for s in range(0, n, self.TILE):
                     tile_rows.append((row + s, min(self.TILE, n - s), total - n + s, b))
+                for s in range(0, n, 2 * self.TILE):        # 128-query tiles of the tcgen05 kernel
+                    big_rows.append((row + s, min(2 * self.TILE, n - s), total - n + s, b))
             row += n
+        self.big_rows, self.big_tiles = big_rows, None
         self.n_items, self.n_tiles = len(item_rows), len(tile_rows)
         self.items, self.tiles = items, tiles
         self.context_bound = None     # an upper bound of the contexts that fixes the split choice (captured graphs)
@@ -166,6 +173,7 @@ class Kernels:
         self.gemm_backend = os.environ.get("IITJ_GEMM_BACKEND", "auto")
         self.gemm_small_tokens = int(os.environ.get("IITJ_GEMM_SMALL_TOKENS", "128"))
         self.gemm_all_small = os.environ.get("IITJ_GEMM_ALL_SMALL", "0") == "1"
+        self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
         if os.environ.get("IITJ_PDL", "1") == "0":
             self.lib.llm_set_pdl(0)
         self._scratch_bufs: dict = {}
@@ -313,7 +321,15 @@ class Kernels:
         page_size = cache_layer.shape[3]
         if qkv.dtype == torch.bfloat16 and self.lib.llm_attention_bf16_supported(heads, kv_heads, head_dim):
             plan = attention_plan(meta, qkv.device)
-            if plan.n_tiles:
+            if plan.n_tiles and self.attention_tcgen05 and \
+                    self.lib.llm_attention_tcgen05_supported(heads, kv_heads, head_dim, page_size):
+                if plan.big_tiles is None:
+                    plan.big_tiles = torch.tensor(plan.big_rows, dtype=torch.int32).to(qkv.device)
+                self._call("llm_attention_prefill_tcgen05", _ptr(qkv), qkv.shape[1], tokens, _ptr(cache_layer),
+                           cache_layer.shape[0], _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.big_tiles),
+                           len(plan.big_rows), _ptr(out), out.shape[1], heads, kv_heads, head_dim, page_size, int(window),
+                           float(scale), self._stream())
+            elif plan.n_tiles:
                 self._call("llm_attention_prefill_bf16", _ptr(qkv), qkv.shape[1], _ptr(cache_layer),
                            _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.tiles), plan.n_tiles, _ptr(out),
                            out.shape[1], heads, kv_heads, head_dim, page_size, int(window), float(scale), self._stream())
@@ -413,6 +429,10 @@ class Kernels:
             if best[0] is None or cost < best[0]:
                 best = (cost, s)
         return best[1]
+
+    def attention_status(self) -> int:
+        """0, or a code if the tcgen05 attention kernel gave up waiting on a barrier since the last call."""
+        return self.lib.llm_attention_tcgen05_status()
 
     def gemm_status(self) -> int:
         """0, or a code if a tcgen05 GEMM gave up waiting on one of its barriers since the last call."""

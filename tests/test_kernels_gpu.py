@@ -361,3 +361,48 @@ def test_gemm_tcgen05_row_does_not_depend_on_batch(K):
     K.gemm_tcgen05(x, w, full, splits=2)
     K.gemm_tcgen05(x[31:32].contiguous(), w, one, splits=2)
     assert torch.equal(full[31:32], one)
+
+
+# ---- the tcgen05 prefill attention (bfloat16, head size 128) -------------------------------
+@pytest.mark.parametrize("heads,kv_heads,page,window", [(8, 2, 16, 0), (4, 1, 8, 0), (2, 2, 64, 0), (3, 1, 128, 0),
+                                                        (4, 2, 16, 100), (4, 2, 32, 128), (16, 1, 16, 0)])
+def test_attention_tcgen05_portions(K, heads, kv_heads, page, window):
+    """Portions of several 128-query tiles, starting at positions that are no multiple of 128, beside
+    short ones; page sizes from 8 to 128.  Decoded tokens in the same call go to the decode kernel."""
+    assert K.lib.llm_attention_tcgen05_supported(heads, kv_heads, 128, page)
+    lens, qlens = [700, 130, 391, 64, 900, 5], [300, 130, 129, 64, 1, 2]
+    q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, 128, page, lens, qlens, 120)
+    out = torch.zeros(q.shape[0], heads * 128, device="cuda", dtype=torch.bfloat16)
+    K.attention(q, cache, meta, out, heads, kv_heads, 128, window=window)
+    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, 128, window)
+    close(out, want, torch.bfloat16)
+    assert K.attention_status() == 0
+    # the mma.sync kernel gives the same to rounding
+    old, K.attention_tcgen05 = K.attention_tcgen05, False
+    try:
+        meta.attention_plan = None
+        out2 = torch.zeros_like(out)
+        K.attention(q, cache, meta, out2, heads, kv_heads, 128, window=window)
+    finally:
+        K.attention_tcgen05 = old
+    close(out2, want, torch.bfloat16)
+
+
+def test_attention_tcgen05_far_key_and_page_edges(K):
+    """One key among 2000 stands out for every query of a 256-token portion; it sits on a page edge."""
+    heads, kv_heads, page, L, n = 2, 1, 16, 2000, 256
+    for far in (0, 15, 16, 127, 128, 1743):
+        q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, 128, page, [L], [n], 130 + far)
+        cache.mul_(0.05)
+        pg, off = int(meta.block_table[0, far // page]), far % page
+        key = rnd((128,), torch.float32, 131)
+        key = key / key.norm()
+        cache[pg, 0, 0, off] = (key * 40.0).to(torch.bfloat16)
+        cache[pg, 1, 0, off] = 3.0
+        q[:, :heads * 128] = (key * 12.0).to(torch.bfloat16).repeat(heads)        # every query points at that key
+        out = torch.zeros(n, heads * 128, device="cuda", dtype=torch.bfloat16)
+        K.attention(q, cache, meta, out, heads, kv_heads, 128)
+        want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, 128)
+        close(out, want, torch.bfloat16)
+        assert (out.float() - 3.0).abs().max() < 0.1
+    assert K.attention_status() == 0
