@@ -139,3 +139,51 @@ def test_trace_run_program(model_dirs, tmp_path, dtype, name):
                 r += 1
             consumed[rid] += len(toks)
     assert worst <= (1e-4 if dtype == "float32" else 2e-2), worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_recomputes_the_same_tokens(lively_dirs, dtype):
+    """A pool so small that running requests are preempted and re-prefilled with what they had generated:
+    the tokens must be those of an engine with room for everything."""
+    cfg_d, seed, page = CONFIGS["B"]
+    prompts = list(cases.requests_for(cfg_d["vocab_size"], [30, 41, 25, 36], seed + 50).values())
+    params = SamplingParams(max_tokens=40, ignore_eos=True)
+    roomy = LLM(lively_dirs["B"], dtype=dtype, page_size=page, num_pages=200, max_num_seqs=4)
+    want = [o.token_ids for o in roomy.generate(prompts, params)]
+    assert roomy.engine.counters["num_preemptions_total"] == 0
+    del roomy
+    tight = LLM(lively_dirs["B"], dtype=dtype, page_size=page, num_pages=26, max_num_seqs=4, max_num_batched_tokens=48)
+    outs = tight.generate(prompts, params)
+    assert tight.engine.counters["num_preemptions_total"] >= 1 and max(o.num_preemptions for o in outs) >= 1
+    got = [o.token_ids for o in outs]
+    if dtype == "float32":
+        assert got == want
+    else:
+        cfg, w = plain.read_model_dir(lively_dirs["B"], torch.float32)
+        assert all(margins_ok(cfg, w, p, g, 0.05) for p, g in zip(prompts, got))
+    tight.engine.cache.check()
+    assert tight.engine.cache.num_free == 26
+
+
+def test_wide_layer_at_the_benchmark_widths(tmp_path):
+    """One layer with the widths of the benchmark model (hidden 4096, 32 heads / 8 kv heads of 128, inner 14336),
+    a smaller vocabulary: float32 and bfloat16 against the plain implementation, whole and in portions."""
+    cfg_d = {"architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 1,
+             "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 2000, "rms_norm_eps": 1e-5,
+             "rope_theta": 500000.0, "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                      "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+             "tie_word_embeddings": False, "max_position_embeddings": 131072}
+    d = str(tmp_path / "wide")
+    write_model_dir(cfg_d, d, seed=9)
+    cfg, w = plain.read_model_dir(d, torch.float32)
+    reqs = cases.requests_for(2000, [300, 140], 60)
+    ref = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    from helpers import make_engine, rel_err, run_steps
+    for dtype, tol in (("float32", 1e-4), ("bfloat16", 2e-2)):
+        eng = make_engine(d, dtype, 16, 64, max_num_seqs=2, max_num_batched_tokens=512)
+        for steps in (cases.whole(reqs), cases.portions(reqs, [130, 2, 64, 1, 100])):
+            rows = run_steps(eng, steps)
+            for rid, toks in reqs.items():
+                got = torch.stack([rows[(rid, i)] for i in range(len(toks))])
+                assert rel_err(got, ref[rid]) <= tol, (dtype, rid)
+        del eng
