@@ -7,9 +7,10 @@
 //
 //   S = Q K^T      tcgen05.mma, M = 128 queries, N = 128 keys, K = 128 dims, both operands K-major
 //                  in shared memory; S lands in tensor memory (two buffers of 128 columns).
-//   softmax        four warps, one thread per query row: a thread reads its row of S with tcgen05.ld
-//                  (no shuffles: a TMEM lane is a row), masks by position, takes the row maximum,
-//                  exponentiates in float32 and writes P as bfloat16 into a swizzled shared tile.
+//   softmax        eight warps, two threads per query row (64 of the tile's 128 keys each): a thread reads
+//                  its part of the row of S with tcgen05.ld (a TMEM lane is a row: no shuffles), masks by
+//                  position, takes the maximum (the two halves meet through shared memory), exponentiates
+//                  in float32 and writes P as bfloat16 into a swizzled shared tile.
 //   O_tile = P V   tcgen05.mma, M = 128 queries, N = 128 dims, K = 128 keys; P is K-major, V is
 //                  MN-major (a key's 128 dims are contiguous), so the V tile is used as it was loaded.
 //   accumulate     the same threads read O_tile from tensor memory and fold it into a float32 row
@@ -33,7 +34,9 @@ constexpr int kKeys = 128;        // keys per tile
 constexpr int kDim = 128;         // head size
 constexpr int kHalfBytes = 128 * 128;          // one 64-column half of a [128 x 128] bf16 tile: 128 rows x 128 bytes
 constexpr int kTileBytes = 2 * kHalfBytes;     // 32 KiB
-constexpr int kThreads = 192;     // warp 0: loads, warp 1: MMA + TMEM, warps 2-5: softmax and output
+constexpr int kThreads = 320;     // warp 0: loads, warp 1: MMA + TMEM, warps 2-9: softmax and output
+constexpr int kSoftmaxThreads = 256;
+constexpr int kCols = 64;         // columns of S (keys) and of O (dims) per softmax thread
 constexpr uint32_t kTmemCols = 512;            // S0 | S1 | O0 | O1, 128 float32 columns each
 
 __device__ int g_attn_status = 0;
@@ -50,43 +53,43 @@ __device__ __forceinline__ float ex2(float x) {          // 2^x, x <= 0 here; on
     return y;
 }
 
-// Row maximum over the 128 columns of one S buffer (this thread's TMEM lane).
+// This thread's 64 columns of one S or O buffer (its TMEM lane) in one round trip.
+__device__ __forceinline__ void load_cols(uint32_t addr, uint32_t (&r)[kCols]) {
+    tmem_ld32(addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+    tmem_ld32(addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Maximum over the 64 scores; k0 = key of the first one.
 template <bool MASK>
-__device__ __forceinline__ float row_max(uint32_t s_addr, int k0, int row_pos, int row_lo) {
+__device__ __forceinline__ float row_max(const uint32_t (&r)[kCols], int k0, int row_pos, int row_lo) {
     float mx = -INFINITY;
 #pragma unroll
-    for (int c0 = 0; c0 < kKeys; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-            if (MASK) {
-                const int key = k0 + c0 + c;
-                if (key <= row_pos && key >= row_lo) mx = fmaxf(mx, __uint_as_float(r[c]));
-            } else {
-                mx = fmaxf(mx, __uint_as_float(r[c]));
-            }
+    for (int c = 0; c < kCols; ++c) {
+        if (MASK) {
+            const int key = k0 + c;
+            if (key <= row_pos && key >= row_lo) mx = fmaxf(mx, __uint_as_float(r[c]));
+        } else {
+            mx = fmaxf(mx, __uint_as_float(r[c]));
         }
     }
     return mx;
 }
 
-// P = 2^(S * sl - mu) as bfloat16 into this thread's row of the swizzled P tile; returns the row sum.
+// P = 2^(S * sl - mu) of the 64 scores as bfloat16 into this thread's row of one half of the swizzled P tile
+// (`p_half` = that half's base: 128 rows of 128 bytes); returns the sum.
 template <bool MASK>
-__device__ __forceinline__ float row_exp(uint32_t s_addr, unsigned char* p_tile, int row, float sl, float mu, int k0,
-                                         int row_pos, int row_lo) {
+__device__ __forceinline__ float row_exp(const uint32_t (&r)[kCols], unsigned char* p_half, int row, float sl, float mu,
+                                         int k0, int row_pos, int row_lo) {
     float sum = 0.f;
+    unsigned char* prow = p_half + row * 128;
 #pragma unroll
-    for (int c0 = 0; c0 < kKeys; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        uint32_t packed[16];
+    for (int c0 = 0; c0 < kCols; c0 += 8) {          // 8 keys = one 16-byte chunk
+        uint32_t packed[4];
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-            float p0 = ex2(fmaf(__uint_as_float(r[c]), sl, -mu));
-            float p1 = ex2(fmaf(__uint_as_float(r[c + 1]), sl, -mu));
+        for (int c = 0; c < 8; c += 2) {
+            float p0 = ex2(fmaf(__uint_as_float(r[c0 + c]), sl, -mu));
+            float p1 = ex2(fmaf(__uint_as_float(r[c0 + c + 1]), sl, -mu));
             if (MASK) {
                 const int key = k0 + c0 + c;
                 if (key > row_pos || key < row_lo) p0 = 0.f;
@@ -95,13 +98,7 @@ __device__ __forceinline__ float row_exp(uint32_t s_addr, unsigned char* p_tile,
             sum += p0 + p1;
             packed[c >> 1] = pack2(p0, p1);
         }
-        unsigned char* prow = p_tile + (c0 >> 6) * kHalfBytes + row * 128;       // 32 keys = 4 chunks of 16 bytes
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-            const int chunk = ((c0 & 63) >> 3) + q4;
-            *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) =
-                make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-        }
+        *reinterpret_cast<uint4*>(prow + (((c0 >> 3) ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
     return sum;
 }
@@ -129,6 +126,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         p_full, p_empty, o_full[2], o_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int failed;
+    __shared__ volatile float xchg[2][2][kRows];   // [tile parity][column half][row]: partial row maxima; sums at the end
+    __shared__ volatile int xflag[2][2][kRows];    // tile number + 1 for which xchg holds a value
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int4 td = a.tiles[gridDim.x - 1 - blockIdx.x];           // longest tiles (latest queries) first
@@ -143,13 +142,14 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_init(&q_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128); mbar_init(&o_full[s], 1); mbar_init(&o_empty[s], 128);
+            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], kSoftmaxThreads); mbar_init(&o_full[s], 1); mbar_init(&o_empty[s], kSoftmaxThreads);
         }
-        mbar_init(&p_full, 128);
+        mbar_init(&p_full, kSoftmaxThreads);
         mbar_init(&p_empty, 1);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    for (int i = threadIdx.x; i < 2 * 2 * kRows; i += kThreads) (&xflag[0][0][0])[i] = 0;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
@@ -238,64 +238,85 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         if (ok) issue_pv(n_tiles - 1);
     } else if (warp >= 2) {
-        // ---- softmax, accumulation, output: one thread per query row ------------------------------
-        const int quarter = warp & 3;
+        // ---- softmax, accumulation, output: two threads per query row, 64 columns each --------------
+        const int quarter = warp & 3;                  // TMEM lanes [32 * quarter, +32) are readable by this warp
+        const int half = (warp - 2) >> 2;              // which 64 keys of a tile / which 64 output dims
         const int row = quarter * 32 + lane;
-        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16) + half * kCols;
         const int row_pos = pos0 + row;
         const int row_lo = a.window > 0 ? row_pos - a.window + 1 : 0;
-        float acc[kDim];
+        unsigned char* p_half = p_tile + half * kHalfBytes;
+        float acc[kCols];
 #pragma unroll
-        for (int d = 0; d < kDim; ++d) acc[d] = 0.f;
+        for (int d = 0; d < kCols; ++d) acc[d] = 0.f;
         float m = -INFINITY, l = 0.f, corr_prev = 1.f;
         bool ok = true;
-        auto fold = [&](int i, float corr) {          // acc = acc * corr + O_tile(i)
+        // The two threads of a row hand each other a value through shared memory: write it, publish the tile
+        // number, wait (bounded) for the partner's.  No block-wide barrier, so a thread that gave up cannot
+        // leave its partner stuck.
+        auto exchange = [&](int buf, int stamp, float mine, float& theirs) {
+            xchg[buf][half][row] = mine;
+            __threadfence_block();
+            xflag[buf][half][row] = stamp;
+            for (uint32_t i = 0; i < kSpinLimit; ++i) {
+                if (xflag[buf][half ^ 1][row] == stamp) {
+                    __threadfence_block();
+                    theirs = xchg[buf][half ^ 1][row];
+                    return true;
+                }
+            }
+            return false;
+        };
+        auto fold = [&](int i, float corr) {          // acc = acc * corr + O_tile(i), this thread's 64 dims
             const int s = i & 1;
             if (!mbar_wait(&o_full[s], (i >> 1) & 1)) { attn_give_up(5); failed = 1; return false; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t r[kCols];
+            load_cols(lane_addr + 256 + s * 128, r);
 #pragma unroll
-            for (int c0 = 0; c0 < kDim; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(lane_addr + 256 + s * 128 + c0, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int c = 0; c < 32; ++c) acc[c0 + c] = fmaf(acc[c0 + c], corr, __uint_as_float(r[c]));
-            }
+            for (int c = 0; c < kCols; ++c) acc[c] = fmaf(acc[c], corr, __uint_as_float(r[c]));
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&o_empty[s]);
             return true;
         };
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            const int s = j & 1, k0 = k_begin + j * kKeys;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j & 1, k0 = k_begin + j * kKeys + half * kCols;
             if (!mbar_wait(&s_full[s], (j >> 1) & 1)) { attn_give_up(6); failed = 1; ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const bool need_mask = (k0 + kKeys - 1 > pos0) || (a.window > 0 && k0 < pos_last - a.window + 1);
-            // pass 1: the row maximum (a row whose keys are all hidden keeps -inf; then mu = 0 and P = 0)
+            const int t0 = k_begin + j * kKeys;
+            const bool need_mask = (t0 + kKeys - 1 > pos0) || (a.window > 0 && t0 < pos_last - a.window + 1);
             const uint32_t s_addr = lane_addr + s * 128;
-            const float mx = need_mask ? row_max<true>(s_addr, k0, row_pos, row_lo) : row_max<false>(s_addr, k0, row_pos, row_lo);
+            uint32_t sc[kCols];
+            load_cols(s_addr, sc);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&s_empty[s]);                                    // S of this buffer is in registers now
+            float mx = need_mask ? row_max<true>(sc, k0, row_pos, row_lo) : row_max<false>(sc, k0, row_pos, row_lo);
+            float other;
+            if (!exchange(s, j + 1, mx, other)) { attn_give_up(8); failed = 1; ok = false; break; }
+            mx = fmaxf(mx, other);
             const float m_new = fmaxf(m, mx * a.sl);
-            const float mu = m_new == -INFINITY ? 0.f : m_new;
+            const float mu = m_new == -INFINITY ? 0.f : m_new;      // a row with no visible key yet
             const float corr = ex2(m - mu);
             m = m_new;
             // the P tile is free once P V of the previous tile has read it
             if (j >= 1 && !mbar_wait(&p_empty, (j - 1) & 1)) { attn_give_up(7); failed = 1; ok = false; break; }
-            // pass 2: P = 2^(S * sl - m), row sum, bf16 into the swizzled tile
-            const float sum = need_mask ? row_exp<true>(s_addr, p_tile, row, a.sl, mu, k0, row_pos, row_lo)
-                                        : row_exp<false>(s_addr, p_tile, row, a.sl, mu, k0, row_pos, row_lo);
+            const float sum = need_mask ? row_exp<true>(sc, p_half, row, a.sl, mu, k0, row_pos, row_lo)
+                                        : row_exp<false>(sc, p_half, row, a.sl, mu, k0, row_pos, row_lo);
             l = l * corr + sum;
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&s_empty[s]);                                    // S of this buffer has been read
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P must be visible to the tensor core
             mbar_arrive(&p_full);
-            if (j >= 1) ok = fold(j - 1, corr_prev);
+            if (j >= 1 && !fold(j - 1, corr_prev)) { ok = false; break; }
             corr_prev = corr;
         }
         if (ok) ok = fold(n_tiles - 1, corr_prev);
-        if (ok && row < rows) {
-            const float inv = 1.0f / l;
-            bf16* dst = a.out + (size_t)(tok0 + row) * a.out_stride + (size_t)h * kDim;
+        // the row sum is the two halves' sums (both are relative to the same running maximum)
+        float l_other = 0.f;
+        if (ok && !exchange(0, n_tiles + 1, l, l_other)) { attn_give_up(9); failed = 1; ok = false; }
+        if (ok && !failed && row < rows) {
+            const float inv = 1.0f / (l + l_other);
+            bf16* dst = a.out + (size_t)(tok0 + row) * a.out_stride + (size_t)h * kDim + half * kCols;
 #pragma unroll
-            for (int d = 0; d < kDim; d += 8) {
+            for (int d = 0; d < kCols; d += 8) {
                 *reinterpret_cast<uint4*>(dst + d) =
                     make_uint4(pack2(acc[d] * inv, acc[d + 1] * inv), pack2(acc[d + 2] * inv, acc[d + 3] * inv),
                                pack2(acc[d + 4] * inv, acc[d + 5] * inv), pack2(acc[d + 6] * inv, acc[d + 7] * inv));
