@@ -91,9 +91,9 @@ class ModelRunner:
         k = getattr(self.model, "k", None)
         return (self.workspace.generation, getattr(k, "scratch_generation", 0), self._meta.data_ptr())
 
-    def _forward_graphed(self, key, ctx):
-        """Runs a decode-shaped step: eagerly the first time its shape is seen (which also
-        brings every scratch buffer to size), captured into a CUDA graph the second time,
+    def _forward_graphed(self, key, ctx, eager_runs: int = 1):
+        """Runs a step whose shape is `key`: eagerly the first `eager_runs` times that shape is seen
+        (which also brings every scratch buffer to size), captured into a CUDA graph the next time,
         replayed from then on.  The index arrays were copied to their fixed places before."""
         rec = self._graphs.get(key)
         if rec is not None and rec["generation"] == self._generation():
@@ -103,7 +103,9 @@ class ModelRunner:
             if k is not None:
                 k.launches += rec["launches"]
             return rec["logits"]
-        if self._graph_seen.get(key, 0) < 1:
+        if self._graph_seen.get(key, 0) < eager_runs:
+            if len(self._graph_seen) > 4096:
+                self._graph_seen.clear()
             self._graph_seen[key] = self._graph_seen.get(key, 0) + 1
             return self.model.forward(ctx)
         if len(self._graphs) >= 64:
@@ -160,17 +162,19 @@ class ModelRunner:
         groups = cache.paged
         rows = {g: [self._table_row(g, e.request) for e in entries] for g in groups}
         widths = {g: max(1, max(r.shape[0] for r in rows[g])) for g in groups}
-        # A step of single tokens that all want logits has the same shape every time: it can be
-        # replayed from a captured graph if the index arrays keep their places, so the block
-        # tables are padded to a power of two of pages.
-        graphable = self.use_graphs and T == B and N == B and all(e.want == [0] for e in entries)
+        # A step whose shape (tokens per request, wanted rows, table width) has been seen before can be
+        # replayed from a captured graph if the index arrays keep their places, so the block tables are
+        # padded to a power of two of pages.  Decode steps repeat at once; prompt portions of the same
+        # length (a chunked prefill under a token budget) repeat too.
+        graphable = self.use_graphs
+        decode_shaped = T == B and N == B
         if graphable:
             widths = {g: max(16, 1 << (w - 1).bit_length()) for g, w in widths.items()}
         plan = AttentionPlan(qlens, seqlens, self.device, items=False, tiles=False)
-        if graphable:
+        if graphable and plan.n_items:
             # the split choice of decode attention is frozen into a graph: fix it by an upper bound of
             # the contexts, in steps of 512 tokens, and capture anew when the batch outgrows the bound
-            plan.context_bound = -(-max(seqlens) // 512) * 512
+            plan.context_bound = (max(plan.decode_pos) + 512) // 512 * 512
 
         # layout of the one int32 buffer
         layout, off = {}, 0
@@ -257,7 +261,8 @@ class ModelRunner:
                           workspace=self.workspace, requests=[e.request for e in entries],
                           query_lens=qlens, starts=starts, slots_host=slots_b)
         if graphable:
-            logits = self._forward_graphed((B, tuple(sorted(widths.items())), plan.context_bound), ctx)
+            key = (tuple(qlens), tuple(len(e.want) for e in entries), tuple(sorted(widths.items())), plan.context_bound)
+            logits = self._forward_graphed(key, ctx, eager_runs=1 if decode_shaped else 2)
         else:
             logits = self.model.forward(ctx)
         for e, end in zip(entries, seqlens):
