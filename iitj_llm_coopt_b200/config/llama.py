@@ -108,9 +108,6 @@ class LlamaConfig:
         if self.head_dim % 16 or self.head_dim > 256:
             raise ConfigError(f"head_dim {self.head_dim} is not supported: the attention kernels take "
                               f"multiples of 16 up to 256")
-        if self.hidden_size % 8 or self.intermediate_size % 8:
-            raise ConfigError("hidden_size and intermediate_size must be multiples of 8 "
-                              "(16-byte rows for the matrix kernels)")
         if not self.rms_norm_eps > 0:
             raise ConfigError(f"rms_norm_eps must be positive, got {self.rms_norm_eps}")
         rs = self.rope_scaling

@@ -12,10 +12,21 @@ namespace {
 
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4x4 outputs each
 
+// Four consecutive k of one row; `vec` = the row starts are 16-byte aligned and K % 4 == 0.
+__device__ __forceinline__ float4 load_k4(const float* row, int k, int K, bool vec) {
+    if (vec) return *reinterpret_cast<const float4*>(row + k);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (k < K) v.x = row[k];
+    if (k + 1 < K) v.y = row[k + 1];
+    if (k + 2 < K) v.z = row[k + 2];
+    if (k + 3 < K) v.w = row[k + 3];
+    return v;
+}
+
 template <bool SWIGLU>
 __global__ void __launch_bounds__(256)
 sgemm_tn_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
-                int M, int N, int K, int lda, int ldw, int ldc) {
+                int M, int N, int K, int lda, int ldw, int ldc, bool vec) {
     pdl_trigger();
     pdl_wait();
     __shared__ float As[BK][BM + 4];
@@ -37,14 +48,14 @@ sgemm_tn_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
         {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             const int r = m0 + lrow, k = k0 + lk;
-            if (r < M && k < K) v = *reinterpret_cast<const float4*>(A + (size_t)r * lda + k);
+            if (r < M && k < K) v = load_k4(A + (size_t)r * lda, k, K, vec);
             As[lk][lrow] = v.x; As[lk + 1][lrow] = v.y; As[lk + 2][lrow] = v.z; As[lk + 3][lrow] = v.w;
         }
 #pragma unroll
         for (int s = 0; s < (SWIGLU ? 2 : 1); ++s) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             const int r = n0 + lrow, k = k0 + lk;
-            if (r < N && k < K) v = *reinterpret_cast<const float4*>(W + ((size_t)s * N + r) * ldw + k);
+            if (r < N && k < K) v = load_k4(W + ((size_t)s * N + r) * ldw, k, K, vec);
             Ws[s][lk][lrow] = v.x; Ws[s][lk + 1][lrow] = v.y; Ws[s][lk + 2][lrow] = v.z; Ws[s][lk + 3][lrow] = v.w;
         }
         __syncthreads();
@@ -88,13 +99,13 @@ sgemm_tn_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
 LLM_API int llm_gemm_f32(const float* A, const float* W, float* C, int M, int N, int K, int lda, int ldw,
                          int ldc, int swiglu, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
-    if (K % 4 || lda % 4 || ldw % 4) LLM_FAIL(-1, "gemm_f32: K %d and the row strides must be multiples of 4", K);
+    const bool vec = !(K % 4 || lda % 4 || ldw % 4) && !((uintptr_t)A & 15) && !((uintptr_t)W & 15);
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) LLM_FAIL(-1, "gemm_f32: M %d is too large", M);
     if (swiglu)
-        llm_launch(sgemm_tn_kernel<true>, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
+        llm_launch(sgemm_tn_kernel<true>, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc, vec);
     else
-        llm_launch(sgemm_tn_kernel<false>, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
+        llm_launch(sgemm_tn_kernel<false>, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc, vec);
     LLM_CHECK_LAUNCH("gemm_f32");
     return 0;
 }

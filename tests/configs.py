@@ -38,4 +38,14 @@ TINY_D = {
     "tie_word_embeddings": True, "max_position_embeddings": 2048, "eos_token_id": 3,
 }
 
-CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 5, 16), "D": (TINY_D, 6, 16)}  # config, seed, page size
+# Awkward sizes: a width and an inner size that are no multiple of 4 or 8, a prime vocabulary, plain multi-head
+# attention (no grouping), query width different from the model width, one layer.
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 100, "intermediate_size": 90, "num_hidden_layers": 1,
+    "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 16,
+    "vocab_size": 131, "rms_norm_eps": 2e-5, "rope_theta": 1000.0, "rope_scaling": None,
+    "tie_word_embeddings": True, "max_position_embeddings": 300, "eos_token_id": 7,
+}
+
+CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 5, 16), "D": (TINY_D, 6, 16), "E": (TINY_E, 7, 4)}  # config, seed, page size

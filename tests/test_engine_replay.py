@@ -12,12 +12,12 @@ from configs import CONFIGS
 from helpers import make_engine, rel_err, run_steps
 
 FP32_TOL, BF16_TOL = 1e-4, 2e-2
-LENGTHS = {"A": [5, 17, 33, 70, 129], "B": [1, 9, 40, 64, 130], "C": [3, 66, 150, 31], "D": [2, 130, 47, 80]}
+LENGTHS = {"A": [5, 17, 33, 70, 129], "B": [1, 9, 40, 64, 130], "C": [3, 66, 150, 31], "D": [2, 130, 47, 80], "E": [70, 3, 41]}
 
 GPU = pytest.mark.gpu
 CASES = [pytest.param("cpu", "float32", n, id=f"cpu-fp32-{n}") for n in "AB"] + \
         [pytest.param("cuda:0", dt, n, marks=GPU, id=f"gpu-{dt}-{n}")
-         for dt in ("float32", "bfloat16") for n in "ABCD"]
+         for dt in ("float32", "bfloat16") for n in "ABCDE"]
 
 
 def reference_rows(model_dir, reqs):

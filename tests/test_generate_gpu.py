@@ -31,7 +31,7 @@ def lively_dirs(tmp_path_factory):
     return out
 
 
-PROMPT_LENS = {"A": [5, 17, 33], "B": [1, 9, 40, 64, 130], "C": [3, 50, 90], "D": [2, 70]}
+PROMPT_LENS = {"A": [5, 17, 33], "B": [1, 9, 40, 64, 130], "C": [3, 50, 90], "D": [2, 70], "E": [11, 60]}
 
 
 def margins_ok(cfg, w, prompt, got, min_margin):
@@ -48,7 +48,7 @@ def margins_ok(cfg, w, prompt, got, min_margin):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_greedy_generation_through_the_entry_point(lively_dirs, dtype, name):
     cfg_d, seed, page = CONFIGS[name]
     cfg, w = plain.read_model_dir(lively_dirs[name], torch.float32)
