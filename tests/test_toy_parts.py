@@ -1,5 +1,6 @@
-"""A toy architecture defined here, in the test: a mixer with state of its own, a layer named
-twice in the run order, and a call that reads another call's cache.  It is registered,
+"""A toy architecture defined here, in the test: a mixer with state of its own, a feed-forward with
+routing, another position encoding, a layer named twice in the run order, and a call that reads
+another call's cache.  It is registered,
 built and stepped through the framework's registries alone; no file of the framework
 knows about it.  Stepping in portions must give what whole prompts give."""
 from dataclasses import dataclass
@@ -53,6 +54,55 @@ class RunningMeanMixer(Part):
         return self.k.linear(means.to(self.dtype), self.w, out)
 
 
+class Top1RoutedFeedForward(Part):
+    """A feed-forward with routing, defined in the test: a float32 router picks one of `experts` small
+    SwiGLU experts per token; y = p_top * expert(x).  Tokens are grouped by expert on the host."""
+
+    def __init__(self, spec, kernels, dtype):
+        self.spec, self.k, self.dtype = spec, kernels, dtype
+        self.router = self.gate_up = self.down = None
+
+    @classmethod
+    def parameters(cls, spec):
+        e = spec.experts
+        return {"router": ParamSpec((e, spec.width), kind="matrix"),
+                "gate_up": ParamSpec((e * 2 * spec.inner, spec.width)),
+                "down": ParamSpec((e * spec.width, spec.inner))}
+
+    def forward(self, ctx, x):
+        sp = self.spec
+        logits = x.float() @ self.router.float().t()                       # router logits in float32
+        probs = torch.softmax(logits, dim=-1)
+        top_p, top_e = probs.max(dim=-1)
+        out = ctx.buffer("toy.ffn", (x.shape[0], sp.width), self.dtype)
+        out.zero_()
+        for e in range(sp.experts):
+            idx = (top_e == e).nonzero().squeeze(-1)
+            if idx.numel() == 0:
+                continue
+            xe = x[idx].contiguous()
+            act = torch.empty(idx.numel(), sp.inner, dtype=self.dtype, device=x.device)
+            self.k.linear(xe, self.gate_up[e * 2 * sp.inner:(e + 1) * 2 * sp.inner], act, swiglu=True)
+            ye = torch.empty(idx.numel(), sp.width, dtype=self.dtype, device=x.device)
+            self.k.linear(act, self.down[e * sp.width:(e + 1) * sp.width], ye)
+            out[idx] = (ye.float() * top_p[idx].unsqueeze(1)).to(self.dtype)
+        return out
+
+
+class LinearFrequencyRotary(Part):
+    """Another position encoding, defined in the test: rotation with frequencies that fall off linearly
+    instead of geometrically; it reuses the engine's rotate-and-store kernel with its own table."""
+
+    def __init__(self, spec, kernels, dtype, device="cuda"):
+        self.spec, self.k, self.head_dim, self.rotary_dim = spec, kernels, spec.head_dim, spec.rotary_dim
+        half = spec.rotary_dim // 2
+        self.inv_freq = (1.0 - torch.arange(half, dtype=torch.float32) / half).div(spec.theta).to(device)
+
+    def encode_and_store(self, ctx, qkv, cache_view, slots, heads, kv_heads):
+        self.k.rope_store(qkv, ctx.positions, self.inv_freq, slots, cache_view, heads, kv_heads, self.head_dim,
+                          self.rotary_dim)
+
+
 @dataclass
 class ToyConfig:
     width: int = 64
@@ -72,11 +122,16 @@ class ToyConfig:
         pos = PositionSpec("rope", head_dim=16, rotary_dim=8, theta=10000.0)       # partial rotation
         attn = LayerSpec("prenorm", MixerSpec("attention", self.width, heads=4, kv_heads=2, head_dim=16, position=pos),
                          ff, norm, norm)
-        toy = LayerSpec("prenorm", MixerSpec("running_mean", self.width), ff, norm, norm)
+        routed = FeedForwardSpec("top1_routed", self.width, 48, experts=3, experts_per_token=1)
+        pos2 = PositionSpec("linear_rotary", head_dim=16, rotary_dim=16, theta=50.0)
+        toy = LayerSpec("prenorm", MixerSpec("running_mean", self.width), routed, norm, norm)
+        attn2 = LayerSpec("prenorm", MixerSpec("attention", self.width, heads=2, kv_heads=1, head_dim=16, position=pos2),
+                          ff, norm, norm)
         order = (LayerCall(layer=0, cache=0), LayerCall(layer=1, cache=1),
                  LayerCall(layer=0, cache=2),                   # layer 0 a second time, with a cache entry of its own
-                 LayerCall(layer=0, cache=0, write=False))      # and a third time, reading the first call's keys
-        return ModelSpec(width=self.width, vocab=self.vocab, layers=(attn, toy), order=order, final_norm=norm,
+                 LayerCall(layer=0, cache=0, write=False),      # and a third time, reading the first call's keys
+                 LayerCall(layer=2, cache=3))                   # other head counts, another position encoding
+        return ModelSpec(width=self.width, vocab=self.vocab, layers=(attn, toy, attn2), order=order, final_norm=norm,
                          tie_embeddings=True, max_position=4096)
 
 
@@ -91,9 +146,13 @@ class ToyArch(Architecture):
 @pytest.fixture
 def toy_registered():
     parts.register_mixer("running_mean", RunningMeanMixer)
+    parts.register_feed_forward("top1_routed", Top1RoutedFeedForward)
+    parts.register_position_encoding("linear_rotary", LinearFrequencyRotary)
     register_architecture(ToyArch())
     yield
     parts.MIXERS.pop("running_mean", None)
+    parts.FEED_FORWARDS.pop("top1_routed", None)
+    parts.POSITION_ENCODINGS.pop("linear_rotary", None)
     ARCHITECTURES.pop("ToyStateLM", None)
 
 
@@ -112,9 +171,9 @@ def _engine(device, dtype):
 def test_toy_mixer_with_state_steps_like_whole_prompts(toy_registered, device, dtype):
     eng = _engine(device, dtype)
     groups = eng.cache.groups
-    assert len(groups) == 2 and len(eng.cache.paged) == 1             # keys/values for calls 0 and 2, state for call 1
+    assert len(groups) == 3 and len(eng.cache.paged) == 2             # two attention geometries, one state group
     assert groups[eng.cache.entry_group[1][0]].storage.shape == (1, 3, 65)
-    assert eng.cache.entry_group[0][0] == eng.cache.entry_group[2][0]
+    assert eng.cache.entry_group[0][0] == eng.cache.entry_group[2][0] != eng.cache.entry_group[3][0]
     reqs = cases.requests_for(200, [50, 23, 70, 9], seed=4)
     whole = run_steps(eng, cases.whole(reqs))
     tol = 1e-4 if dtype == "float32" else 3e-2
