@@ -52,7 +52,7 @@ struct GemmArgs {
 };
 
 template <int N_TOK, bool SWIGLU>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs a) {
     constexpr int kABytes = kFeatTile * kBlockK * 2;               // 16 KiB per weight tile
     constexpr int kBBytes = N_TOK * kBlockK * 2;
@@ -272,16 +272,19 @@ namespace {
 template <int N_TOK, bool SWIGLU>
 int launch_tile(const CUtensorMap& mw, const CUtensorMap& mx, GemmArgs a, dim3 grid, cudaStream_t stream) {
     constexpr int stage_bytes = (SWIGLU ? 2 : 1) * kFeatTile * kBlockK * 2 + N_TOK * kBlockK * 2;
-    int stages = (200 * 1024) / stage_bytes;
+    // shared memory for the ring: 200 KiB (one CTA per SM), or about half of it when the caller wants two
+    // CTAs per SM (more CTAs in flight for products with few tiles)
+    int stages = ((a.stages > 0 ? a.stages : 200) * 1024) / stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) stages = 2;
     a.stages = stages;
     const size_t smem = (size_t)stages * stage_bytes + 1024;
     auto kern = gemm_tn_kernel<N_TOK, SWIGLU>;
-    static bool configured = false;            // one flag per instantiation
-    if (!configured) {
+    static size_t configured = 0;              // largest size set so far, one per instantiation
+    if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LLM_FAIL(-2, "gemm_bf16: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        configured = true;
+        configured = smem;
     }
     llm_launch(kern, grid, kThreads, smem, stream, mw, mx, a);
     LLM_CHECK_LAUNCH("gemm_bf16");
@@ -298,8 +301,9 @@ LLM_API int llm_gemm_bf16_token_tile(int tokens) {
 // out = x . w^T.   x [tokens, K] bf16, w [n (or 2n with swiglu), K] bf16.
 // out_f32 == 0: out is bf16 [tokens, ldc]; out_f32 != 0: float32 [tokens, ldc].
 // splits > 1 needs `scratch` with splits * tokens * (swiglu ? 2n : n) floats; the reduction runs right after.
+// smem_kb: shared memory of one CTA's ring in KiB (0 = 200: one CTA per SM; about 100 lets two CTAs share an SM).
 LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, int tokens, int n, int K, int ldc,
-                          int swiglu, int splits, float* scratch, cudaStream_t stream) {
+                          int swiglu, int splits, float* scratch, int smem_kb, cudaStream_t stream) {
     if (tokens == 0 || n == 0) return 0;
     if (K % 8) LLM_FAIL(-1, "gemm_bf16: K %d must be a multiple of 8", K);
     if (swiglu && out_f32) LLM_FAIL(-1, "gemm_bf16: the SwiGLU variant writes bfloat16");
@@ -322,7 +326,7 @@ LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, 
     a.ldc = splits > 1 ? w_rows : ldc;
     a.k_blocks = k_blocks;
     a.splits = splits;
-    a.stages = 0;
+    a.stages = smem_kb;          // launch_tile turns the budget into a stage count
     dim3 grid((n + kFeatTile - 1) / kFeatTile, splits, (tokens + tile - 1) / tile);
     if (grid.y > 65535 || grid.z > 65535) LLM_FAIL(-1, "gemm_bf16: grid out of range");
     int rc;

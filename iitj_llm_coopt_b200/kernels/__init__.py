@@ -57,7 +57,7 @@ _SIGNATURES = {
                      _c_void_p],
     "llm_gemm_bf16_token_tile": [_c_int],
     "llm_gemm_bf16": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
-                      _c_void_p],
+                      _c_int, _c_void_p],
     "llm_gemm_bf16_status": [],
     "llm_sample_scratch_floats": [_c_int, _c_int],
     "llm_sample": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
@@ -169,10 +169,9 @@ class Kernels:
             fn.restype = _c_int
         self.launches = 0  # kernels of this library launched so far (the bench reports it)
         # IITJ_GEMM_BACKEND=cublas|tcgen05 forces one matrix-product path, IITJ_GEMM_SMALL_TOKENS moves the
-        # boundary, IITJ_PDL=0 switches programmatic dependent launch off (all three are for measurements)
+        # SwiGLU boundary, IITJ_PDL=0 switches programmatic dependent launch off (all for measurements)
         self.gemm_backend = os.environ.get("IITJ_GEMM_BACKEND", "auto")
         self.gemm_small_tokens = int(os.environ.get("IITJ_GEMM_SMALL_TOKENS", "128"))
-        self.gemm_all_small = os.environ.get("IITJ_GEMM_ALL_SMALL", "0") == "1"
         self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
         if os.environ.get("IITJ_PDL", "1") == "0":
             self.lib.llm_set_pdl(0)
@@ -372,7 +371,8 @@ class Kernels:
         # bfloat16: this library's tcgen05 kernel where it is the faster one, else cuBLAS through torch
         tokens, k = x.shape
         if self.gemm_policy(tokens, n, k, swiglu) == "tcgen05":
-            return self.gemm_tcgen05(x, weight, out, swiglu, self.gemm_splits(tokens, n, k, swiglu))
+            splits, smem_kb = self.gemm_plan(tokens, n, k, swiglu)
+            return self.gemm_tcgen05(x, weight, out, swiglu, splits, smem_kb)
         if swiglu:
             gu = torch.mm(x, weight.t())
             return self.silu_mul(gu, out)
@@ -382,7 +382,7 @@ class Kernels:
             torch.mm(x, weight.t(), out=out)
         return out
 
-    def gemm_tcgen05(self, x, weight, out, swiglu: bool = False, splits: int = 1):
+    def gemm_tcgen05(self, x, weight, out, swiglu: bool = False, splits: int = 1, smem_kb: int = 0):
         """out = x . weight^T on this library's tcgen05 kernel (bfloat16 in, bfloat16 or float32 out)."""
         _check(x, "gemm.x", torch.bfloat16, 2)
         _check(weight, "gemm.weight", torch.bfloat16, 2)
@@ -395,48 +395,54 @@ class Kernels:
         if splits > 1:
             scratch = self._scratch("gemm.partials", splits * tokens * weight.shape[0], x.device)
         self._call("llm_gemm_bf16", _ptr(x), _ptr(weight), _ptr(out), 1 if out.dtype == torch.float32 else 0, tokens,
-                   n, k, out.shape[1], 1 if swiglu else 0, splits, _ptr(scratch), self._stream())
+                   n, k, out.shape[1], 1 if swiglu else 0, splits, _ptr(scratch), int(smem_kb), self._stream())
         if splits > 1:
             self.launches += 1
         return out
 
     # Which kernel multiplies: "tcgen05" (this library) or "cublas".  `gemm_backend` may force one.
     def gemm_policy(self, tokens, n, k, swiglu) -> str:
-        """Measured on B200 at the 8B shapes: the fused SwiGLU product of this library matches
-        cuBLAS + a separate SiLU kernel up to 128 tokens and saves a launch; the plain products
-        are left to cuBLAS."""
+        """Measured on B200 at the 8B shapes (in CUDA graphs, cold weights): with two CTAs per SM and up to
+        eight k-splits this library's product matches or beats cuBLAS up to 64 tokens for every shape of the
+        model (and its weight prefetch overlaps the kernel before it); the fused SwiGLU product holds up to
+        128 tokens; above that cuBLAS is faster."""
         if k % 8:
             return "cublas"
         if self.gemm_backend != "auto":
             return self.gemm_backend
-        if tokens <= self.gemm_small_tokens and (swiglu or self.gemm_all_small):
+        if tokens <= (self.gemm_small_tokens if swiglu else min(64, self.gemm_small_tokens)):
             return "tcgen05"
         return "cublas"
 
-    def gemm_splits(self, tokens, n, k, swiglu) -> int:
-        """Split the k range when the product has too few CTAs to fill the GPU: candidates are
-        scored by waves * (k-blocks per CTA + a fixed per-CTA cost), one CTA per SM."""
-        tile = self.lib.llm_gemm_bf16_token_tile(tokens)
-        ctas = -(-n // 128) * -(-tokens // tile)
-        k_blocks = -(-k // 64)
-        if tokens > 256 or ctas >= self.sm_count or n % 4:
-            return 1
-        best = (None, 1)
-        for s in range(1, min(16, max(1, k_blocks // 4)) + 1):
-            per = -(-k_blocks // s)
-            waves = -(-ctas * s // self.sm_count)
-            cost = waves * (per + 8)
-            if best[0] is None or cost < best[0]:
-                best = (cost, s)
-        return best[1]
+    def gemm_plan(self, tokens, n, k, swiglu) -> tuple:
+        """(k-splits, shared memory per CTA in KiB) for the tcgen05 product.
 
-    def attention_status(self) -> int:
-        """0, or a code if the tcgen05 attention kernel gave up waiting on a barrier since the last call."""
-        return self.lib.llm_attention_tcgen05_status()
+        Products with many feature tiles (the LM head) run unsplit with three CTAs per SM.  Products with
+        few tiles are split along k until about two CTAs per SM are in flight (at most eight splits, at
+        least four k-blocks each).  The SwiGLU product beyond a handful of tokens runs unsplit with the
+        whole shared memory as its ring."""
+        tile = self.lib.llm_gemm_bf16_token_tile(tokens)
+        tiles = -(-n // 128) * -(-tokens // tile)
+        k_blocks = -(-k // 64)
+        if tokens > 256 or n % 4:
+            return 1, 0
+        if tiles >= 2 * self.sm_count:
+            return 1, 66
+        if swiglu and tokens > 8:
+            return 1, 0
+        splits = max(1, min(8, round(2 * self.sm_count / tiles), k_blocks // 4))
+        return splits, 100
+
+    def gemm_splits(self, tokens, n, k, swiglu) -> int:
+        return self.gemm_plan(tokens, n, k, swiglu)[0]
 
     def gemm_status(self) -> int:
         """0, or a code if a tcgen05 GEMM gave up waiting on one of its barriers since the last call."""
         return self.lib.llm_gemm_bf16_status()
+
+    def attention_status(self) -> int:
+        """0, or a code if the tcgen05 attention kernel gave up waiting on a barrier since the last call."""
+        return self.lib.llm_attention_tcgen05_status()
 
     # ---- sampling --------------------------------------------------------------------
     def sample(self, logits, temperature, keys, out):
