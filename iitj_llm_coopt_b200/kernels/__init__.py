@@ -403,14 +403,14 @@ class Kernels:
     # Which kernel multiplies: "tcgen05" (this library) or "cublas".  `gemm_backend` may force one.
     def gemm_policy(self, tokens, n, k, swiglu) -> str:
         """Measured on B200 at the 8B shapes (in CUDA graphs, cold weights): with two CTAs per SM and up to
-        eight k-splits this library's product matches or beats cuBLAS up to 64 tokens for every shape of the
+        eight k-splits this library's product matches or beats cuBLAS up to 32 tokens for every shape of the
         model (and its weight prefetch overlaps the kernel before it); the fused SwiGLU product holds up to
         128 tokens; above that cuBLAS is faster."""
         if k % 8:
             return "cublas"
         if self.gemm_backend != "auto":
             return self.gemm_backend
-        if tokens <= (self.gemm_small_tokens if swiglu else min(64, self.gemm_small_tokens)):
+        if tokens <= (self.gemm_small_tokens if swiglu else min(32, self.gemm_small_tokens)):
             return "tcgen05"
         return "cublas"
 
