@@ -187,3 +187,29 @@ def test_wide_layer_at_the_benchmark_widths(tmp_path):
                 got = torch.stack([rows[(rid, i)] for i in range(len(toks))])
                 assert rel_err(got, ref[rid]) <= tol, (dtype, rid)
         del eng
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("C", "bfloat16"), ("D", "bfloat16")])
+def test_many_random_requests_under_pressure(lively_dirs, name, dtype):
+    """Forty requests of random lengths through a small pool and a small token budget: portions, mixed steps,
+    captured decode steps of changing batch size, preemptions.  Every output against the plain implementation."""
+    import random
+    cfg_d, seed, page = CONFIGS[name]
+    rng = random.Random(1234 + seed)
+    prompts = [[rng.randrange(cfg_d["vocab_size"]) for _ in range(rng.choice([1, 2, 3, 7, 16, 17, 40, 90, 150]))]
+               for _ in range(40)]
+    params = [SamplingParams(max_tokens=rng.randint(1, 30), ignore_eos=True) for _ in prompts]
+    pages = -(-(150 + 30) // page) * 2            # room for two of the longest requests; six may run
+    llm = LLM(lively_dirs[name], dtype=dtype, page_size=page, num_pages=pages, max_num_seqs=6, max_num_batched_tokens=48)
+    outs = llm.generate(prompts, params)
+    cfg, w = plain.read_model_dir(lively_dirs[name], torch.float32)
+    for p, sp, o in zip(prompts, params, outs):
+        assert len(o.token_ids) == sp.max_tokens and o.finish_reason == "length"
+        if dtype == "float32":
+            assert o.token_ids == plain.greedy_generate(cfg, w, p, sp.max_tokens)
+        else:
+            assert margins_ok(cfg, w, p, o.token_ids, 0.05)
+    assert llm.engine.counters["num_preemptions_total"] >= 1
+    assert llm.engine.runner.graph_replays > 0
+    llm.engine.cache.check()
+    assert llm.engine.cache.num_free == pages
