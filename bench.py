@@ -141,7 +141,7 @@ def main() -> int:
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference has no setup.py or pyproject.toml: 'pip install --no-index ... /root/reference' "
+                          "the reference has no setup.py or pyproject.toml: the offline 'pip install --no-index' of its tree "
                           "fails with 'not installable'; its engine also needs vLLM's CUDA ops and a downloaded checkpoint"}))
         return 0
     if args.gpus != 1:

@@ -1,6 +1,6 @@
 """Makes tests/golden/*.safetensors: logits of the reference's own model code on CPU.
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 The reference's engine/model.py imports vllm's CUDA ops at import time, which cannot load
 without a GPU driver, so three modules are replaced by stand-ins before the import:
@@ -52,7 +52,9 @@ def paged_attention_stand_in(q, k, v, cu_seqlens_q, max_seqlen_q, seqused_k, max
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_DIR", "/root/reference")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_DIR")
+    if not ref or not os.path.isdir(ref):
+        sys.exit("give the reference's checkout as the first argument or in $REFERENCE_DIR")
     fa = types.ModuleType("vllm.vllm_flash_attn")
     fa.flash_attn_varlen_func = paged_attention_stand_in
     ops = types.ModuleType("vllm._custom_ops")
