@@ -35,6 +35,7 @@ class EngineConfig:
     watermark: float = 0.01             # fraction of pages kept free when admitting
     seed: int = 0
     cuda_graphs: bool = True            # replay decode-only steps from captured graphs
+    lookahead: bool = True              # launch the next decode step before the host has read this one's tokens
     device: str = "cuda:0"
 
     def __post_init__(self):

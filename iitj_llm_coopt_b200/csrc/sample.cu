@@ -129,6 +129,22 @@ sample_pick_kernel(const float* __restrict__ part_v, const int* __restrict__ par
 
 }  // namespace
 
+// dst[i] = src[rows[i]] where rows[i] >= 0: feeds the ids sampled by the previous step into this step's token
+// slots on the device, so the host can launch a step before it has read the previous step's tokens.
+__global__ void gather_tokens_kernel(int* __restrict__ dst, const int* __restrict__ src, const int* __restrict__ rows, int n) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && rows[i] >= 0) dst[i] = src[rows[i]];
+}
+
+LLM_API int llm_gather_tokens(int* dst, const int* src, const int* rows, int n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    llm_launch(gather_tokens_kernel, (n + 255) / 256, 256, 0, stream, dst, src, rows, n);
+    LLM_CHECK_LAUNCH("gather_tokens");
+    return 0;
+}
+
 // Number of floats of scratch llm_sample wants for `rows` rows of `vocab` logits (0: none needed).
 LLM_API int llm_sample_scratch_floats(int rows, int vocab) {
     const int chunks = (vocab + kChunk - 1) / kChunk;

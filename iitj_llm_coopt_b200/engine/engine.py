@@ -24,8 +24,11 @@ COUNTERS = ("prompt_tokens_total", "generation_tokens_total", "num_preemptions_t
 
 
 class Engine:
-    def __init__(self, runner, cache, sampler, policy=None, max_model_len: int = 32768, eos_ids=()):
+    def __init__(self, runner, cache, sampler, policy=None, max_model_len: int = 32768, eos_ids=(),
+                 lookahead: bool = False):
         self.runner, self.cache, self.sampler = runner, cache, sampler
+        self.lookahead = bool(lookahead) and hasattr(sampler, "launch")
+        self._inflight = None
         self.policy = policy or StaticPolicy()
         self.eos_ids = set(eos_ids)
         self.max_model_len = max_model_len
@@ -93,7 +96,22 @@ class Engine:
         return kept
 
     # ---- one step ------------------------------------------------------------------------
+    # A step is launched (scheduler, step function, sampling kernel, copy of the ids to the host) and
+    # collected (ids read, tokens appended, stop rules, finish and free).  Without lookahead `step()` does
+    # both.  With lookahead a launched step stays in flight, and the next `step()` first launches its
+    # successor -- when that needs no scheduling decision: nobody waits, every running sequence got a token
+    # in the step in flight, the pages fit -- with the input tokens taken from the sampled ids on the
+    # device; only then does it collect the step in flight.  The GPU so never waits for the host.  Stops by
+    # max_tokens and max_model_len are known beforehand; a stop by EOS is seen one step late, and the token
+    # the successor computed for that sequence is dropped.
     def step(self) -> bool:
+        prev = self._inflight
+        if prev is not None:
+            nxt = self._launch_follow(prev) if self._can_follow(prev) else None
+            self._inflight = None
+            self._collect(prev)
+            self._inflight = nxt
+            return True
         try:
             plan = self.scheduler.schedule()
         except OutOfPages as e:
@@ -106,6 +124,14 @@ class Engine:
             return True
         if not plan:
             return False
+        rec = self._launch(plan)
+        if self.lookahead:
+            self._inflight = rec
+        else:
+            self._collect(rec)
+        return True
+
+    def _launch(self, plan) -> dict:
         t0 = time.perf_counter()
         entries, sampled = [], []         # sampled: sequences whose last fed token wants logits
         for s, end in plan.chunks:
@@ -117,18 +143,55 @@ class Engine:
         for s in plan.decodes:
             entries.append(StepEntry(s.seq_id, [s.tokens[-1]], [0]))
             sampled.append(s)
-        n_tokens = sum(len(e.tokens) for e in entries)
         logits = self.runner.step(entries)
-        new_tokens = []
-        if sampled:
-            rows = [(s.temperature, s.seq_id if s.seed is None else s.seed, s.num_generated) for s in sampled]
-            new_tokens = self.sampler.sample(logits, rows)
-
         for s, end in plan.chunks:
             self.counters["prompt_tokens_total"] += end - s.num_computed
             s.num_computed = end
+        return self._sample(logits, sampled, [s.num_generated for s in sampled], sum(len(e.tokens) for e in entries), t0)
+
+    def _sample(self, logits, sampled, token_index, n_tokens, t0) -> dict:
+        handle = None
+        if sampled:
+            rows = [(s.temperature, s.seq_id if s.seed is None else s.seed, i) for s, i in zip(sampled, token_index)]
+            if hasattr(self.sampler, "launch"):
+                handle = self.sampler.launch(logits, rows)
+            else:
+                handle = list(self.sampler.sample(logits, rows))
+        return {"sampled": sampled, "handle": handle, "n_tokens": n_tokens, "t0": t0}
+
+    def _ends_by_length(self, s, extra: int = 1) -> bool:
+        """True if the sequence stops for length once `extra` more tokens are appended."""
+        return s.num_generated + extra >= s.max_tokens or len(s.tokens) + extra >= self.max_model_len
+
+    def _can_follow(self, prev) -> bool:
+        if not self.lookahead or prev["handle"] is None or self.scheduler.waiting:
+            return False
+        got = {id(s) for s in prev["sampled"]}
+        return all(id(s) in got for s in self.scheduler.running)
+
+    def _launch_follow(self, prev):
+        """The step after `prev` for the sequences that go on decoding, fed from prev's ids on the device."""
+        t0 = time.perf_counter()
+        rows = [(i, s) for i, s in enumerate(prev["sampled"]) if not s.finished and not self._ends_by_length(s)]
+        if not rows:
+            return None
+        need = sum(self.cache.extra_pages_needed(s.seq_id, self.cache.num_tokens(s.seq_id) + 1) for _, s in rows)
+        if need > self.cache.num_free:
+            return None                   # pages are short: collect first, then the scheduler decides who gives way
+        entries = [StepEntry(s.seq_id, [0], [0], source_rows=[i]) for i, s in rows]
+        logits = self.runner.step(entries, prev_ids=prev["handle"].ids)
+        seqs = [s for _, s in rows]
+        return self._sample(logits, seqs, [s.num_generated + 1 for s in seqs], len(entries), t0)
+
+    def _collect(self, rec) -> None:
+        sampled, handle = rec["sampled"], rec["handle"]
+        new_tokens = []
+        if sampled:
+            new_tokens = self.sampler.fetch(handle) if hasattr(self.sampler, "fetch") else handle
         now = time.perf_counter()
         for s, tok in zip(sampled, new_tokens):
+            if s.finished:
+                continue                  # it ended at EOS one step ago; this token was computed in vain
             kept = self._append(s, [tok])
             s.num_computed = len(s.tokens) - 1      # everything but the newly sampled token is cached
             self.counters["generation_tokens_total"] += len(kept)
@@ -139,23 +202,21 @@ class Engine:
                 self._finish(s, s.finish_reason)
             if s.on_output:
                 s.on_output(s, kept, done)
-
         end_t = time.perf_counter()
         self.counters["steps_total"] += 1
-        self.counters["step_seconds_total"] += end_t - t0
+        self.counters["step_seconds_total"] += end_t - rec["t0"]
         self.gauges = {
             "num_requests_running": len(self.scheduler.running),
             "num_requests_waiting": len(self.scheduler.waiting),
             "kv_cache_usage_perc": self.cache.usage,
             "kv_capacity_tokens": self.kv_capacity_tokens,
-            "step_time_s": end_t - t0,
-            "batch_tokens": n_tokens,
+            "step_time_s": end_t - rec["t0"],
+            "batch_tokens": rec["n_tokens"],
             **self.policy.state(),
         }
-        return True
 
     def has_work(self) -> bool:
-        return bool(self.scheduler.running or self.scheduler.waiting)
+        return bool(self.scheduler.running or self.scheduler.waiting or self._inflight is not None)
 
     def run_until_done(self, max_steps: int | None = None) -> int:
         """The reference's worker loop (engine/worker.py:64-65) in-process."""

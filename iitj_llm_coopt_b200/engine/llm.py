@@ -94,7 +94,7 @@ def build_engine(model: str | None = None, engine_config: EngineConfig | None = 
     pol = policy or StaticPolicy(max_num_seqs=ec.max_num_seqs, max_batched_tokens=ec.max_num_batched_tokens,
                                  watermark=ec.watermark)
     eng = Engine(runner, cache, sampler, pol, max_model_len=min(ec.max_model_len, spec.max_position),
-                 eos_ids=spec.eos_token_ids)
+                 eos_ids=spec.eos_token_ids, lookahead=ec.lookahead and device.type == "cuda")
     eng.model_config, eng.model_spec, eng.engine_config = cfg, spec, ec
     return eng
 
@@ -112,11 +112,11 @@ class LLM:
                  page_size: int = 16, num_pages: int | None = None, kv_gb: float | None = None,
                  gpu_memory_utilization: float = 0.9, max_model_len: int = 32768, max_num_seqs: int = 256,
                  max_num_batched_tokens: int = 2048, seed: int = 0, device: str = "cuda:0", kernels=None,
-                 cuda_graphs: bool = True):
+                 cuda_graphs: bool = True, lookahead: bool = True):
         ec = EngineConfig(dtype=dtype, page_size=page_size, num_pages=num_pages, kv_gb=kv_gb,
                           gpu_memory_utilization=gpu_memory_utilization, max_model_len=max_model_len,
                           max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens, seed=seed,
-                          device=device, cuda_graphs=cuda_graphs)
+                          device=device, cuda_graphs=cuda_graphs, lookahead=lookahead)
         self.engine = build_engine(model, ec, config=config, random_seed=random_seed, kernels=kernels)
 
     def generate(self, prompt_token_ids, sampling_params=None) -> list:

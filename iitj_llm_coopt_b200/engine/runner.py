@@ -30,6 +30,8 @@ class StepEntry:
     request: object
     tokens: list
     want: list = field(default_factory=list)   # indices into `tokens`
+    source_rows: list | None = None            # per token: row of the previous step's sampled ids that holds it
+    #                                            (the host does not know it yet), or -1 for a token given here
 
 
 class ModelRunner:
@@ -135,7 +137,8 @@ class ModelRunner:
         return logits
 
     # ---- the step --------------------------------------------------------------------
-    def step(self, entries: list):
+    def step(self, entries: list, prev_ids=None):
+        """`prev_ids`: the previous step's sampled ids on the device, for entries with `source_rows`."""
         if not entries:
             return None
         cache = self.cache
@@ -189,6 +192,9 @@ class ModelRunner:
         for g in groups:
             place(f"slots{g}", T)
             place(f"table{g}", B * widths[g])
+        fed = prev_ids is not None and any(e.source_rows is not None for e in entries)
+        if fed:
+            place("token_src", T)
         place("attn_items", plan.n_items)
         place("attn_tiles", 4 * plan.n_tiles)
         place("attn_big_tiles", 4 * len(plan.big_rows))
@@ -202,6 +208,11 @@ class ModelRunner:
             host[o:o + n] = values
 
         ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T)
+        if fed:
+            src = np.concatenate([np.asarray(e.source_rows if e.source_rows is not None else [-1] * len(e.tokens),
+                                             dtype=np.int64) for e in entries])
+            put("token_src", src)
+            ids = np.where(src >= 0, 0, ids)          # placeholders: the device fills them in
         if ids.min() < 0 or ids.max() >= self.vocab:
             raise ValueError(f"token id out of range [0, {self.vocab}) in this step")
         put("token_ids", ids)
@@ -242,6 +253,8 @@ class ModelRunner:
             o, n = layout[name]
             return self._meta[o:o + n]
 
+        if fed:
+            self.model.k.gather_tokens(dev("token_ids"), prev_ids, dev("token_src"))
         plan.items = dev("attn_items") if plan.n_items else None
         plan.tiles = dev("attn_tiles").view(-1, 4) if plan.n_tiles else None
         plan.big_tiles = dev("attn_big_tiles").view(-1, 4) if plan.n_tiles else None
@@ -261,7 +274,7 @@ class ModelRunner:
                           workspace=self.workspace, requests=[e.request for e in entries],
                           query_lens=qlens, starts=starts, slots_host=slots_b)
         if graphable:
-            key = (tuple(qlens), tuple(len(e.want) for e in entries), tuple(sorted(widths.items())), plan.context_bound)
+            key = (tuple(qlens), tuple(len(e.want) for e in entries), tuple(sorted(widths.items())), plan.context_bound, fed)
             logits = self._forward_graphed(key, ctx, eager_runs=1 if decode_shaped else 2)
         else:
             logits = self.model.forward(ctx)

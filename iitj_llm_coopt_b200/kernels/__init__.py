@@ -59,6 +59,7 @@ _SIGNATURES = {
     "llm_gemm_bf16": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                       _c_int, _c_void_p],
     "llm_gemm_bf16_status": [],
+    "llm_gather_tokens": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
     "llm_sample_scratch_floats": [_c_int, _c_int],
     "llm_sample": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
 }
@@ -443,6 +444,15 @@ class Kernels:
     def attention_status(self) -> int:
         """0, or a code if the tcgen05 attention kernel gave up waiting on a barrier since the last call."""
         return self.lib.llm_attention_tcgen05_status()
+
+    def gather_tokens(self, dst, src, rows):
+        """dst[i] = src[rows[i]] where rows[i] >= 0 (int32 device tensors): the previous step's sampled ids
+        become this step's input tokens without a trip to the host."""
+        _check(dst, "gather_tokens.dst", torch.int32, 1)
+        _check(src, "gather_tokens.src", torch.int32, 1)
+        _check(rows, "gather_tokens.rows", torch.int32, 1)
+        _need(rows.shape[0] == dst.shape[0], "gather_tokens: one source row per destination")
+        self._call("llm_gather_tokens", _ptr(dst), _ptr(src), _ptr(rows), dst.shape[0], self._stream())
 
     # ---- sampling --------------------------------------------------------------------
     def sample(self, logits, temperature, keys, out):

@@ -32,32 +32,80 @@ def _signed(u: int) -> int:
     return u - (1 << 64) if u >= (1 << 63) else u
 
 
+class _Slot:
+    """Device output, pinned host copies and an event: one sampling call in flight."""
+
+    def __init__(self, cap, device):
+        pin = torch.cuda.is_available()
+        self.cap = cap
+        self.out = torch.empty(cap, dtype=torch.int32, device=device)
+        self.temps = torch.empty(cap, dtype=torch.float32, device=device)
+        self.keys = torch.empty(cap, dtype=torch.int64, device=device)
+        self.host = torch.empty(cap, dtype=torch.int32)
+        self.temps_host = torch.empty(cap, dtype=torch.float32)
+        self.keys_host = torch.empty(cap, dtype=torch.int64)
+        if pin:
+            self.host, self.temps_host, self.keys_host = self.host.pin_memory(), self.temps_host.pin_memory(), self.keys_host.pin_memory()
+        self.event = torch.cuda.Event() if str(device).startswith("cuda") else None
+
+
 class Sampler:
+    """`launch` starts the kernel and the copy of the ids to pinned host memory and returns a handle;
+    `fetch` waits for that copy.  Three slots rotate, so a step can be launched while the ids of the step
+    before it are still on their way (and still feed that step's tokens on the device)."""
+
     def __init__(self, kernels, seed: int = 0, device="cuda"):
         self.k, self.seed, self.device = kernels, seed, device
-        self._out = None
-        self._host = None
+        self._slots: list = [None, None, None]
+        self._turn = 0
+
+    def _slot(self, n):
+        i = self._turn
+        self._turn = (self._turn + 1) % len(self._slots)
+        if self._slots[i] is None or self._slots[i].cap < n:
+            self._slots[i] = _Slot(max(256, 2 * n), self.device)
+        return self._slots[i]
 
     def _buffers(self, n):
-        if self._out is None or self._out.numel() < n:
-            cap = max(256, 2 * n)
-            self._out = torch.empty(cap, dtype=torch.int32, device=self.device)
-            self._host = torch.empty(cap, dtype=torch.int32)
-            if torch.cuda.is_available():
-                self._host = self._host.pin_memory()
-        return self._out[:n], self._host[:n]
+        """(device ids, host ids) of a fresh slot (for callers that launch the kernel themselves)."""
+        slot = self._slot(n)
+        return slot.out[:n], slot.host[:n]
 
-    def sample(self, logits, rows: list) -> list:
-        """rows[i] = (temperature, request seed, token index) for logits row i; returns ids."""
+    def launch(self, logits, rows: list):
+        """rows[i] = (temperature, request seed, token index) for logits row i; returns a handle for `fetch`.
+        `handle.ids` are the sampled ids on the device."""
         n = logits.shape[0]
         if n != len(rows):
             raise ValueError(f"{n} logits rows but {len(rows)} sampling records")
-        out, host = self._buffers(n)
+        slot = self._slot(n)
+        out = slot.out[:n]
         if all(t <= 0 for t, _, _ in rows):
             self.k.sample(logits, None, None, out)
         else:
-            temps = torch.tensor([float(t) for t, _, _ in rows], dtype=torch.float32)
-            keys = torch.tensor([_signed(row_key(self.seed, s, i)) for _, s, i in rows], dtype=torch.int64)
-            self.k.sample(logits, temps.to(self.device), keys.to(self.device), out)
-        host.copy_(out)          # synchronous: the step's one device-to-host read
-        return host.tolist()
+            slot.temps_host[:n] = torch.tensor([float(t) for t, _, _ in rows], dtype=torch.float32)
+            slot.keys_host[:n] = torch.tensor([_signed(row_key(self.seed, s, i)) for _, s, i in rows], dtype=torch.int64)
+            slot.temps[:n].copy_(slot.temps_host[:n], non_blocking=True)
+            slot.keys[:n].copy_(slot.keys_host[:n], non_blocking=True)
+            self.k.sample(logits, slot.temps[:n], slot.keys[:n], out)
+        slot.host[:n].copy_(out, non_blocking=True)
+        if slot.event is not None:
+            slot.event.record()
+        return _Handle(slot, n)
+
+    def fetch(self, handle) -> list:
+        if handle.slot.event is not None:
+            handle.slot.event.synchronize()
+        return handle.slot.host[:handle.n].tolist()
+
+    def sample(self, logits, rows: list) -> list:
+        """Ids of the rows; one device-to-host read."""
+        return self.fetch(self.launch(logits, rows))
+
+
+class _Handle:
+    def __init__(self, slot, n):
+        self.slot, self.n = slot, n
+
+    @property
+    def ids(self):
+        return self.slot.out[:self.n]
