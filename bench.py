@@ -228,8 +228,8 @@ def main() -> int:
         return times
 
     if args.only == "prefill":
-        t = prefill_run(args.prefill_tokens, 1, 1)
-        print(json.dumps({"only": "prefill", "tokens": args.prefill_tokens, "ms": t[0]}))
+        t = sorted(prefill_run(args.prefill_tokens, max(1, K), 1))
+        print(json.dumps({"only": "prefill", "tokens": args.prefill_tokens, "ms": t[len(t) // 2], "min_ms": t[0], "reps": len(t)}))
         return 0
     if args.only == "decode":
         t, n = decode_run(B, max(1, K), 3)

@@ -59,6 +59,10 @@ _SIGNATURES = {
     "llm_gemm_bf16": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                       _c_int, _c_void_p],
     "llm_gemm_bf16_status": [],
+    "llm_gemm_bf16_pair": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                           _c_void_p, _c_void_p],
+    "llm_gemm_bf16_pair_scratch": [_c_int],
+    "llm_gemm_bf16_pair_status": [],
     "llm_gather_tokens": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
     "llm_sample_scratch_floats": [_c_int, _c_int],
     "llm_sample": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
@@ -173,10 +177,12 @@ class Kernels:
         # SwiGLU boundary, IITJ_PDL=0 switches programmatic dependent launch off (all for measurements)
         self.gemm_backend = os.environ.get("IITJ_GEMM_BACKEND", "auto")
         self.gemm_small_tokens = int(os.environ.get("IITJ_GEMM_SMALL_TOKENS", "128"))
+        self.gemm_pair_mode = os.environ.get("IITJ_GEMM_PAIR", "swiglu")   # off | swiglu | all
         self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
         if os.environ.get("IITJ_PDL", "1") == "0":
             self.lib.llm_set_pdl(0)
         self._scratch_bufs: dict = {}
+        self._pair_counters: dict = {}
         self.scratch_generation = 0
         self._sm_count = None
 
@@ -371,9 +377,12 @@ class Kernels:
             return out
         # bfloat16: this library's tcgen05 kernel where it is the faster one, else cuBLAS through torch
         tokens, k = x.shape
-        if self.gemm_policy(tokens, n, k, swiglu) == "tcgen05":
+        policy = self.gemm_policy(tokens, n, k, swiglu)
+        if policy == "tcgen05":
             splits, smem_kb = self.gemm_plan(tokens, n, k, swiglu)
             return self.gemm_tcgen05(x, weight, out, swiglu, splits, smem_kb)
+        if policy == "pair":
+            return self.gemm_pair(x, weight, out, swiglu)
         if swiglu:
             gu = torch.mm(x, weight.t())
             return self.silu_mul(gu, out)
@@ -401,18 +410,44 @@ class Kernels:
             self.launches += 1
         return out
 
+    def gemm_pair(self, x, weight, out, swiglu: bool = False, tail_split: bool = True):
+        """out = x . weight^T on this library's persistent CTA-pair tcgen05 kernel (many tokens).  With
+        `tail_split` the tiles of the last, partly filled round are cut along k over all clusters."""
+        _check(x, "gemm.x", torch.bfloat16, 2)
+        _check(weight, "gemm.weight", torch.bfloat16, 2)
+        _check(out, "gemm.out", (torch.bfloat16, torch.float32), 2)
+        tokens, k = x.shape
+        n = weight.shape[0] // 2 if swiglu else weight.shape[0]
+        _need(weight.shape[1] == k and out.shape == (tokens, n), "gemm: shapes do not fit")
+        partials = counters = None
+        if tail_split:
+            partials = self._scratch("gemm.pair.partials", self.lib.llm_gemm_bf16_pair_scratch(0), x.device)
+            counters = self._pair_counters.get(x.device)
+            if counters is None:      # zeroed once; every launch leaves them zero again
+                counters = torch.zeros(self.lib.llm_gemm_bf16_pair_scratch(1), dtype=torch.int32, device=x.device)
+                self._pair_counters[x.device] = counters
+        self._call("llm_gemm_bf16_pair", _ptr(x), _ptr(weight), _ptr(out), 1 if out.dtype == torch.float32 else 0,
+                   tokens, n, k, out.shape[1], 1 if swiglu else 0, _ptr(partials), _ptr(counters), self._stream())
+        return out
+
     # Which kernel multiplies: "tcgen05" (this library) or "cublas".  `gemm_backend` may force one.
     def gemm_policy(self, tokens, n, k, swiglu) -> str:
-        """Measured on B200 at the 8B shapes (in CUDA graphs, cold weights): with two CTAs per SM and up to
-        eight k-splits this library's product matches or beats cuBLAS up to 32 tokens for every shape of the
-        model (and its weight prefetch overlaps the kernel before it); the fused SwiGLU product holds up to
-        128 tokens; above that cuBLAS is faster."""
+        """"tcgen05" (one CTA per tile, weights on the 128-row side), "pair" (persistent CTA pairs, tokens on
+        the 256-row side) or "cublas".  Measured on B200 at the 8B shapes, in CUDA graphs with cold weights:
+        up to 32 tokens the tcgen05 product with two or three CTAs per SM and up to eight k-splits matches
+        or beats cuBLAS for every shape of the model (and its weight prefetch overlaps the kernel before
+        it); its fused SwiGLU form holds up to 128 tokens.  From about 640 tokens the pair kernel's fused
+        SwiGLU product beats cuBLAS plus a separate activation kernel (2048 tokens: 330 against 365 us).  Its
+        plain products stay about 7 % behind cuBLAS, which halves its operand traffic with multicast loads
+        that this library does not use, so those stay on cuBLAS (IITJ_GEMM_PAIR=all moves them over)."""
         if k % 8:
             return "cublas"
         if self.gemm_backend != "auto":
             return self.gemm_backend
         if tokens <= (self.gemm_small_tokens if swiglu else min(32, self.gemm_small_tokens)):
             return "tcgen05"
+        if tokens >= 640 and (self.gemm_pair_mode == "all" or (swiglu and self.gemm_pair_mode == "swiglu")):
+            return "pair"
         return "cublas"
 
     def gemm_plan(self, tokens, n, k, swiglu) -> tuple:
@@ -440,6 +475,10 @@ class Kernels:
     def gemm_status(self) -> int:
         """0, or a code if a tcgen05 GEMM gave up waiting on one of its barriers since the last call."""
         return self.lib.llm_gemm_bf16_status()
+
+    def gemm_pair_status(self) -> int:
+        """0, or a code if the CTA-pair GEMM gave up waiting on one of its barriers since the last call."""
+        return self.lib.llm_gemm_bf16_pair_status()
 
     def attention_status(self) -> int:
         """0, or a code if the tcgen05 attention kernel gave up waiting on a barrier since the last call."""

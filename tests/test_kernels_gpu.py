@@ -363,6 +363,43 @@ def test_gemm_tcgen05_row_does_not_depend_on_batch(K):
     assert torch.equal(full[31:32], one)
 
 
+# ---- the persistent CTA-pair matrix product for many tokens (bfloat16) -------------------
+@pytest.mark.parametrize("tokens,n,k", [(256, 256, 64), (300, 264, 136), (513, 1000, 264), (1000, 520, 4104), (130, 72, 64)])
+def test_gemm_pair_shapes(K, tokens, n, k):
+    x, w = rnd((tokens, k), torch.bfloat16, 110), rnd((n, k), torch.bfloat16, 111, 0.05)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((tokens, n), float("nan"), device="cuda", dtype=out_dtype)
+        K.gemm_pair(x, w, out)
+        close(out, R.ref_linear(x, w), torch.bfloat16, 0.5 if out_dtype == torch.bfloat16 else 0.01)
+    assert K.gemm_pair_status() == 0
+
+
+@pytest.mark.parametrize("tokens,n,k", [(256, 128, 128), (300, 176, 72), (700, 1000, 264), (1030, 344, 2056)])
+def test_gemm_pair_swiglu(K, tokens, n, k):
+    x, w = rnd((tokens, k), torch.bfloat16, 112), rnd((2 * n, k), torch.bfloat16, 113, 0.2)
+    out = torch.full((tokens, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    K.gemm_pair(x, w, out, swiglu=True)
+    close(out, R.ref_linear(x, w, swiglu=True), torch.bfloat16, 0.5)
+    assert K.gemm_pair_status() == 0
+
+
+@pytest.mark.parametrize("tokens,n,k,swiglu", [(300, 600, 8200, False), (1200, 520, 8192, False), (520, 300, 9000, True)])
+def test_gemm_pair_tail_split(K, tokens, n, k, swiglu):
+    """Few tiles and a long k: every tile is cut along k over many clusters, whose partial sums the tile's
+    first cluster adds.  Three launches in a row: the counters must be back at zero after each."""
+    x, w = rnd((tokens, k), torch.bfloat16, 114), rnd(((2 if swiglu else 1) * n, k), torch.bfloat16, 115, 0.05)
+    want = R.ref_linear(x, w, swiglu=swiglu)
+    for _ in range(3):
+        out = torch.full((tokens, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+        K.gemm_pair(x, w, out, swiglu=swiglu, tail_split=True)
+        close(out, want, torch.bfloat16, 0.5)
+        assert int(K._pair_counters[x.device].abs().sum()) == 0
+    whole = torch.empty_like(out)
+    K.gemm_pair(x, w, whole, swiglu=swiglu, tail_split=False)
+    close(whole, want, torch.bfloat16, 0.5)
+    assert K.gemm_pair_status() == 0
+
+
 # ---- the tcgen05 prefill attention (bfloat16, head size 128) -------------------------------
 @pytest.mark.parametrize("heads,kv_heads,page,window", [(8, 2, 16, 0), (4, 1, 8, 0), (2, 2, 64, 0), (3, 1, 128, 0),
                                                         (4, 2, 16, 100), (4, 2, 32, 128), (16, 1, 16, 0)])
