@@ -1,43 +1,47 @@
 // Paged causal attention for prompt portions on the fifth-generation tensor cores
 // (bfloat16, head size 128, page sizes 8 .. 128 that divide 128).
 //
-// One CTA = 128 queries of one request x one query head.  Keys and values walk through shared
-// memory in tiles of 128 keys; each page of a tile is one TMA box per 64-dim half, placed at
-// its row offset of the 128-byte-swizzled tile, so the paged cache needs no gather pass.
+// One CTA = 128 query positions of one request x two query heads of one key/value group (the last head of
+// a group with an odd number of heads runs alone).  Both heads see the same keys, so every key/value tile
+// is loaded once for two tiles of scores, and the two heads' chains (scores -> softmax -> P V) run in
+// ping-pong: while the softmax warps of one head work, the tensor core serves the other.  Keys and values
+// walk through shared memory in tiles of 128 keys; each page of a tile is one TMA box per 64-dim half,
+// placed at its row offset of the 128-byte-swizzled tile, so the paged cache needs no gather pass.
 //
-//   S = Q K^T      tcgen05.mma, M = 128 queries, N = 128 keys, K = 128 dims, both operands K-major
-//                  in shared memory; S lands in tensor memory (two buffers of 128 columns).
-//   softmax        eight warps, two threads per query row (64 of the tile's 128 keys each): a thread reads
-//                  its part of the row of S with tcgen05.ld (a TMEM lane is a row: no shuffles), masks by
-//                  position, takes the maximum (the two halves meet through shared memory), exponentiates
-//                  in float32 and writes P as bfloat16 into a swizzled shared tile.
-//   O_tile = P V   tcgen05.mma, M = 128 queries, N = 128 dims, K = 128 keys; P is K-major, V is
-//                  MN-major (a key's 128 dims are contiguous), so the V tile is used as it was loaded.
-//   accumulate     the same threads read O_tile from tensor memory and fold it into a float32 row
-//                  accumulator in registers with the online-softmax correction.
+//   S = Q K^T      tcgen05.mma, M = 128 queries, N = 128 keys, K = 128 dims, both operands K-major in
+//                  shared memory; S lands in tensor memory (128 float32 columns per head).
+//   softmax        four warps per head, one thread per query row: it reads its row of S with tcgen05.ld (a
+//                  TMEM lane is a row: no shuffles), masks by position, takes the maximum, exponentiates in
+//                  float32 and writes P as bfloat16 back over the first 64 columns of S (tcgen05.st).
+//   O += P V       tcgen05.mma with P read from tensor memory and V MN-major from shared memory (a key's 128
+//                  dims are contiguous, so the V tile is used as it was loaded); O stays in tensor memory for
+//                  the whole sequence of key tiles.
+//   rescaling      P is taken relative to a running maximum that is only moved when a row's maximum has
+//                  grown by more than 2^8; then, and only then, the row of O is read, scaled and written
+//                  back before the next P V.  The sum l follows the same reference, so O / l is exact.
 //
-// The MMA warp issues S of tile j+1 before P V of tile j, so the tensor core works on the next
-// scores while the softmax warps work on the current ones.  Replaces flash_attn_varlen_func
-// (engine/model.py:204-207) for portions; same masking and float32 statistics as the mma.sync
-// kernel of attention_bf16.cu, which remains for other head and page sizes.
+// Replaces flash_attn_varlen_func (engine/model.py:204-207) for portions; same masking and float32
+// statistics as the mma.sync kernel of attention_bf16.cu, which remains for other head and page sizes.
 //
 // Every mbarrier wait is bounded; a wait that runs out records a code (llm_attention_tcgen05_status)
 // and the CTA falls through to its teardown, where the tensor memory is freed.
 #include "tcgen05_common.cuh"
 
+#include <type_traits>
+
 namespace {
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int kRows = 128;        // queries per CTA (UMMA M)
+constexpr int kRows = 128;        // queries per CTA and head (UMMA M)
 constexpr int kKeys = 128;        // keys per tile
 constexpr int kDim = 128;         // head size
 constexpr int kHalfBytes = 128 * 128;          // one 64-column half of a [128 x 128] bf16 tile: 128 rows x 128 bytes
 constexpr int kTileBytes = 2 * kHalfBytes;     // 32 KiB
-constexpr int kThreads = 320;     // warp 0: loads, warp 1: MMA + TMEM, warps 2-9: softmax and output
-constexpr int kSoftmaxThreads = 256;
-constexpr int kCols = 64;         // columns of S (keys) and of O (dims) per softmax thread
-constexpr uint32_t kTmemCols = 512;            // S0 | S1 | O0 | O1, 128 float32 columns each
+constexpr int kThreads = 320;     // warp 0: loads, warp 1: MMA + TMEM, warps 2-5: softmax of head A, warps 6-9: of head B
+constexpr int kGroupThreads = 128;
+constexpr uint32_t kTmemCols = 512;            // S_A | S_B | O_A | O_B, 128 float32 columns each
+constexpr float kRescaleStep = 8.0f;           // in log2 units: P stays below 2^8
 
 __device__ int g_attn_status = 0;
 __device__ __forceinline__ void attn_give_up(int code) { atomicCAS(&g_attn_status, 0, (code << 16) | (int)(blockIdx.x & 0xffff)); }
@@ -47,60 +51,65 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__device__ __forceinline__ float ex2(float x) {          // 2^x, x <= 0 here; one MUFU instruction
+__device__ __forceinline__ float ex2(float x) {          // 2^x; one MUFU instruction
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 
-// This thread's 64 columns of one S or O buffer (its TMEM lane) in one round trip.
-__device__ __forceinline__ void load_cols(uint32_t addr, uint32_t (&r)[kCols]) {
-    tmem_ld32(addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-    tmem_ld32(addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+// D[tmem] (+)= A[tmem] . B[smem]: the A operand (P) is read from tensor memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-// Maximum over the 64 scores; k0 = key of the first one.
+// Maximum of 32 scores (keys k0 .. k0+31) with four independent chains.
 template <bool MASK>
-__device__ __forceinline__ float row_max(const uint32_t (&r)[kCols], int k0, int row_pos, int row_lo) {
-    float mx = -INFINITY;
+__device__ __forceinline__ float chunk_max(const uint32_t (&r)[32], int k0, int row_pos, int row_lo, float mx) {
+    float m0 = mx, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-    for (int c = 0; c < kCols; ++c) {
+    for (int c = 0; c < 32; c += 4) {
+        float a0 = __uint_as_float(r[c]), a1 = __uint_as_float(r[c + 1]), a2 = __uint_as_float(r[c + 2]), a3 = __uint_as_float(r[c + 3]);
         if (MASK) {
             const int key = k0 + c;
-            if (key <= row_pos && key >= row_lo) mx = fmaxf(mx, __uint_as_float(r[c]));
-        } else {
-            mx = fmaxf(mx, __uint_as_float(r[c]));
+            if (key > row_pos || key < row_lo) a0 = -INFINITY;
+            if (key + 1 > row_pos || key + 1 < row_lo) a1 = -INFINITY;
+            if (key + 2 > row_pos || key + 2 < row_lo) a2 = -INFINITY;
+            if (key + 3 > row_pos || key + 3 < row_lo) a3 = -INFINITY;
         }
+        m0 = fmaxf(m0, a0); m1 = fmaxf(m1, a1); m2 = fmaxf(m2, a2); m3 = fmaxf(m3, a3);
     }
-    return mx;
+    return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
-// P = 2^(S * sl - mu) of the 64 scores as bfloat16 into this thread's row of one half of the swizzled P tile
-// (`p_half` = that half's base: 128 rows of 128 bytes); returns the sum.
+// P = 2^(S * sl - mu) of 32 scores, packed as 16 columns of two bfloat16; adds to four partial sums.
 template <bool MASK>
-__device__ __forceinline__ float row_exp(const uint32_t (&r)[kCols], unsigned char* p_half, int row, float sl, float mu,
-                                         int k0, int row_pos, int row_lo) {
-    float sum = 0.f;
-    unsigned char* prow = p_half + row * 128;
+__device__ __forceinline__ void chunk_exp(const uint32_t (&r)[32], uint32_t (&packed)[16], float sl, float mu, int k0, int row_pos,
+                                          int row_lo, float (&sum)[4]) {
 #pragma unroll
-    for (int c0 = 0; c0 < kCols; c0 += 8) {          // 8 keys = one 16-byte chunk
-        uint32_t packed[4];
-#pragma unroll
-        for (int c = 0; c < 8; c += 2) {
-            float p0 = ex2(fmaf(__uint_as_float(r[c0 + c]), sl, -mu));
-            float p1 = ex2(fmaf(__uint_as_float(r[c0 + c + 1]), sl, -mu));
-            if (MASK) {
-                const int key = k0 + c0 + c;
-                if (key > row_pos || key < row_lo) p0 = 0.f;
-                if (key + 1 > row_pos || key + 1 < row_lo) p1 = 0.f;
-            }
-            sum += p0 + p1;
-            packed[c >> 1] = pack2(p0, p1);
+    for (int c = 0; c < 32; c += 4) {
+        float p0 = ex2(fmaf(__uint_as_float(r[c]), sl, -mu)), p1 = ex2(fmaf(__uint_as_float(r[c + 1]), sl, -mu));
+        float p2 = ex2(fmaf(__uint_as_float(r[c + 2]), sl, -mu)), p3 = ex2(fmaf(__uint_as_float(r[c + 3]), sl, -mu));
+        if (MASK) {
+            const int key = k0 + c;
+            if (key > row_pos || key < row_lo) p0 = 0.f;
+            if (key + 1 > row_pos || key + 1 < row_lo) p1 = 0.f;
+            if (key + 2 > row_pos || key + 2 < row_lo) p2 = 0.f;
+            if (key + 3 > row_pos || key + 3 < row_lo) p3 = 0.f;
         }
-        *reinterpret_cast<uint4*>(prow + (((c0 >> 3) ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        sum[0] += p0; sum[1] += p1; sum[2] += p2; sum[3] += p3;
+        packed[c >> 1] = pack2(p0, p1);
+        packed[(c >> 1) + 1] = pack2(p2, p3);
     }
-    return sum;
 }
 
 struct AttnArgs {
@@ -110,6 +119,7 @@ struct AttnArgs {
     bf16* out;
     int out_stride;
     int heads, kv_heads, page_size, window;
+    int pairs;                    // CTAs per key/value group: ceil(heads per group / 2)
     float sl;                     // softmax scale * log2(e)
 };
 
@@ -118,21 +128,20 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const AttnArgs a) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_tile = base;                                  // 32 KiB
-    unsigned char* k_tile[2] = {base + kTileBytes, base + 2 * kTileBytes};
-    unsigned char* v_tile[2] = {base + 3 * kTileBytes, base + 4 * kTileBytes};
-    unsigned char* p_tile = base + 5 * kTileBytes;                 // 32 KiB
-    __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2],
-        p_full, p_empty, o_full[2], o_empty[2];
+    unsigned char* q_tile[2] = {base, base + kTileBytes};                          // head A, head B
+    unsigned char* k_tile[2] = {base + 2 * kTileBytes, base + 3 * kTileBytes};
+    unsigned char* v_tile[2] = {base + 4 * kTileBytes, base + 5 * kTileBytes};
+    __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_done[2];
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int failed;
-    __shared__ volatile float xchg[2][2][kRows];   // [tile parity][column half][row]: partial row maxima; sums at the end
-    __shared__ volatile int xflag[2][2][kRows];    // tile number + 1 for which xchg holds a value
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int4 td = a.tiles[gridDim.x - 1 - blockIdx.x];           // longest tiles (latest queries) first
     const int tok0 = td.x, rows = td.y, pos0 = td.z, req = td.w;
-    const int h = blockIdx.y, hk = h / (a.heads / a.kv_heads);
+    const int group = a.heads / a.kv_heads;
+    const int hk = blockIdx.y / a.pairs, pr = blockIdx.y - hk * a.pairs;
+    const int head_a = hk * group + 2 * pr;
+    const int n_heads = (2 * pr + 1 < group) ? 2 : 1;              // heads this CTA serves
     const int pos_last = pos0 + rows - 1;
     const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
     const int k_begin = lo0 & ~(kKeys - 1);
@@ -142,14 +151,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_init(&q_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], kSoftmaxThreads); mbar_init(&o_full[s], 1); mbar_init(&o_empty[s], kSoftmaxThreads);
+            mbar_init(&s_full[s], 1); mbar_init(&p_full[s], kGroupThreads / 32); mbar_init(&o_done[s], 1);
         }
-        mbar_init(&p_full, kSoftmaxThreads);
-        mbar_init(&p_empty, 1);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = threadIdx.x; i < 2 * 2 * kRows; i += kThreads) (&xflag[0][0][0])[i] = 0;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
@@ -165,9 +171,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // ---- loads: lane 0 keeps the barriers, lane p fetches page p of every tile (its block-table entry
         //      and the four boxes of that page: K and V, two 64-dim halves each) ----------------------------
         if (lane == 0) {
-            mbar_expect_tx(&q_full, kTileBytes);
-            tma_load_2d(q_tile, &map_q, &q_full, h * kDim, tok0);
-            tma_load_2d(q_tile + kHalfBytes, &map_q, &q_full, h * kDim + 64, tok0);
+            mbar_expect_tx(&q_full, n_heads * kTileBytes);
+            for (int x = 0; x < n_heads; ++x) {
+                tma_load_2d(q_tile[x], &map_q, &q_full, (head_a + x) * kDim, tok0);
+                tma_load_2d(q_tile[x] + kHalfBytes, &map_q, &q_full, (head_a + x) * kDim + 64, tok0);
+            }
         }
         const int* table = a.block_table + (size_t)req * a.table_width;
         const int ps = a.page_size, pages_per_tile = kKeys / ps;
@@ -200,126 +208,159 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer --------------------------------------------------------------------------
+        // Order: S_A(0) S_B(0), then per key tile j: PV_A(j) S_A(j+1) PV_B(j) S_B(j+1).  The tensor core runs
+        // its instructions in the order of issue, so S_x(j+1) overwrites P_x(j) only after PV_x(j) has read it.
         constexpr uint32_t idesc_s = umma_idesc(kRows, kKeys);                         // Q, K both K-major
-        constexpr uint32_t idesc_o = umma_idesc(kRows, kDim) | (1u << 16);             // P K-major, V MN-major
+        constexpr uint32_t idesc_o = umma_idesc(kRows, kDim) | (1u << 16);             // P from TMEM, V MN-major
         bool ok = mbar_wait(&q_full, 0);
         if (!ok) { attn_give_up(2); failed = 1; }
-        auto issue_pv = [&](int i) {
-            const int s = i & 1;
-            if (!mbar_wait(&v_full[s], (i >> 1) & 1) || !mbar_wait(&p_full, i & 1) ||
-                (i >= 2 && !mbar_wait(&o_empty[s], ((i >> 1) - 1) & 1))) { attn_give_up(3); failed = 1; return false; }
+        auto issue_s = [&](int x, int j) {
+            const int s = j & 1;
+#pragma unroll
+            for (int kk = 0; kk < kDim / 16; ++kk) {
+                const uint64_t da = umma_desc(q_tile[x] + (kk >> 2) * kHalfBytes) + 2 * (kk & 3);
+                const uint64_t db = umma_desc(k_tile[s] + (kk >> 2) * kHalfBytes) + 2 * (kk & 3);
+                umma_f16(tmem + x * 128, da, db, idesc_s, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(&s_full[x]);
+        };
+        auto issue_pv = [&](int x, int j) {
+            const int s = j & 1;
+            if (!mbar_wait(&p_full[x], j & 1)) { attn_give_up(3); failed = 1; return false; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int kk = 0; kk < kKeys / 16; ++kk) {
-                const uint64_t da = umma_desc(p_tile + (kk >> 2) * kHalfBytes) + 2 * (kk & 3);
                 const uint64_t db = umma_desc_mn(v_tile[s] + kk * 16 * 128, kHalfBytes);
-                umma_f16(tmem + 256 + s * 128, da, db, idesc_o, kk > 0 ? 1u : 0u);
+                umma_f16_ts(tmem + 256 + x * 128, tmem + x * 128 + kk * 8, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(&o_done[x]);
+            return true;
+        };
+        if (ok) {
+            if (!mbar_wait(&k_full[0], 0)) { attn_give_up(4); failed = 1; ok = false; }
+        }
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int x = 0; x < n_heads; ++x) issue_s(x, 0);
+            umma_commit(&k_empty[0]);
+        }
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int s = j & 1, s1 = (j + 1) & 1;
+            const bool more = j + 1 < n_tiles;
+            if (!mbar_wait(&v_full[s], (j >> 1) & 1)) { attn_give_up(5); failed = 1; ok = false; break; }
+            if (!(ok = issue_pv(0, j))) break;
+            if (more) {
+                if (!mbar_wait(&k_full[s1], ((j + 1) >> 1) & 1)) { attn_give_up(4); failed = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_s(0, j + 1);
+            }
+            if (n_heads == 2) {
+                if (!(ok = issue_pv(1, j))) break;
+                if (more) issue_s(1, j + 1);
             }
             umma_commit(&v_empty[s]);
-            umma_commit(&p_empty);
-            umma_commit(&o_full[s]);
-            return true;
-        };
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            const int s = j & 1;
-            if (!mbar_wait(&k_full[s], (j >> 1) & 1) || (j >= 2 && !mbar_wait(&s_empty[s], ((j >> 1) - 1) & 1))) {
-                attn_give_up(4); failed = 1; ok = false; break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int kk = 0; kk < kDim / 16; ++kk) {
-                const uint64_t da = umma_desc(q_tile + (kk >> 2) * kHalfBytes) + 2 * (kk & 3);
-                const uint64_t db = umma_desc(k_tile[s] + (kk >> 2) * kHalfBytes) + 2 * (kk & 3);
-                umma_f16(tmem + s * 128, da, db, idesc_s, kk > 0 ? 1u : 0u);
-            }
-            umma_commit(&k_empty[s]);
-            umma_commit(&s_full[s]);
-            if (j >= 1) ok = issue_pv(j - 1);
+            if (more) umma_commit(&k_empty[s1]);
         }
-        if (ok) issue_pv(n_tiles - 1);
-    } else if (warp >= 2) {
-        // ---- softmax, accumulation, output: two threads per query row, 64 columns each --------------
+    } else if (warp >= 2 && ((warp - 2) >> 2) < n_heads) {
+        // ---- softmax and output: one thread per query row of one head ---------------------------------
+        const int x = (warp - 2) >> 2;                 // head A or B
         const int quarter = warp & 3;                  // TMEM lanes [32 * quarter, +32) are readable by this warp
-        const int half = (warp - 2) >> 2;              // which 64 keys of a tile / which 64 output dims
         const int row = quarter * 32 + lane;
-        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16) + half * kCols;
+        const uint32_t s_addr = tmem + ((uint32_t)(quarter * 32) << 16) + x * 128;
+        const uint32_t o_addr = s_addr + 256;
         const int row_pos = pos0 + row;
         const int row_lo = a.window > 0 ? row_pos - a.window + 1 : 0;
-        unsigned char* p_half = p_tile + half * kHalfBytes;
-        float acc[kCols];
-#pragma unroll
-        for (int d = 0; d < kCols; ++d) acc[d] = 0.f;
-        float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+        float m = -INFINITY, l = 0.f;                  // reference maximum (log2 units) and sum relative to it
         bool ok = true;
-        // The two threads of a row hand each other a value through shared memory: write it, publish the tile
-        // number, wait (bounded) for the partner's.  No block-wide barrier, so a thread that gave up cannot
-        // leave its partner stuck.
-        auto exchange = [&](int buf, int stamp, float mine, float& theirs) {
-            xchg[buf][half][row] = mine;
-            __threadfence_block();
-            xflag[buf][half][row] = stamp;
-            for (uint32_t i = 0; i < kSpinLimit; ++i) {
-                if (xflag[buf][half ^ 1][row] == stamp) {
-                    __threadfence_block();
-                    theirs = xchg[buf][half ^ 1][row];
-                    return true;
-                }
-            }
-            return false;
-        };
-        auto fold = [&](int i, float corr) {          // acc = acc * corr + O_tile(i), this thread's 64 dims
-            const int s = i & 1;
-            if (!mbar_wait(&o_full[s], (i >> 1) & 1)) { attn_give_up(5); failed = 1; return false; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t r[kCols];
-            load_cols(lane_addr + 256 + s * 128, r);
-#pragma unroll
-            for (int c = 0; c < kCols; ++c) acc[c] = fmaf(acc[c], corr, __uint_as_float(r[c]));
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&o_empty[s]);
-            return true;
-        };
         for (int j = 0; j < n_tiles; ++j) {
-            const int s = j & 1, k0 = k_begin + j * kKeys + half * kCols;
-            if (!mbar_wait(&s_full[s], (j >> 1) & 1)) { attn_give_up(6); failed = 1; ok = false; break; }
+            if (!mbar_wait(&s_full[x], j & 1)) { attn_give_up(6); failed = 1; ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int t0 = k_begin + j * kKeys;
             const bool need_mask = (t0 + kKeys - 1 > pos0) || (a.window > 0 && t0 < pos_last - a.window + 1);
-            const uint32_t s_addr = lane_addr + s * 128;
-            uint32_t sc[kCols];
-            load_cols(s_addr, sc);
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&s_empty[s]);                                    // S of this buffer is in registers now
-            float mx = need_mask ? row_max<true>(sc, k0, row_pos, row_lo) : row_max<false>(sc, k0, row_pos, row_lo);
-            float other;
-            if (!exchange(s, j + 1, mx, other)) { attn_give_up(8); failed = 1; ok = false; break; }
-            mx = fmaxf(mx, other);
-            const float m_new = fmaxf(m, mx * a.sl);
-            const float mu = m_new == -INFINITY ? 0.f : m_new;      // a row with no visible key yet
-            const float corr = ex2(m - mu);
-            m = m_new;
-            // the P tile is free once P V of the previous tile has read it
-            if (j >= 1 && !mbar_wait(&p_empty, (j - 1) & 1)) { attn_give_up(7); failed = 1; ok = false; break; }
-            const float sum = need_mask ? row_exp<true>(sc, p_half, row, a.sl, mu, k0, row_pos, row_lo)
-                                        : row_exp<false>(sc, p_half, row, a.sl, mu, k0, row_pos, row_lo);
-            l = l * corr + sum;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P must be visible to the tensor core
-            mbar_arrive(&p_full);
-            if (j >= 1 && !fold(j - 1, corr_prev)) { ok = false; break; }
-            corr_prev = corr;
-        }
-        if (ok) ok = fold(n_tiles - 1, corr_prev);
-        // the row sum is the two halves' sums (both are relative to the same running maximum)
-        float l_other = 0.f;
-        if (ok && !exchange(0, n_tiles + 1, l, l_other)) { attn_give_up(9); failed = 1; ok = false; }
-        if (ok && !failed && row < rows) {
-            const float inv = 1.0f / (l + l_other);
-            bf16* dst = a.out + (size_t)(tok0 + row) * a.out_stride + (size_t)h * kDim + half * kCols;
+            // Two passes over the row of S in chunks of 32 columns, each chunk's load issued while the chunk
+            // before it is worked on: pass 1 takes the maximum, pass 2 exponentiates and writes P.
+            uint32_t ca[32], cb[32];
+            auto pass_max = [&](auto tag) {
+                constexpr bool MASK = decltype(tag)::value;
+                float mx = -INFINITY;
+                tmem_ld32(s_addr, ca);
+#pragma unroll 1
+                for (int c0 = 0; c0 < kKeys; c0 += 64) {
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    tmem_ld32(s_addr + c0 + 32, cb);
+                    mx = chunk_max<MASK>(ca, t0 + c0, row_pos, row_lo, mx);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (c0 + 64 < kKeys) tmem_ld32(s_addr + c0 + 64, ca);
+                    mx = chunk_max<MASK>(cb, t0 + c0 + 32, row_pos, row_lo, mx);
+                }
+                return mx;
+            };
+            const float mx = need_mask ? pass_max(std::true_type{}) : pass_max(std::false_type{});
+            tmem_ld32(s_addr, ca);                                   // pass 2's first chunk, in flight during the decision
+            // move the reference only when the maximum has grown by more than the step (always from -inf)
+            const float m_tile = mx * a.sl;
+            const bool move = m_tile > m + kRescaleStep || (m == -INFINITY && m_tile > -INFINITY);
+            if (j > 0 && __any_sync(0xffffffffu, move)) {
+                // O of the tiles so far must be complete before its rows are scaled
+                if (!mbar_wait(&o_done[x], (j - 1) & 1)) { attn_give_up(7); failed = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float f = move ? ex2(m - m_tile) : 1.0f;      // 0 when the row had no visible key so far
+#pragma unroll 1
+                for (int c = 0; c < kDim; c += 16) {
+                    uint32_t o[16];
+                    tmem_ld16(o_addr + c, o);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int d = 0; d < kCols; d += 8) {
-                *reinterpret_cast<uint4*>(dst + d) =
-                    make_uint4(pack2(acc[d] * inv, acc[d + 1] * inv), pack2(acc[d + 2] * inv, acc[d + 3] * inv),
-                               pack2(acc[d + 4] * inv, acc[d + 5] * inv), pack2(acc[d + 6] * inv, acc[d + 7] * inv));
+                    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                    tmem_st16(o_addr + c, o);
+                }
+                l *= f;
+            }
+            if (move) m = m_tile;
+            const float mu = m == -INFINITY ? 0.f : m;      // a row with no visible key yet
+            float sums[4] = {0.f, 0.f, 0.f, 0.f};
+            auto pass_exp = [&](auto tag) {
+                constexpr bool MASK = decltype(tag)::value;
+                uint32_t packed[16];
+#pragma unroll 1
+                for (int c0 = 0; c0 < kKeys; c0 += 64) {
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    tmem_ld32(s_addr + c0 + 32, cb);
+                    chunk_exp<MASK>(ca, packed, a.sl, mu, t0 + c0, row_pos, row_lo, sums);
+                    tmem_st16(s_addr + (c0 >> 1), packed);           // keys c0 .. c0+31 as 16 columns of two bfloat16
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (c0 + 64 < kKeys) tmem_ld32(s_addr + c0 + 64, ca);
+                    chunk_exp<MASK>(cb, packed, a.sl, mu, t0 + c0 + 32, row_pos, row_lo, sums);
+                    tmem_st16(s_addr + (c0 >> 1) + 16, packed);
+                }
+            };
+            if (need_mask) pass_exp(std::true_type{}); else pass_exp(std::false_type{});
+            const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            l += sum;
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[x]);              // one arrival per warp
+        }
+        if (ok && !mbar_wait(&o_done[x], (n_tiles - 1) & 1)) { attn_give_up(8); failed = 1; ok = false; }
+        if (ok && !failed) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = 1.0f / l;
+            bf16* dst = a.out + (size_t)(tok0 + row) * a.out_stride + (size_t)(head_a + x) * kDim;
+#pragma unroll 1
+            for (int c = 0; c < kDim; c += 32) {
+                uint32_t o[32];
+                tmem_ld32(o_addr + c, o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < rows) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 8)
+                        *reinterpret_cast<uint4*>(dst + c + d) =
+                            make_uint4(pack2(__uint_as_float(o[d]) * inv, __uint_as_float(o[d + 1]) * inv),
+                                       pack2(__uint_as_float(o[d + 2]) * inv, __uint_as_float(o[d + 3]) * inv),
+                                       pack2(__uint_as_float(o[d + 4]) * inv, __uint_as_float(o[d + 5]) * inv),
+                                       pack2(__uint_as_float(o[d + 6]) * inv, __uint_as_float(o[d + 7]) * inv));
+                }
             }
         }
     }
@@ -367,6 +408,7 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
     a.page_size = page_size;
     a.window = window;
     a.sl = scale * 1.4426950408889634f;
+    a.pairs = (heads / kv_heads + 1) / 2;
     const size_t smem = 6 * kTileBytes + 1024;
     static bool configured = false;
     if (!configured) {
@@ -374,7 +416,7 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
         if (e != cudaSuccess) LLM_FAIL(-2, "attention_prefill_tcgen05: %s", cudaGetErrorString(e));
         configured = true;
     }
-    llm_launch(attn_prefill_tcgen05_kernel, dim3(n_tiles, heads), kThreads, smem, stream, mq, mkv, a);
+    llm_launch(attn_prefill_tcgen05_kernel, dim3(n_tiles, kv_heads * a.pairs), kThreads, smem, stream, mq, mkv, a);
     LLM_CHECK_LAUNCH("attention_prefill_tcgen05");
     return 0;
 }

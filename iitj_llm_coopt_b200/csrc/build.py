@@ -28,6 +28,7 @@ LIB_NAME = "libllm_kernels.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr", "-diag-suppress", "177"]
+NVCC_FLAGS += os.environ.get("IITJ_NVCC_FLAGS", "").split()      # extra flags, e.g. -D switches for measurements
 
 
 class BuildError(RuntimeError):
