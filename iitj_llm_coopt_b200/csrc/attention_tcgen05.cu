@@ -119,7 +119,8 @@ struct AttnArgs {
     bf16* out;
     int out_stride;
     int heads, kv_heads, page_size, window;
-    int pairs;                    // CTAs per key/value group: ceil(heads per group / 2)
+    int per_cta;                  // query heads per CTA: 2 (ping-pong), or 1 when that fills more of the GPU
+    int pairs;                    // CTAs per key/value group: ceil(heads per group / per_cta)
     float sl;                     // softmax scale * log2(e)
 };
 
@@ -140,8 +141,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int tok0 = td.x, rows = td.y, pos0 = td.z, req = td.w;
     const int group = a.heads / a.kv_heads;
     const int hk = blockIdx.y / a.pairs, pr = blockIdx.y - hk * a.pairs;
-    const int head_a = hk * group + 2 * pr;
-    const int n_heads = (2 * pr + 1 < group) ? 2 : 1;              // heads this CTA serves
+    const int head_a = hk * group + a.per_cta * pr;
+    const int n_heads = (a.per_cta == 2 && 2 * pr + 1 < group) ? 2 : 1;      // heads this CTA serves
     const int pos_last = pos0 + rows - 1;
     const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
     const int k_begin = lo0 & ~(kKeys - 1);
@@ -214,25 +215,27 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         constexpr uint32_t idesc_o = umma_idesc(kRows, kDim) | (1u << 16);             // P from TMEM, V MN-major
         bool ok = mbar_wait(&q_full, 0);
         if (!ok) { attn_give_up(2); failed = 1; }
+        // Descriptors are built once; inside the loops only constants are added.
+        const uint64_t dq[2] = {umma_desc(q_tile[0]), umma_desc(q_tile[1])};
+        const uint64_t dk[2] = {umma_desc(k_tile[0]), umma_desc(k_tile[1])};
+        const uint64_t dv[2] = {umma_desc_mn(v_tile[0], kHalfBytes), umma_desc_mn(v_tile[1], kHalfBytes)};
         auto issue_s = [&](int x, int j) {
-            const int s = j & 1;
+            const uint64_t da = x ? dq[1] : dq[0], db = (j & 1) ? dk[1] : dk[0];
 #pragma unroll
             for (int kk = 0; kk < kDim / 16; ++kk) {
-                const uint64_t da = umma_desc(q_tile[x] + (kk >> 2) * kHalfBytes) + 2 * (kk & 3);
-                const uint64_t db = umma_desc(k_tile[s] + (kk >> 2) * kHalfBytes) + 2 * (kk & 3);
-                umma_f16(tmem + x * 128, da, db, idesc_s, kk > 0 ? 1u : 0u);
+                const uint64_t off = (uint64_t)((kk >> 2) * (kHalfBytes >> 4) + 2 * (kk & 3));
+                umma_f16(tmem + x * 128, da + off, db + off, idesc_s, kk > 0 ? 1u : 0u);
             }
             umma_commit(&s_full[x]);
         };
         auto issue_pv = [&](int x, int j) {
-            const int s = j & 1;
             if (!mbar_wait(&p_full[x], j & 1)) { attn_give_up(3); failed = 1; return false; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t db = (j & 1) ? dv[1] : dv[0];
 #pragma unroll
-            for (int kk = 0; kk < kKeys / 16; ++kk) {
-                const uint64_t db = umma_desc_mn(v_tile[s] + kk * 16 * 128, kHalfBytes);
-                umma_f16_ts(tmem + 256 + x * 128, tmem + x * 128 + kk * 8, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-            }
+            for (int kk = 0; kk < kKeys / 16; ++kk)
+                umma_f16_ts(tmem + 256 + x * 128, tmem + x * 128 + kk * 8, db + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_o,
+                            (j > 0 || kk > 0) ? 1u : 0u);
             umma_commit(&o_done[x]);
             return true;
         };
@@ -408,7 +411,14 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
     a.page_size = page_size;
     a.window = window;
     a.sl = scale * 1.4426950408889634f;
-    a.pairs = (heads / kv_heads + 1) / 2;
+    // Two heads per CTA share each key/value tile and keep the tensor core busier; with few CTAs one head per
+    // CTA spreads the work over more SMs (512 queries over 8192 keys at 32 heads: 168 -> 125 us).
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int group = heads / kv_heads;
+    a.per_cta = (group >= 2 && (long long)n_tiles * kv_heads * ((group + 1) / 2) >= sms) ? 2 : 1;
+    a.pairs = (group + a.per_cta - 1) / a.per_cta;
     const size_t smem = 6 * kTileBytes + 1024;
     static bool configured = false;
     if (!configured) {
