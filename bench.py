@@ -4,11 +4,12 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 8192] [--layers L]
 
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch (default 8)
-with `context` tokens per request already in the cache, timed on the device with CUDA
-events around each decode step (model step + sampling kernel).  `e2e` is the same metric
-through the Python entry point (`LLM.generate`: host token ids in, host token ids out,
-prefill included in the run but not in the decode rate, which is counted from the first
-to the last generated token).  `prefill` is one 2,048-token prompt in one step; `roofline`
+with `context` tokens per request already in the cache, timed on the device with one pair
+of CUDA events around the K decode steps (model step + sampling kernel, run back to back:
+each step takes its tokens on the device from the ids the step before sampled).  `e2e` is
+the same metric through the engine's public entry point (host token ids in, host token ids
+out every step; the prompts' prefill and W warm-up decode steps run first, then the rate is
+counted over the timed decode steps).  `prefill` is one 2,048-token prompt in one step; `roofline`
 relates the decode step's mandatory HBM reads to its time; `points` holds decode at batch
 1 and 64.  Weights are random (seeded, drawn on the device), token ids are random.
 
@@ -188,23 +189,29 @@ def main() -> int:
             cache.ensure(r, C)
             cache.advance(r, C)
         toks = torch.randint(0, typed.vocab_size, (batch,), generator=gen).tolist()
-        rows = [(0.0, 0, 0)] * batch
-        times, launches = [], 0
+        # Steps run back to back as in serving: each step's input tokens are the ids the sampling kernel of the
+        # step before left on the device (no host round trip in between); one pair of events brackets the timed
+        # steps, with a synchronize on both sides.
+        prev = None
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches = 0
         for it in range(warmup + steps):
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            entries = [StepEntry(r, [t], [0]) for r, t in zip(ids, toks)]
-            l0 = kernels.launches
-            torch.cuda.synchronize()
-            start.record()
-            logits = runner.step(entries)
-            out, host = sampler._buffers(batch)
+            if it == warmup:
+                torch.cuda.synchronize()
+                launches = kernels.launches
+                start.record()
+            if prev is None:
+                entries = [StepEntry(r, [t], [0]) for r, t in zip(ids, toks)]
+            else:
+                entries = [StepEntry(r, [0], [0], source_rows=[i]) for i, r in enumerate(ids)]
+            logits = runner.step(entries, prev_ids=prev)
+            out, _ = sampler._buffers(batch)
             kernels.sample(logits, None, None, out)
-            end.record()
-            torch.cuda.synchronize()
-            toks = out.tolist()
-            if it >= warmup:
-                times.append(start.elapsed_time(end))
-                launches += kernels.launches - l0
+            prev = out
+        end.record()
+        torch.cuda.synchronize()
+        times = [start.elapsed_time(end) / steps] * steps
+        launches = kernels.launches - launches
         for r in ids:
             cache.release(r)
             runner.forget(r)
@@ -265,25 +272,25 @@ def main() -> int:
         llm.engine = engine
         prompts = [torch.randint(0, typed.vocab_size, (C,), generator=gen).tolist() for _ in range(B)]
         stamps = []
-        first = {}
 
         def on_out(seq, new, fin):
-            now = time.perf_counter()
-            first.setdefault(seq.seq_id, now)
-            stamps.append(now)
+            stamps.append(time.perf_counter())
 
         budget = engine.policy.max_batched_tokens
         engine.policy.max_batched_tokens = B * C          # all prompts in one prefill step, then decode steps only
-        KE = max(K, 96)                                    # enough steps to amortise the one-off graph capture
-        seqs = [engine.new_sequence(p, KE + 1, 0.0, True, None, on_out) for p in prompts]
+        WE, KE = max(W, 4), max(K, 64)                     # untimed decode steps (graph capture among them), timed ones
+        seqs = [engine.new_sequence(p, WE + KE + 1, 0.0, True, None, on_out) for p in prompts]
         engine.run_until_done()
         torch.cuda.synchronize()
         engine.policy.max_batched_tokens = budget
-        t_first, t_last = max(first.values()), max(stamps)
-        decoded = sum(len(s.tokens) - s.prompt_len - 1 for s in seqs)
+        # every decode step hands one token of each request to the callback: the timed region runs from the
+        # last callback of warm-up step WE to the last callback of all (KE steps of B tokens)
+        per_step = sorted(stamps)
+        t_start, t_last = per_step[B * (WE + 1) - 1], per_step[-1]
+        decoded = len(per_step) - B * (WE + 1)
         h2d = (4 * B + (B + 1) + 4 * B + B * max(16, 1 << ((-(-(C + K) // page)) - 1).bit_length())) * 4
-        e2e = {"value": decoded / (t_last - t_first), "unit": "tok/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": 4 * B}
+        e2e = {"value": decoded / (t_last - t_start), "unit": "tok/s", "steps": decoded // B, "warmup": WE,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B}
 
     line = {
         "metric": "decode tok/s at batch 8 (Llama 3.1 8B shape, 8192-token contexts); prefill and batch 1/64 alongside",
