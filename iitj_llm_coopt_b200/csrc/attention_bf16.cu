@@ -313,7 +313,6 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    int heads, int kv_heads, int page_size, int page_shift, int window, float sl, int keys_per_split,
                    int max_splits) {
     pdl_trigger();
-    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* kv = reinterpret_cast<bf16*>(smem_raw);                 // [kStages][K,V][64][D]
     const int split = blockIdx.x, hk = blockIdx.y, item = blockIdx.z;
@@ -334,15 +333,21 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     auto stage_k = [&](int s) { return kv + (size_t)s * 2 * kTile * D; };
     auto stage_v = [&](int s) { return kv + (size_t)s * 2 * kTile * D + kTile * D; };
 
+    // The step's index arrays were copied in before its first kernel, and keys and values of positions before
+    // `pos` were stored by earlier steps: tiles that end before `pos` are requested ahead of the wait for the
+    // kernel before this one (which stores the token's own key and value, and writes the queries).
     int pg[TileMap<D>::ITERS];
+    bool waited = false;
 #pragma unroll
     for (int s = 0; s < kStages - 1; ++s) {
+        if (!waited && c0 + (s + 1) * kTile > pos) { pdl_wait(); waited = true; }
         if (s < n_tiles) {
             tile_pages<D>(pg, table, c0 + s * kTile, pos, page_size, page_shift);
             load_kv_tiles<D>(stage_k(s), stage_v(s), kplane, plane, pg, c0 + s * kTile, pos, page_size, page_shift, 2 * plane);
         }
         cp_async_commit();
     }
+    if (!waited) pdl_wait();
     // page ids of the tile that the first iteration will request, fetched one iteration ahead from here on
     if (kStages - 1 < n_tiles) tile_pages<D>(pg, table, c0 + (kStages - 1) * kTile, pos, page_size, page_shift);
     // the group's query heads are rows 0 .. G-1 of the MMA tile; the other rows are zero
@@ -600,3 +605,5 @@ LLM_API int llm_attention_decode_bf16_static(const void* q, int q_stride, const 
                                      positions, part_o, part_ml, out, out_stride, heads, kv_heads, head_dim, page_size,
                                      window, scale, keys_per_split, max_splits, stream);
 }
+
+LLM_TRACE_EXPORT(attention_bf16)

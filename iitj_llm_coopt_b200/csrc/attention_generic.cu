@@ -147,3 +147,5 @@ LLM_API int llm_attention_generic(const void* q, int q_stride, const void* cache
         return 0;
     });
 }
+
+LLM_TRACE_EXPORT(attention_generic)

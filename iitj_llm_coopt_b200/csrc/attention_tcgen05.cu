@@ -437,3 +437,5 @@ LLM_API int llm_attention_tcgen05_status() {
     if (v) cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int));
     return v;
 }
+
+LLM_TRACE_EXPORT(attention_tcgen05)

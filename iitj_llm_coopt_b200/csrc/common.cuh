@@ -73,8 +73,38 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
 // earlier kernel has completed and its writes are visible.  pdl_trigger() at a kernel's top
 // tells the scheduler that the next kernel may start as soon as resources allow.  Both are
 // no-ops in a launch without the attribute.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#ifdef LLM_TRACE
+// Measurement build (-DLLM_TRACE): the first thread of every kernel's first block notes the global timer when
+// the kernel starts and when its wait for the kernel before it returns; one buffer per source file, read
+// with llm_trace_dump_<file>().
+namespace {
+__device__ unsigned long long llm_trace_buf[1 << 14];
+__device__ unsigned int llm_trace_n;
+__device__ __forceinline__ void llm_trace_mark(unsigned what) {
+    if (threadIdx.x == 0 && threadIdx.y == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        const unsigned i = atomicAdd(&llm_trace_n, 1u);
+        if (i < (1u << 14)) llm_trace_buf[i] = (t << 4) | what;
+    }
+}
+}  // namespace
+#define LLM_TRACE_EXPORT(name)                                                                          \
+    LLM_API int llm_trace_dump_##name(unsigned long long* host, int cap) {                              \
+        unsigned int n = 0, zero = 0;                                                                   \
+        cudaMemcpyFromSymbol(&n, llm_trace_n, sizeof(n));                                               \
+        if ((int)n > cap) n = cap;                                                                      \
+        if (n > (1u << 14)) n = 1u << 14;                                                               \
+        cudaMemcpyFromSymbol(host, llm_trace_buf, sizeof(unsigned long long) * n);                      \
+        cudaMemcpyToSymbol(llm_trace_n, &zero, sizeof(zero));                                           \
+        return (int)n;                                                                                  \
+    }
+#else
+#define LLM_TRACE_EXPORT(name)
+__device__ __forceinline__ void llm_trace_mark(unsigned) {}
+#endif
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); llm_trace_mark(1); }
+__device__ __forceinline__ void pdl_trigger() { llm_trace_mark(0); asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 bool llm_pdl_enabled();  // runtime.cu
 
@@ -94,6 +124,44 @@ static inline cudaError_t llm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 b
         cfg.numAttrs = 1;
     }
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// The same for a kernel whose blocks form clusters of `cluster_x` along x (distributed shared memory).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t llm_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                             unsigned cluster_x, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_x; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.numAttrs = 1;
+    if (llm_pdl_enabled()) {
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
+    cfg.attrs = attr;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// ---- thread-block clusters (device) -------------------------------------------------------
+__device__ __forceinline__ uint32_t llm_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void llm_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Stores `v` at the same shared-memory location in block `rank` of this cluster.
+__device__ __forceinline__ void llm_cluster_write(float* local, uint32_t rank, float v) {
+    uint32_t addr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
 template <typename F> static inline int llm_dispatch_dtype(int dtype, F&& f) {

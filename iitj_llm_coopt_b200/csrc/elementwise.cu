@@ -5,6 +5,8 @@
 // statistics are computed in float32, only the norm's output is rounded to the model type.
 #include "common.cuh"
 
+#include <stdlib.h>
+
 // ---------------------------------------------------------------------------------------
 // embedding: out[t, :] = scale * table[ids[t], :]   (float32 residual stream)
 // replaces F.embedding of the reference (engine/model.py:191)
@@ -39,11 +41,14 @@ LLM_API int llm_embed(const int* ids, const void* table, int table_dtype, float*
 //     residual[s] = v                     (only when rows == nullptr and delta != nullptr)
 //     out[r] = v * rsqrt(mean(v^2) + eps) * weight
 // Formula: engine/model.py:85-89; the add-then-norm form: engine/model.py:236.
+// With `splits` > 0 delta is the float32 partial sums [splits][rows][width] of a matrix product split along
+// k (`split_stride` elements apart); they are added here in split order, which saves the product its own
+// reduction kernel.
 // ---------------------------------------------------------------------------------------
 template <typename TD, typename TW>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                    const int* __restrict__ rows, const TW* __restrict__ weight,
-                                   TD* __restrict__ out, int width, float eps) {
+                                   TD* __restrict__ out, int width, float eps, int splits, size_t split_stride) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float row_buf[];  // width floats
@@ -52,11 +57,18 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     const size_t s = rows ? (size_t)rows[r] : (size_t)r;
     float* res = residual + s * width;
     const TD* dl = delta ? delta + s * width : nullptr;
+    const float* parts = splits > 0 ? reinterpret_cast<const float*>(delta) + s * width : nullptr;
     float ss = 0.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float v = res[i];
         if (dl) {
-            v += to_f32(dl[i]);
+            if (parts) {
+                float d = 0.f;
+                for (int k = 0; k < splits; ++k) d += parts[(size_t)k * split_stride + i];
+                v += d;
+            } else {
+                v += to_f32(dl[i]);
+            }
             if (!rows) res[i] = v;
         }
         row_buf[i] = v;
@@ -91,10 +103,25 @@ template <> struct Vec4<__nv_bfloat16> {
     }
 };
 
+// Sum of up to kMaxParts partial sums of four neighbouring elements, all loads in flight at once.
+constexpr int kMaxParts = 8;
+
+__device__ __forceinline__ float4 sum_parts4(const float* p, int splits, size_t split_stride) {
+    float4 e[kMaxParts];
+#pragma unroll
+    for (int k = 0; k < kMaxParts; ++k)
+        if (k < splits) e[k] = *reinterpret_cast<const float4*>(p + (size_t)k * split_stride);
+    float4 a = e[0];
+#pragma unroll
+    for (int k = 1; k < kMaxParts; ++k)
+        if (k < splits) { a.x += e[k].x; a.y += e[k].y; a.z += e[k].z; a.w += e[k].w; }
+    return a;
+}
+
 template <typename TD, typename TW, int PER_THREAD>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+__global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                        const int* __restrict__ rows, const TW* __restrict__ weight,
-                                       TD* __restrict__ out, int width, float eps) {
+                                       TD* __restrict__ out, int width, float eps, int splits, size_t split_stride) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[32];
@@ -102,6 +129,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* _
     const size_t s = rows ? (size_t)rows[r] : (size_t)r;
     float* res = residual + s * width;
     const TD* dl = delta ? delta + s * width : nullptr;
+    const float* parts = splits > 0 ? reinterpret_cast<const float*>(delta) + s * width : nullptr;
     float4 v[PER_THREAD];
     float ss = 0.f;
 #pragma unroll
@@ -110,7 +138,10 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* _
         v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i < width) {
             v[j] = Vec4<float>::load(res + i);
-            if (dl) {
+            if (parts) {
+                const float4 d = sum_parts4(parts + i, splits, split_stride);
+                v[j].x += d.x; v[j].y += d.y; v[j].z += d.z; v[j].w += d.w;
+            } else if (dl) {
                 const float4 d = Vec4<TD>::load(dl + i);
                 v[j].x += d.x; v[j].y += d.y; v[j].z += d.z; v[j].w += d.w;
             }
@@ -137,26 +168,104 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* _
     }
 }
 
+// Few rows (decode): a row is shared by a cluster of blocks, each with width / cluster columns, so that the
+// reads (above all of partial sums) are spread over more SMs; each block pushes its sum of squares into the
+// shared memory of all blocks of the cluster, and after one cluster barrier every block adds them in block order.
+template <typename TD, typename TW, int PER_THREAD>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_cluster_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const int* __restrict__ rows,
+                           const TW* __restrict__ weight, TD* __restrict__ out, int width, float eps, int splits,
+                           size_t split_stride, int cluster) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[32];
+    __shared__ float all_ss[8];               // the sums of squares of the cluster's blocks, pushed here by each of them
+    const int c = (int)llm_cluster_rank();
+    const int r = blockIdx.x / cluster;
+    const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+    float* res = residual + s * width;
+    const TD* dl = delta ? delta + s * width : nullptr;
+    const float* parts = splits > 0 ? reinterpret_cast<const float*>(delta) + s * width : nullptr;
+    const int cols = width / cluster, col0 = c * cols;       // this block's columns (a multiple of 4)
+    float4 v[PER_THREAD], w[PER_THREAD];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER_THREAD; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < cols) {
+            v[j] = Vec4<float>::load(res + col0 + i);
+            w[j] = Vec4<TW>::load(weight + col0 + i);       // asked for now, used after the sums have met
+            if (parts) {
+                const float4 d = sum_parts4(parts + col0 + i, splits, split_stride);
+                v[j].x += d.x; v[j].y += d.y; v[j].z += d.z; v[j].w += d.w;
+            } else if (dl) {
+                const float4 d = Vec4<TD>::load(dl + col0 + i);
+                v[j].x += d.x; v[j].y += d.y; v[j].z += d.z; v[j].w += d.w;
+            }
+            if (dl && !rows) Vec4<float>::store(res + col0 + i, v[j]);
+            ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+        }
+    }
+    const float mine = block_sum(ss, red);
+    if ((int)threadIdx.x < cluster) llm_cluster_write(&all_ss[c], (uint32_t)threadIdx.x, mine);
+    llm_cluster_sync();                       // every block's sum has arrived in every block; no remote access after this
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        if (k < cluster) total += all_ss[k];  // in block order in every block: the same total everywhere
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+    TD* o = out + (size_t)r * width + col0;
+#pragma unroll
+    for (int j = 0; j < PER_THREAD; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        if (i < cols)
+            Vec4<TD>::store(o + i, make_float4(v[j].x * inv * w[j].x, v[j].y * inv * w[j].y, v[j].z * inv * w[j].z, v[j].w * inv * w[j].w));
+    }
+}
+
 LLM_API int llm_add_rmsnorm(float* residual, const void* delta, const int* rows, const void* weight,
                             int weight_dtype, void* out, int dtype, int out_rows, int width, float eps,
-                            cudaStream_t stream) {
+                            int splits, long long split_stride, cudaStream_t stream) {
     if (out_rows == 0) return 0;
+    if (splits > 0 && (!delta || split_stride % 4 || splits > kMaxParts))
+        LLM_FAIL(-1, "add_rmsnorm: partial sums need a pointer, a stride that is a multiple of 4 and at most %d splits (%d)", kMaxParts, splits);
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) LLM_FAIL(-1, "add_rmsnorm: width %d is larger than 51200", width);
     return llm_dispatch_dtype(dtype, [&](auto tag) {
         using TD = decltype(tag);
         return llm_dispatch_dtype(weight_dtype, [&](auto wtag) {
             using TW = decltype(wtag);
+            if (width % 4 == 0 && out_rows < 512) {
+                // few rows: clusters of up to eight blocks per row, up to 256 threads with up to 4 float4 each
+                static const int max_cluster = getenv("IITJ_NORM_CLUSTER") ? atoi(getenv("IITJ_NORM_CLUSTER")) : 8;
+                int cluster = max_cluster;
+                while (cluster > 1 && (width % (4 * cluster) || width / (4 * cluster) < 32)) cluster >>= 1;
+                const int vecs = width / (4 * cluster);
+                int threads = (vecs + 31) / 32 * 32;
+                if (threads > 256) threads = 256;
+                const int per = (vecs + threads - 1) / threads;
+                if (per <= 4) {
+                    auto go = [&](auto kern) {
+                        llm_launch_cluster(kern, out_rows * cluster, threads, 0, stream, cluster, residual, (const TD*)delta, rows,
+                                           (const TW*)weight, (TD*)out, width, eps, splits, (size_t)split_stride, cluster);
+                    };
+                    if (per <= 1) go(add_rmsnorm_cluster_kernel<TD, TW, 1>);
+                    else if (per <= 2) go(add_rmsnorm_cluster_kernel<TD, TW, 2>);
+                    else go(add_rmsnorm_cluster_kernel<TD, TW, 4>);
+                    LLM_CHECK_LAUNCH("add_rmsnorm");
+                    return 0;
+                }
+            }
             if (width % 4 == 0 && width <= 4 * 256 * 16) {
-                // Many rows: 256 threads with up to 16 float4 each (bytes in flight per SM).  Few rows (decode):
-                // up to 1024 threads so that a row is one round of loads (latency).
+                // many rows: one block of 256 threads per row with up to 16 float4 each (bytes in flight per SM)
                 const int vecs = width / 4;
                 int threads = (vecs + 31) / 32 * 32;
-                const int cap = out_rows >= 512 ? 256 : 1024;
-                if (threads > cap) threads = cap;
+                if (threads > 256) threads = 256;
                 const int per = (vecs + threads - 1) / threads;
                 auto go = [&](auto kern) {
-                    llm_launch(kern, out_rows, threads, 0, stream, residual, (const TD*)delta, rows, (const TW*)weight, (TD*)out, width, eps);
+                    llm_launch(kern, out_rows, threads, 0, stream, residual, (const TD*)delta, rows, (const TW*)weight, (TD*)out, width, eps,
+                               splits, (size_t)split_stride);
                 };
                 if (per <= 1) go(add_rmsnorm_vec_kernel<TD, TW, 1>);
                 else if (per <= 2) go(add_rmsnorm_vec_kernel<TD, TW, 2>);
@@ -172,7 +281,7 @@ LLM_API int llm_add_rmsnorm(float* residual, const void* delta, const int* rows,
                 if (e != cudaSuccess) LLM_FAIL(-2, "add_rmsnorm: %s", cudaGetErrorString(e));
             }
             llm_launch(kern, out_rows, 256, smem, stream, residual, (const TD*)delta, rows, (const TW*)weight,
-                                                  (TD*)out, width, eps);
+                                                  (TD*)out, width, eps, splits, (size_t)split_stride);
             LLM_CHECK_LAUNCH("add_rmsnorm");
             return 0;
         });
@@ -276,6 +385,70 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
     }
 }
 
+// The same for a qkv that still lies in the float32 partial sums [splits][tokens][row_width] of a k-split
+// product (rotary_dim == head_dim, head_dim % 8 == 0, at most kMaxParts splits): the sums are taken here in
+// split order, the rotated queries go to `q_out` (row width as qkv), keys and values to the cache.  One block
+// per token and group of eight heads; every thread has all loads of its item in flight at once.
+constexpr int kSumHeads = 8;
+
+template <typename T>
+__global__ void rope_store_sum_kernel(const float* __restrict__ parts, int splits, size_t split_stride,
+                                      T* __restrict__ q_out, const int* __restrict__ positions,
+                                      const float* __restrict__ inv_freq, const float* __restrict__ cos_table,
+                                      const float* __restrict__ sin_table, const int* __restrict__ slots,
+                                      T* __restrict__ cache, int heads, int kv_heads, int head_dim, int page_size) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int half = head_dim / 2, hp = half / 4, per_head = head_dim / 4;
+    const int all_heads = heads + 2 * kv_heads, rot_heads = heads + kv_heads;
+    const int row_width = all_heads * head_dim;
+    const float* row = parts + (size_t)t * row_width;
+    T* qrow = q_out + (size_t)t * row_width;
+    const int slot = slots ? slots[t] : -1;
+    const size_t plane = (size_t)kv_heads * page_size * head_dim;
+    size_t kbase = 0;
+    if (slot >= 0) {
+        const int page = slot / page_size, off = slot % page_size;
+        kbase = (size_t)page * 2 * plane + (size_t)off * head_dim;
+    }
+    const size_t head_stride = (size_t)page_size * head_dim;
+    const int h0 = blockIdx.y * kSumHeads;
+    // items of this block: per rotated head `hp` pairs of four dims, per value head `per_head` groups of four
+    for (int w = threadIdx.x; w < kSumHeads * per_head; w += blockDim.x) {
+        const int h = h0 + w / per_head, j = w % per_head;
+        if (h >= all_heads) break;
+        if (h < rot_heads) {
+            if (j >= hp) continue;
+            const int i = j * 4;
+            const float4 a = sum_parts4(row + h * head_dim + i, splits, split_stride);
+            const float4 b = sum_parts4(row + h * head_dim + i + half, splits, split_stride);
+            float4 c, sg;
+            if (cos_table) {
+                c = *reinterpret_cast<const float4*>(cos_table + (size_t)t * half + i);
+                sg = *reinterpret_cast<const float4*>(sin_table + (size_t)t * half + i);
+            } else {
+                const float pos = (float)positions[t];
+                sincosf(pos * inv_freq[i], &sg.x, &c.x); sincosf(pos * inv_freq[i + 1], &sg.y, &c.y);
+                sincosf(pos * inv_freq[i + 2], &sg.z, &c.z); sincosf(pos * inv_freq[i + 3], &sg.w, &c.w);
+            }
+            const float4 lo4 = make_float4(a.x * c.x - b.x * sg.x, a.y * c.y - b.y * sg.y, a.z * c.z - b.z * sg.z, a.w * c.w - b.w * sg.w);
+            const float4 hi4 = make_float4(b.x * c.x + a.x * sg.x, b.y * c.y + a.y * sg.y, b.z * c.z + a.z * sg.z, b.w * c.w + a.w * sg.w);
+            T* dst = nullptr;
+            if (h < heads) dst = qrow + (size_t)h * head_dim;
+            else if (slot >= 0) dst = cache + kbase + (size_t)(h - heads) * head_stride;
+            if (dst) {
+                Vec4<T>::store(dst + i, lo4);
+                Vec4<T>::store(dst + i + half, hi4);
+            }
+        } else if (slot >= 0) {
+            const int i = j * 4;
+            Vec4<T>::store(cache + kbase + plane + (size_t)(h - rot_heads) * head_stride + i,
+                           sum_parts4(row + h * head_dim + i, splits, split_stride));
+        }
+    }
+}
+
 // cos[t, i] = cos(positions[t] * inv_freq[i]), sin likewise: computed once per step and shared by all
 // layers with the same position encoding (float32 angles, float32 sincosf).
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
@@ -299,8 +472,21 @@ LLM_API int llm_rope_table(const int* positions, const float* inv_freq, float* c
 
 LLM_API int llm_rope_store(void* qkv, const int* positions, const float* inv_freq, const float* cos_table,
                            const float* sin_table, const int* slots, void* cache, int dtype, int tokens, int heads, int kv_heads, int head_dim,
-                           int rotary_dim, int page_size, cudaStream_t stream) {
+                           int rotary_dim, int page_size, const float* parts, int splits, long long split_stride, cudaStream_t stream) {
     if (tokens == 0) return 0;
+    if (parts) {
+        if (rotary_dim != head_dim || head_dim % 8 || splits < 1 || splits > kMaxParts || split_stride % 4)
+            LLM_FAIL(-1, "rope_store: partial sums need rotary_dim == head_dim (%d, %d), a multiple of 8, and 1..%d splits (%d)",
+                     rotary_dim, head_dim, kMaxParts, splits);
+        return llm_dispatch_dtype(dtype, [&](auto tag) {
+            using T = decltype(tag);
+            const dim3 grid(tokens, (heads + 2 * kv_heads + kSumHeads - 1) / kSumHeads);
+            llm_launch(rope_store_sum_kernel<T>, grid, 256, 0, stream, parts, splits, (size_t)split_stride, (T*)qkv, positions, inv_freq,
+                       cos_table, sin_table, slots, (T*)cache, heads, kv_heads, head_dim, page_size);
+            LLM_CHECK_LAUNCH("rope_store");
+            return 0;
+        });
+    }
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 3) || head_dim % 16 || head_dim > 256)
         LLM_FAIL(-1, "rope_store: rotary_dim %d must be a multiple of 4 and at most head_dim %d (a multiple of 16 up to 256)",
                  rotary_dim, head_dim);
@@ -366,3 +552,5 @@ LLM_API int llm_silu_mul(const void* gu, void* act, int dtype, int tokens, int i
         return 0;
     });
 }
+
+LLM_TRACE_EXPORT(elementwise)

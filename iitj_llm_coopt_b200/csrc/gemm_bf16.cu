@@ -300,10 +300,12 @@ LLM_API int llm_gemm_bf16_token_tile(int tokens) {
 
 // out = x . w^T.   x [tokens, K] bf16, w [n (or 2n with swiglu), K] bf16.
 // out_f32 == 0: out is bf16 [tokens, ldc]; out_f32 != 0: float32 [tokens, ldc].
-// splits > 1 needs `scratch` with splits * tokens * (swiglu ? 2n : n) floats; the reduction runs right after.
+// splits > 1 needs `scratch` with splits * tokens * (swiglu ? 2n : n) floats; the reduction runs right after,
+// unless `defer` is set: then the partial sums [splits][tokens][n] stay in scratch for the kernel that reads
+// the result (llm_add_rmsnorm, llm_rope_store) and `out` is not written.
 // smem_kb: shared memory of one CTA's ring in KiB (0 = 200: one CTA per SM; about 100 lets two CTAs share an SM).
 LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, int tokens, int n, int K, int ldc,
-                          int swiglu, int splits, float* scratch, int smem_kb, cudaStream_t stream) {
+                          int swiglu, int splits, float* scratch, int smem_kb, int defer, cudaStream_t stream) {
     if (tokens == 0 || n == 0) return 0;
     if (K % 8) LLM_FAIL(-1, "gemm_bf16: K %d must be a multiple of 8", K);
     if (swiglu && out_f32) LLM_FAIL(-1, "gemm_bf16: the SwiGLU variant writes bfloat16");
@@ -342,7 +344,8 @@ LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, 
     }
 #undef LLM_GEMM_CASE
     if (rc) return rc;
-    if (splits > 1) {
+    if (defer && swiglu) LLM_FAIL(-1, "gemm_bf16: the SwiGLU sums cannot be deferred");
+    if (splits > 1 && !defer) {
         const size_t work = (size_t)tokens * (n / 4);
         const int blocks = (int)((work + 255) / 256 < 148 * 8 ? (work + 255) / 256 : 148 * 8);
         if (swiglu)
@@ -364,3 +367,5 @@ LLM_API int llm_gemm_bf16_status() {
     if (v) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
     return v;
 }
+
+LLM_TRACE_EXPORT(gemm_bf16)

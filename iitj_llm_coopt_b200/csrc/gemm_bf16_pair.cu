@@ -570,3 +570,5 @@ LLM_API int llm_gemm_bf16_pair_status() {
     if (v) cudaMemcpyToSymbol(g_pair_status, &zero, sizeof(int));
     return v;
 }
+
+LLM_TRACE_EXPORT(gemm_bf16_pair)

@@ -109,3 +109,5 @@ LLM_API int llm_gemm_f32(const float* A, const float* W, float* C, int M, int N,
     LLM_CHECK_LAUNCH("gemm_f32");
     return 0;
 }
+
+LLM_TRACE_EXPORT(gemm_f32)

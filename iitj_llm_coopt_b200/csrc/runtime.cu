@@ -33,3 +33,5 @@ LLM_API int llm_check_device() {
         LLM_FAIL(-3, "device %d is sm_%d%d; this library holds sm_100a code only", dev, p.major, p.minor);
     return 0;
 }
+
+LLM_TRACE_EXPORT(runtime)

@@ -170,3 +170,5 @@ LLM_API int llm_sample(const float* logits, int ld, const float* temperature, co
     LLM_CHECK_LAUNCH("sample");
     return 0;
 }
+
+LLM_TRACE_EXPORT(sample)

@@ -36,10 +36,10 @@ _SIGNATURES = {
     "llm_abi_version": [],
     "llm_embed": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "llm_add_rmsnorm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
-                        _c_float, _c_void_p],
+                        _c_float, _c_int, ctypes.c_longlong, _c_void_p],
     "llm_rope_table": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
     "llm_rope_store": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
-                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, ctypes.c_longlong, _c_void_p],
     "llm_silu_mul": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "llm_attention_generic": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
@@ -57,7 +57,7 @@ _SIGNATURES = {
                      _c_void_p],
     "llm_gemm_bf16_token_tile": [_c_int],
     "llm_gemm_bf16": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
-                      _c_int, _c_void_p],
+                      _c_int, _c_int, _c_void_p],
     "llm_gemm_bf16_status": [],
     "llm_gemm_bf16_pair": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                            _c_void_p, _c_void_p],
@@ -87,6 +87,33 @@ def _check(t, name, dtype=None, dims=None):
     if dims is not None:
         _need(t.dim() == dims, f"{name}: expected {dims} dims, got shape {tuple(t.shape)}")
     _need(t.is_contiguous(), f"{name}: tensor must be contiguous")
+
+
+class PartialSums:
+    """The result of a matrix product that was split along k and whose partial sums are still to be added:
+    `parts` [splits, tokens, n] float32 (in this library's scratch: valid until the next split product on the
+    stream), `out` the tensor the sum belongs in.  `Kernels.add_rmsnorm` and `Kernels.rope_store` take it in
+    place of the tensor and add the parts while they read; `sum()` adds them into `out` by a kernel of its own."""
+
+    def __init__(self, kernels, parts, out):
+        self.k, self.parts, self.out = kernels, parts, out
+        self.shape, self.dtype = out.shape, out.dtype
+
+    @property
+    def splits(self) -> int:
+        return self.parts.shape[0]
+
+    @property
+    def stride(self) -> int:
+        return self.parts.shape[1] * self.parts.shape[2]
+
+    def sum(self):
+        return self.k.sum_parts(self.parts, self.out)
+
+
+def materialize(x):
+    """The tensor of `x`, which may be a PartialSums."""
+    return x.sum() if isinstance(x, PartialSums) else x
 
 
 class AttentionPlan:
@@ -178,6 +205,7 @@ class Kernels:
         self.gemm_backend = os.environ.get("IITJ_GEMM_BACKEND", "auto")
         self.gemm_small_tokens = int(os.environ.get("IITJ_GEMM_SMALL_TOKENS", "128"))
         self.gemm_pair_mode = os.environ.get("IITJ_GEMM_PAIR", "swiglu")   # off | swiglu | all
+        self.defer_sums = os.environ.get("IITJ_DEFER_SUMS", "1") == "1"     # k-split sums added by the reading kernel
         self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
         if os.environ.get("IITJ_PDL", "1") == "0":
             self.lib.llm_set_pdl(0)
@@ -239,7 +267,13 @@ class Kernels:
         _check(out, "add_rmsnorm.out", tuple(DTYPE_CODE), 2)
         _check(weight, "add_rmsnorm.weight", tuple(DTYPE_CODE), 1)
         _need(weight.shape[0] == width and out.shape[1] == width, "add_rmsnorm: widths differ")
-        if delta is not None:
+        splits, stride = 0, 0
+        if isinstance(delta, PartialSums) and (delta.splits > 8 or delta.stride % 4):
+            delta = delta.sum()
+        if isinstance(delta, PartialSums):
+            _need(tuple(delta.shape) == tuple(residual.shape), "add_rmsnorm.delta: shape differs from residual")
+            splits, stride, delta = delta.splits, delta.stride, delta.parts
+        elif delta is not None:
             _check(delta, "add_rmsnorm.delta", out.dtype, 2)
             _need(delta.shape == residual.shape, "add_rmsnorm.delta: shape differs from residual")
         if rows is not None:
@@ -249,7 +283,7 @@ class Kernels:
             _need(out.shape[0] == residual.shape[0], "add_rmsnorm.out: shape differs from residual")
         self._call("llm_add_rmsnorm", _ptr(residual), _ptr(delta), _ptr(rows), _ptr(weight),
                    DTYPE_CODE[weight.dtype], _ptr(out), DTYPE_CODE[out.dtype], out.shape[0], width, float(eps),
-                   self._stream())
+                   splits, stride, self._stream())
         return out
 
     def rope_tables(self, positions, inv_freq, cos, sin):
@@ -268,7 +302,15 @@ class Kernels:
         """Rotate q (in place) and k, store k and v of every token in its cache slot.
 
         cache_layer: [pages, 2, kv_heads, page_size, head_dim]; slots may be None (rotate only).
-        tables: (cos, sin) of `rope_tables` for these positions, else the angles are evaluated here."""
+        tables: (cos, sin) of `rope_tables` for these positions, else the angles are evaluated here.
+        `qkv` may be a PartialSums: its parts are added on the way (all dims rotated, head_dim % 8 == 0),
+        else summed first.  Returns the tensor that holds the rotated queries."""
+        parts = None
+        if isinstance(qkv, PartialSums):
+            if rotary_dim == head_dim and head_dim % 8 == 0 and qkv.splits <= 8:
+                parts, qkv = qkv, qkv.out
+            else:
+                qkv = qkv.sum()
         _check(qkv, "rope_store.qkv", tuple(DTYPE_CODE), 2)
         _check(positions, "rope_store.positions", torch.int32, 1)
         tokens = qkv.shape[0]
@@ -293,7 +335,9 @@ class Kernels:
             _need(cos.shape == (tokens, rotary_dim // 2) and sin.shape == cos.shape, "rope_store: wrong table shape")
         self._call("llm_rope_store", _ptr(qkv), _ptr(positions), _ptr(inv_freq) if rotary_dim else None, _ptr(cos), _ptr(sin),
                    _ptr(slots), _ptr(cache_layer) if slots is not None else None, DTYPE_CODE[qkv.dtype], tokens,
-                   heads, kv_heads, head_dim, rotary_dim, page_size, self._stream())
+                   heads, kv_heads, head_dim, rotary_dim, page_size, _ptr(parts.parts) if parts is not None else None,
+                   parts.splits if parts is not None else 0, parts.stride if parts is not None else 0, self._stream())
+        return qkv
 
     def silu_mul(self, gu, act):
         _check(gu, "silu_mul.gu", tuple(DTYPE_CODE), 2)
@@ -360,9 +404,10 @@ class Kernels:
         return out
 
     # ---- matrix products -------------------------------------------------------------
-    def linear(self, x, weight, out, swiglu: bool = False):
+    def linear(self, x, weight, out, swiglu: bool = False, defer: bool = False):
         """out = x . weight^T; with swiglu, weight holds gate rows then up rows and
-        out = silu(x . gate^T) * (x . up^T)."""
+        out = silu(x . gate^T) * (x . up^T).  With `defer` the result may come back as a PartialSums (the product
+        was split along k and the caller's next kernel adds the parts); else `out`."""
         _check(x, "linear.x", tuple(DTYPE_CODE), 2)
         _check(weight, "linear.weight", x.dtype, 2)
         _check(out, "linear.out", (x.dtype, torch.float32), 2)
@@ -380,7 +425,7 @@ class Kernels:
         policy = self.gemm_policy(tokens, n, k, swiglu)
         if policy == "tcgen05":
             splits, smem_kb = self.gemm_plan(tokens, n, k, swiglu)
-            return self.gemm_tcgen05(x, weight, out, swiglu, splits, smem_kb)
+            return self.gemm_tcgen05(x, weight, out, swiglu, splits, smem_kb, defer=defer and not swiglu and self.defer_sums)
         if policy == "pair":
             return self.gemm_pair(x, weight, out, swiglu)
         if swiglu:
@@ -392,8 +437,9 @@ class Kernels:
             torch.mm(x, weight.t(), out=out)
         return out
 
-    def gemm_tcgen05(self, x, weight, out, swiglu: bool = False, splits: int = 1, smem_kb: int = 0):
-        """out = x . weight^T on this library's tcgen05 kernel (bfloat16 in, bfloat16 or float32 out)."""
+    def gemm_tcgen05(self, x, weight, out, swiglu: bool = False, splits: int = 1, smem_kb: int = 0, defer: bool = False):
+        """out = x . weight^T on this library's tcgen05 kernel (bfloat16 in, bfloat16 or float32 out).  With `defer`
+        and more than one split the partial sums are returned as a PartialSums instead of being added here."""
         _check(x, "gemm.x", torch.bfloat16, 2)
         _check(weight, "gemm.weight", torch.bfloat16, 2)
         _check(out, "gemm.out", (torch.bfloat16, torch.float32), 2)
@@ -404,10 +450,21 @@ class Kernels:
         scratch = None
         if splits > 1:
             scratch = self._scratch("gemm.partials", splits * tokens * weight.shape[0], x.device)
+        defer = bool(defer and splits > 1 and not swiglu)
         self._call("llm_gemm_bf16", _ptr(x), _ptr(weight), _ptr(out), 1 if out.dtype == torch.float32 else 0, tokens,
-                   n, k, out.shape[1], 1 if swiglu else 0, splits, _ptr(scratch), int(smem_kb), self._stream())
+                   n, k, out.shape[1], 1 if swiglu else 0, splits, _ptr(scratch), int(smem_kb), 1 if defer else 0,
+                   self._stream())
+        if defer:
+            return PartialSums(self, scratch[:splits * tokens * n].view(splits, tokens, n), out)
         if splits > 1:
             self.launches += 1
+        return out
+
+    def sum_parts(self, parts, out):
+        """out = the sum over the first dimension of `parts` [splits, tokens, n] float32."""
+        _check(parts, "sum_parts.parts", torch.float32, 3)
+        _need(tuple(parts.shape[1:]) == tuple(out.shape), "sum_parts: shapes do not fit")
+        torch.sum(parts, dim=0, out=out) if out.dtype == torch.float32 else out.copy_(torch.sum(parts, dim=0))
         return out
 
     def gemm_pair(self, x, weight, out, swiglu: bool = False, tail_split: bool = True):

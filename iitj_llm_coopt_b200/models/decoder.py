@@ -10,6 +10,7 @@ from __future__ import annotations
 import torch
 
 from .. import parts as P
+from ..parts.base import delta_for
 
 
 def _layer_part_classes(layer):
@@ -129,7 +130,7 @@ class DecoderModel:
             residual, delta = self.layers[call.layer].forward(ctx, residual, delta, call)
         if ctx.num_logits == 0:
             return None
-        x = self.final_norm.forward(ctx, residual, delta, rows=ctx.logit_rows)
+        x = self.final_norm.forward(ctx, residual, delta_for(self.final_norm, delta), rows=ctx.logit_rows)
         return self.head.forward(ctx, x)
 
 

@@ -14,10 +14,25 @@ Interfaces (T = tokens of the step, w = model width):
   Mixer.forward(ctx, x[T,w], call) -> delta[T,w];  Mixer.cache_need() -> CacheNeed
   FeedForward.forward(ctx, x[T,w]) -> delta[T,w]
   Block.forward(ctx, residual, delta, call) -> (residual, delta)
+
+A delta (and the qkv handed to a position encoding) may be a `kernels.PartialSums`: a matrix product
+that was split along k and whose parts are still to be added.  It is only handed to a norm or a position
+encoding whose class sets `takes_partial_sums = True` (the built-in ones pass it on to kernels that add the
+parts while they read); for any other part `delta_for(part, delta)` adds them first.  The parts live in
+scratch that the next split product overwrites, so an arrangement uses a delta before it runs another product.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
+
+import torch
+
+
+def delta_for(part, delta):
+    """`delta` as `part` can take it: partial sums are added now unless the part adds them itself."""
+    if delta is not None and not isinstance(delta, torch.Tensor) and not getattr(part, "takes_partial_sums", False):
+        return delta.sum()
+    return delta
 
 
 @dataclass(frozen=True)

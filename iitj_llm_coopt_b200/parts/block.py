@@ -9,6 +9,8 @@
 """
 from __future__ import annotations
 
+from .base import delta_for
+
 
 class PreNormBlock:
     def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward):
@@ -24,7 +26,7 @@ class PreNormBlock:
                 "feed_forward_norm": self.feed_forward_norm, "feed_forward": self.feed_forward}
 
     def forward(self, ctx, residual, delta, call):
-        x = self.mixer_norm.forward(ctx, residual, delta)
+        x = self.mixer_norm.forward(ctx, residual, delta_for(self.mixer_norm, delta))
         a = self.mixer.forward(ctx, x, call)
-        x = self.feed_forward_norm.forward(ctx, residual, a)
+        x = self.feed_forward_norm.forward(ctx, residual, delta_for(self.feed_forward_norm, a))
         return residual, self.feed_forward.forward(ctx, x)

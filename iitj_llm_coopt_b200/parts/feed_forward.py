@@ -30,4 +30,4 @@ class SwiGLU(Part):
         act = ctx.buffer("ffn.act", (t, self.inner), self.dtype)
         self.k.linear(x, self.gate_up, act, swiglu=True)
         out = ctx.buffer("ffn.out", (t, self.width), self.dtype)
-        return self.k.linear(act, self.down, out)
+        return self.k.linear(act, self.down, out, defer=True)

@@ -13,6 +13,7 @@ layer's cache.
 from __future__ import annotations
 
 from ..config.specs import CacheNeed
+from ..kernels import materialize
 from .base import ParamSpec, Part
 
 
@@ -46,11 +47,13 @@ class PagedAttention(Part):
         group, view = ctx.cache.view(call.cache)
         meta = ctx.group(group)
         qkv = ctx.buffer("attn.qkv", (t, self.qkv_width), self.dtype)
-        self.k.linear(x, self.qkv, qkv)
-        self.position.encode_and_store(ctx, qkv, view, meta.slots if call.write else None,
-                                       self.heads, self.kv_heads)
+        # a position encoding that says so takes the product's k-split partial sums and adds them as it reads
+        qkv = self.k.linear(x, self.qkv, qkv, defer=getattr(self.position, "takes_partial_sums", False))
+        rotated = self.position.encode_and_store(ctx, qkv, view, meta.slots if call.write else None,
+                                                 self.heads, self.kv_heads)
+        qkv = rotated if rotated is not None else materialize(qkv)
         attn = ctx.buffer("attn.ctx", (t, self.heads * self.head_dim), self.dtype)
         self.k.attention(qkv, view, meta, attn, self.heads, self.kv_heads, self.head_dim,
                          window=self.window, scale=self.scale)
         out = ctx.buffer("attn.out", (t, self.width), self.dtype)
-        return self.k.linear(attn, self.o, out)
+        return self.k.linear(attn, self.o, out, defer=True)

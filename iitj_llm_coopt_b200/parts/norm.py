@@ -11,6 +11,7 @@ from .base import ParamSpec, Part
 
 class RMSNorm(Part):
     graph_safe = True
+    takes_partial_sums = True     # `delta` may be the k-split parts of a matrix product: added while they are read
 
     def __init__(self, spec, kernels, dtype):
         self.spec, self.k, self.dtype = spec, kernels, dtype

@@ -36,6 +36,7 @@ def rope_inverse_frequencies(rotary_dim: int, theta: float, scaling: dict | None
 
 class RotaryEmbedding(Part):
     graph_safe = True
+    takes_partial_sums = True     # encode_and_store adds the k-split parts of the qkv product as it reads them
 
     def __init__(self, spec, kernels, dtype, device="cuda"):
         self.spec, self.k = spec, kernels
@@ -56,8 +57,8 @@ class RotaryEmbedding(Part):
         return tabs
 
     def encode_and_store(self, ctx, qkv, cache_view, slots, heads, kv_heads):
-        self.k.rope_store(qkv, ctx.positions, self.inv_freq, slots, cache_view, heads, kv_heads,
-                          self.head_dim, self.rotary_dim, tables=self.tables(ctx) if self.rotary_dim else None)
+        return self.k.rope_store(qkv, ctx.positions, self.inv_freq, slots, cache_view, heads, kv_heads,
+                                 self.head_dim, self.rotary_dim, tables=self.tables(ctx) if self.rotary_dim else None)
 
 
 class NoPosition(Part):

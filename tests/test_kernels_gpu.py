@@ -321,6 +321,68 @@ def test_attention_bf16_same_result_in_any_batch(K):
     assert torch.equal(out1[0], out[41])
 
 
+# ---- k-split partial sums added by the kernel that reads the result ------------------------
+@pytest.mark.parametrize("rows,width,splits", [(9, 264, 3), (1, 96, 2), (40, 4096, 8), (5, 100, 4)])
+def test_add_rmsnorm_partial_sums(K, rows, width, splits):
+    from iitj_llm_coopt_b200.kernels import PartialSums
+    res = rnd((rows, width), torch.float32, 130)
+    parts = rnd((splits, rows, width), torch.float32, 131, 0.3)
+    w = (1 + 0.1 * rnd((width,), torch.float32, 132)).to(torch.bfloat16)
+    delta = PartialSums(K, parts, torch.empty(rows, width, device="cuda", dtype=torch.bfloat16))
+    out = torch.empty(rows, width, device="cuda", dtype=torch.bfloat16)
+    before = res.clone()
+    K.add_rmsnorm(res, delta, w, 1e-5, out)
+    v, y = R.ref_add_rmsnorm(before, parts.sum(0), w, 1e-5)
+    close(res, v, torch.float32)
+    close(out, y, torch.bfloat16)
+    idx = torch.tensor([rows - 1, 0], device="cuda", dtype=torch.int32)
+    out2 = torch.empty(2, width, device="cuda", dtype=torch.bfloat16)
+    keep = res.clone()
+    K.add_rmsnorm(res, delta, w, 1e-5, out2, rows=idx)
+    assert torch.equal(res, keep)
+    close(out2, R.ref_add_rmsnorm(keep, parts.sum(0), w, 1e-5, rows=idx)[1], torch.bfloat16)
+    close(delta.sum(), parts.sum(0), torch.bfloat16)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,splits", [(4, 2, 32, 8, 3), (3, 1, 128, 16, 2), (8, 8, 64, 16, 5)])
+def test_rope_store_partial_sums(K, heads, kv_heads, head_dim, page, splits):
+    from iitj_llm_coopt_b200.kernels import PartialSums
+    tokens, pages = 11, 6
+    width = (heads + 2 * kv_heads) * head_dim
+    parts = rnd((splits, tokens, width), torch.float32, 133, 0.5)
+    positions = torch.randint(0, 100000, (tokens,), device="cuda", dtype=torch.int32)
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, head_dim, 2).float() / head_dim))).cuda()
+    slots = torch.randperm(pages * page, device="cuda")[:tokens].to(torch.int32)
+    slots[2] = -1
+    cache = torch.full((pages, 2, kv_heads, page, head_dim), 7.0, device="cuda", dtype=torch.bfloat16)
+    want_cache = cache.clone()
+    want = R.ref_rope(parts.sum(0), positions, inv_freq, heads, kv_heads, head_dim, head_dim)
+    R.ref_store(want_cache, want.to(torch.bfloat16), slots, heads, kv_heads, head_dim)
+    qkv = PartialSums(K, parts, torch.zeros(tokens, width, device="cuda", dtype=torch.bfloat16))
+    got = K.rope_store(qkv, positions, inv_freq, slots, cache, heads, kv_heads, head_dim, head_dim)
+    q = heads * head_dim
+    close(got[:, :q], want[:, :q], torch.bfloat16)
+    close(cache, want_cache, torch.bfloat16)
+    assert torch.equal(cache == 7.0, want_cache == 7.0)
+    # a rotation that covers only part of the head: the parts are added first, then the usual kernel runs
+    cache2 = torch.full_like(cache, 7.0)
+    half_freq = (1.0 / (500000.0 ** (torch.arange(0, head_dim // 2, 2).float() / (head_dim // 2)))).cuda()
+    got2 = K.rope_store(PartialSums(K, parts, torch.zeros(tokens, width, device="cuda", dtype=torch.bfloat16)), positions,
+                        half_freq, slots, cache2, heads, kv_heads, head_dim, head_dim // 2)
+    want2 = R.ref_rope(parts.sum(0).to(torch.bfloat16), positions, half_freq, heads, kv_heads, head_dim, head_dim // 2)
+    close(got2[:, :q], want2[:, :q], torch.bfloat16)
+
+
+def test_linear_defers_split_sums(K):
+    from iitj_llm_coopt_b200.kernels import PartialSums
+    x, w = rnd((8, 4096), torch.bfloat16, 134), rnd((512, 4096), torch.bfloat16, 135, 0.05)
+    out = torch.zeros(8, 512, device="cuda", dtype=torch.bfloat16)
+    got = K.linear(x, w, out, defer=True)
+    assert isinstance(got, PartialSums) and got.splits > 1
+    close(got.sum(), R.ref_linear(x, w), torch.bfloat16, 0.5)
+    assert isinstance(K.linear(x, w, out), torch.Tensor)
+
+
 # ---- the tcgen05 matrix product (bfloat16) ---------------------------------------------
 @pytest.mark.parametrize("tokens", [1, 7, 16, 17, 40, 100, 129, 300, 600])
 @pytest.mark.parametrize("n,k", [(128, 64), (200, 96), (320, 176), (1000, 264), (136, 4104)])

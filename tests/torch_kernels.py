@@ -152,6 +152,7 @@ class TorchKernels:
         if slots is not None:
             ref_store(cache_layer, rot, slots, heads, kv_heads, head_dim)
         qkv[:, :heads * head_dim] = rot[:, :heads * head_dim]
+        return qkv
 
     def silu_mul(self, gu, act):
         act.copy_(ref_silu_mul(gu))
@@ -162,8 +163,8 @@ class TorchKernels:
                                       heads, kv_heads, head_dim, window, scale))
         return out
 
-    def linear(self, x, weight, out, swiglu=False):
-        out.copy_(ref_linear(x, weight, swiglu))
+    def linear(self, x, weight, out, swiglu=False, defer=False):
+        out.copy_(ref_linear(x, weight, swiglu))     # never split: `defer` has nothing to leave for later
         return out
 
     def sample(self, logits, temperature, keys, out):
