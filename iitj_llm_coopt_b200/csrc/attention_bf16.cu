@@ -438,6 +438,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     }
 }
 
+// All loads of a thread are asked for at once (the partial results of every possible split, and the position
+// that tells how many of them count): the kernel is one round trip to memory long instead of four.
+constexpr int kMergeSplits = 16;
+
 template <int D>
 __global__ void __launch_bounds__(D)
 attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ items,
@@ -446,19 +450,44 @@ attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
     pdl_trigger();
     pdl_wait();
     const int item = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    const size_t base = ((size_t)item * heads + head) * max_splits;
+    float pm[kMergeSplits], pl[kMergeSplits], po[kMergeSplits];
+    if (max_splits <= kMergeSplits) {
+#pragma unroll
+        for (int s = 0; s < kMergeSplits; ++s) {
+            if (s < max_splits) {
+                pm[s] = part_ml[(base + s) * 2];
+                pl[s] = part_ml[(base + s) * 2 + 1];
+                po[s] = part_o[(base + s) * D + d];
+            }
+        }
+    }
     const int tok = items[item];
     const int pos = positions[tok];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int n_splits = (pos - (lo & ~(kTile - 1))) / keys_per_split + 1;
     if (n_splits == 1) return;                                    // the decode kernel wrote the result itself
-    const size_t base = ((size_t)item * heads + head) * max_splits;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-    float L = 0.f, O = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float f = exp2f(part_ml[(base + s) * 2] - M);
-        L += part_ml[(base + s) * 2 + 1] * f;
-        O += part_o[(base + s) * D + d] * f;
+    float M = -INFINITY, L = 0.f, O = 0.f;
+    if (max_splits <= kMergeSplits) {
+        // splits past n_splits were not written by this launch: they are left out by index, never by value
+#pragma unroll
+        for (int s = 0; s < kMergeSplits; ++s)
+            if (s < n_splits) M = fmaxf(M, pm[s]);
+#pragma unroll
+        for (int s = 0; s < kMergeSplits; ++s) {
+            if (s < n_splits) {
+                const float f = exp2f(pm[s] - M);
+                L += pl[s] * f;
+                O += po[s] * f;
+            }
+        }
+    } else {
+        for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+        for (int s = 0; s < n_splits; ++s) {
+            const float f = exp2f(part_ml[(base + s) * 2] - M);
+            L += part_ml[(base + s) * 2 + 1] * f;
+            O += part_o[(base + s) * D + d] * f;
+        }
     }
     out[(size_t)tok * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(O / L);
 }
