@@ -164,7 +164,8 @@ def main() -> int:
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     typed = LlamaConfig.from_dict(cfg)
-    B, C, K, W = args.batch, args.context, args.steps, args.warmup
+    # at least six warm-up steps: a step shape is captured into a CUDA graph at its fourth sighting
+    B, C, K, W = args.batch, args.context, args.steps, max(args.warmup, 6)
     page = 16
     biggest = max(B, 1 if args.no_points else 64)
     pool_tokens = biggest * (C + max(K, 96) + W + 2 * page) + args.prefill_tokens + 4 * page
@@ -239,7 +240,7 @@ def main() -> int:
         print(json.dumps({"only": "prefill", "tokens": args.prefill_tokens, "ms": t[len(t) // 2], "min_ms": t[0], "reps": len(t)}))
         return 0
     if args.only == "decode":
-        t, n = decode_run(B, max(1, K), 3)
+        t, n = decode_run(B, max(1, K), 6)
         print(json.dumps({"only": "decode", "batch": B, "ms": sum(t) / len(t), "launches_per_step": n / len(t)}))
         return 0
     clocks = ClockSampler()
@@ -262,7 +263,7 @@ def main() -> int:
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            t, _ = decode_run(b, max(8, K // 2), 3)
+            t, _ = decode_run(b, max(8, K // 2), 6)
             points[f"decode_b{b}"] = b / (sum(t) / len(t) / 1e3)
 
     e2e = None
@@ -278,7 +279,7 @@ def main() -> int:
 
         budget = engine.policy.max_batched_tokens
         engine.policy.max_batched_tokens = B * C          # all prompts in one prefill step, then decode steps only
-        WE, KE = max(W, 4), max(K, 64)                     # untimed decode steps (graph capture among them), timed ones
+        WE, KE = W, max(K, 64)                     # untimed decode steps (graph capture among them), timed ones
         seqs = [engine.new_sequence(p, WE + KE + 1, 0.0, True, None, on_out) for p in prompts]
         engine.run_until_done()
         torch.cuda.synchronize()

@@ -17,7 +17,8 @@ table[p // page] * page + p % page, `ensure` that raises before it allocates any
   kind "state" keep a [entries, max_requests, *state_shape] buffer indexed by it.  The
   slot exists even when no layer keeps state (Llama: zero bytes).
 
-Device storage of a paged group: [entries, pages, 2, kv_heads, page_size, head_dim]
+Device storage of a paged group: [entries, pages + 1, 2, kv_heads, page_size, head_dim] (the last page is
+the padding page, never handed out)
 (K plane then V plane of a page; one head's rows of a page are contiguous).
 """
 from __future__ import annotations
@@ -133,12 +134,24 @@ class CacheManager:
         for g in self.groups:
             if isinstance(g, PagedGroup):
                 n = g.need
-                g.storage = torch.zeros((len(g.entries), self.num_pages, 2, n.kv_heads, self.page_size, n.head_dim),
+                # one page more than the pool hands out: the padding page (see pad_page)
+                g.storage = torch.zeros((len(g.entries), self.num_pages + 1, 2, n.kv_heads, self.page_size, n.head_dim),
                                         dtype=self.dtype, device=self.device)
             else:
                 dt = getattr(torch, g.need.state_dtype)
-                g.storage = torch.zeros((len(g.entries), self.max_requests) + tuple(g.need.state_shape),
+                g.storage = torch.zeros((len(g.entries), self.max_requests + 1) + tuple(g.need.state_shape),
                                         dtype=dt, device=self.device)
+
+    @property
+    def pad_page(self) -> int:
+        """A page id that no request ever gets: rows that only pad a batch to a size with a captured graph
+        read and write there (the reference keeps such a scratch page too, engine/engine.py:207-211)."""
+        return self.num_pages
+
+    @property
+    def pad_slot(self) -> int:
+        """The state slot of padding rows."""
+        return self.max_requests
 
     @staticmethod
     def bytes_per_page(needs: list, page_size: int, itemsize: int) -> int:

@@ -42,6 +42,11 @@ class ModelRunner:
         self._graphs: dict = {}      # key -> captured decode step
         self._graph_seen: dict = {}  # key -> eager runs so far
         self.graph_replays = 0
+        self.graph_captures = 0
+        self.padded_steps = 0
+        # A step shape is captured into a graph once it has been seen this often: a capture costs about as much as
+        # ten eager steps, so shapes that come and go (a batch that shrinks every few steps) are not worth one.
+        self.graph_after = 3
         self.vocab = model.spec.vocab
         self.workspace = Workspace(device)
         self._pinned = None          # int32 staging buffer (host, pinned)
@@ -115,6 +120,7 @@ class ModelRunner:
         k = getattr(self.model, "k", None)
         before = k.launches if k is not None else 0
         generation = self._generation()
+        self.graph_captures += 1
         graph = torch.cuda.CUDAGraph()
         # The garbage collector must not run inside the capture: collecting an older engine there would
         # destroy its graphs, which CUDA forbids while a capture is open and which voids the capture.
@@ -135,6 +141,15 @@ class ModelRunner:
         graph.replay()
         self.graph_replays += 1
         return logits
+
+    @staticmethod
+    def _padded_batch(b: int) -> int:
+        """The batch size a decode step of `b` requests runs at: itself up to 8, then the next multiple of 8
+        (to 64), of 16 (to 128), of 32."""
+        if b <= 8:
+            return b
+        step = 8 if b <= 64 else 16 if b <= 128 else 32
+        return -(-b // step) * step
 
     # ---- the step --------------------------------------------------------------------
     def step(self, entries: list, prev_ids=None):
@@ -164,6 +179,23 @@ class ModelRunner:
         N = sum(len(e.want) for e in entries)
         groups = cache.paged
         rows = {g: [self._table_row(g, e.request) for e in entries] for g in groups}
+        # A decode step (one token and one wanted row per request) is padded to the next batch size of a short
+        # ladder, so that batches which shrink by a request every few steps still meet captured graphs.  A padding
+        # row is a one-token request at position 0 whose block table and state slot are the cache's padding page
+        # and slot; its logits row is cut off below.
+        pad = 0
+        if self.use_graphs and T == B and N == B:
+            pad = self._padded_batch(B) - B
+        if pad:
+            self.padded_steps += 1
+            starts += [0] * pad
+            qlens += [1] * pad
+            seqlens += [1] * pad
+            slots_b += [cache.pad_slot] * pad
+            pad_row = np.asarray([cache.pad_page], dtype=np.int32)
+            for g in groups:
+                rows[g] += [pad_row] * pad
+            T, B, N = T + pad, B + pad, N + pad
         widths = {g: max(1, max(r.shape[0] for r in rows[g])) for g in groups}
         # A step whose shape (tokens per request, wanted rows, table width) has been seen before can be
         # replayed from a captured graph if the index arrays keep their places, so the block tables are
@@ -207,10 +239,11 @@ class ModelRunner:
             o, n = layout[name]
             host[o:o + n] = values
 
-        ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T)
+        ids = np.zeros(T, dtype=np.int64)
+        ids[:T - pad] = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T - pad)
         if fed:
             src = np.concatenate([np.asarray(e.source_rows if e.source_rows is not None else [-1] * len(e.tokens),
-                                             dtype=np.int64) for e in entries])
+                                             dtype=np.int64) for e in entries] + [np.full(pad, -1, dtype=np.int64)])
             put("token_src", src)
             ids = np.where(src >= 0, 0, ids)          # placeholders: the device fills them in
         if ids.min() < 0 or ids.max() >= self.vocab:
@@ -222,7 +255,7 @@ class ModelRunner:
         put("token_request", np.repeat(np.arange(B), qlens))
         put("cu_seqlens", cu)
         put("seq_lens", seqlens)
-        put("logit_rows", [int(cu[b]) + w for b, e in enumerate(entries) for w in e.want])
+        put("logit_rows", [int(cu[b]) + w for b, e in enumerate(entries) for w in e.want] + [int(cu[B - pad + i]) for i in range(pad)])
         put("state_slots", slots_b)
         put("first_portion", [1 if s == 0 else 0 for s in starts])
         if plan.n_items:
@@ -271,14 +304,16 @@ class ModelRunner:
                           positions=positions, token_request=token_request, cu_seqlens=cu_dev, seq_lens=seq_dev,
                           logit_rows=dev("logit_rows"), state_slots=dev("state_slots"),
                           first_portion=dev("first_portion"), groups=metas, cache=cache,
-                          workspace=self.workspace, requests=[e.request for e in entries],
+                          workspace=self.workspace, requests=[e.request for e in entries] + [None] * pad,
                           query_lens=qlens, starts=starts, slots_host=slots_b)
         if graphable:
-            key = (tuple(qlens), tuple(len(e.want) for e in entries), tuple(sorted(widths.items())), plan.context_bound, fed)
-            logits = self._forward_graphed(key, ctx, eager_runs=1 if decode_shaped else 2)
+            key = (tuple(qlens), tuple(len(e.want) for e in entries) + (1,) * pad, tuple(sorted(widths.items())), plan.context_bound, fed)
+            logits = self._forward_graphed(key, ctx, eager_runs=self.graph_after if decode_shaped else max(4, self.graph_after))
         else:
             logits = self.model.forward(ctx)
         for e, end in zip(entries, seqlens):
             cache.advance(e.request, end)
         self.steps += 1
+        if pad and logits is not None:
+            logits = logits[:N - pad]
         return logits

@@ -213,3 +213,27 @@ def test_many_random_requests_under_pressure(lively_dirs, name, dtype):
     assert llm.engine.runner.graph_replays > 0
     llm.engine.cache.check()
     assert llm.engine.cache.num_free == pages
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("C", "bfloat16")])
+def test_padded_decode_batches(lively_dirs, name, dtype):
+    """Thirteen requests that finish one after the other: their decode steps run at batch sizes 13 .. 9, which the
+    step function pads to 16 with rows on the cache's padding page so that one captured graph serves them all.
+    The padding rows must not show in anybody's output."""
+    import random
+    cfg_d, seed, page = CONFIGS[name]
+    rng = random.Random(99 + seed)
+    prompts = [[rng.randrange(cfg_d["vocab_size"]) for _ in range(rng.choice([3, 9, 20, 33]))] for _ in range(13)]
+    params = [SamplingParams(max_tokens=12 + 3 * i, ignore_eos=True) for i in range(13)]
+    llm = LLM(lively_dirs[name], dtype=dtype, page_size=page, num_pages=13 * (-(-(33 + 52) // page)) + 4, max_num_seqs=13,
+              max_num_batched_tokens=512)
+    outs = llm.generate(prompts, params)
+    cfg, w = plain.read_model_dir(lively_dirs[name], torch.float32)
+    for p, sp, o in zip(prompts, params, outs):
+        assert len(o.token_ids) == sp.max_tokens
+        if dtype == "float32":
+            assert o.token_ids == plain.greedy_generate(cfg, w, p, sp.max_tokens)
+        else:
+            assert margins_ok(cfg, w, p, o.token_ids, 0.05)
+    runner = llm.engine.runner
+    assert runner.padded_steps > 0 and runner.graph_replays > 0

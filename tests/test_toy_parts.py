@@ -172,7 +172,7 @@ def test_toy_mixer_with_state_steps_like_whole_prompts(toy_registered, device, d
     eng = _engine(device, dtype)
     groups = eng.cache.groups
     assert len(groups) == 3 and len(eng.cache.paged) == 2             # two attention geometries, one state group
-    assert groups[eng.cache.entry_group[1][0]].storage.shape == (1, 3, 65)
+    assert groups[eng.cache.entry_group[1][0]].storage.shape == (1, 3 + 1, 65)        # three request slots and the padding slot
     assert eng.cache.entry_group[0][0] == eng.cache.entry_group[2][0] != eng.cache.entry_group[3][0]
     reqs = cases.requests_for(200, [50, 23, 70, 9], seed=4)
     whole = run_steps(eng, cases.whole(reqs))
