@@ -41,6 +41,7 @@ constexpr int kTileBytes = 2 * kHalfBytes;     // 32 KiB
 constexpr int kThreads = 320;     // warp 0: loads, warp 1: MMA + TMEM, warps 2-5: softmax of head A, warps 6-9: of head B
 constexpr int kGroupThreads = 128;
 constexpr uint32_t kTmemCols = 512;            // S_A | S_B | O_A | O_B, 128 float32 columns each
+constexpr int kMinSplitTiles = 16;              // key tiles per split, about (the count of splits is rounded)
 constexpr float kRescaleStep = 8.0f;           // in log2 units: P stays below 2^8
 
 __device__ int g_attn_status = 0;
@@ -119,6 +120,9 @@ struct AttnArgs {
     bf16* out;
     int out_stride;
     int heads, kv_heads, page_size, window;
+    int splits;                   // CTAs along the keys of a query tile (> 1: partial results go to scratch, see attn_tc_merge_kernel)
+    float* part_o;                // [tile][head][split][128 rows][128] float32, relative to the split's reference maximum
+    float* part_ml;               // [tile][head][split][128 rows][2]: reference maximum (log2 units), sum
     int per_cta;                  // query heads per CTA: 2 (ping-pong), or 1 when that fills more of the GPU
     int pairs;                    // CTAs per key/value group: ceil(heads per group / per_cta)
     float sl;                     // softmax scale * log2(e)
@@ -145,8 +149,18 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int n_heads = (a.per_cta == 2 && 2 * pr + 1 < group) ? 2 : 1;      // heads this CTA serves
     const int pos_last = pos0 + rows - 1;
     const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
-    const int k_begin = lo0 & ~(kKeys - 1);
-    const int n_tiles = (pos_last - k_begin) / kKeys + 1;
+    // this CTA's share of the query tile's key tiles (all of them without splits)
+    const int tile_id = gridDim.x - 1 - blockIdx.x, split = blockIdx.z;
+    const int k_first = lo0 & ~(kKeys - 1);
+    const int all_tiles = (pos_last - k_first) / kKeys + 1;
+    // the launch allows a.splits CTAs per tile and head; a tile uses as many as leave each about 16 key tiles or more
+    // (decided here, from the tile's own context, so that a captured graph follows a prompt as it grows)
+    const int eff_splits = max(1, min(a.splits, (all_tiles + kMinSplitTiles / 2) / kMinSplitTiles));
+    const int per_split = (all_tiles + eff_splits - 1) / eff_splits;
+    const int k_begin = k_first + split * per_split * kKeys;
+    const int n_tiles = split < eff_splits ? max(0, min(all_tiles - split * per_split, per_split)) : 0;
+
+    if (n_tiles == 0) return;      // a split past the end of this tile's keys: nothing to do (the merge leaves it out by index)
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
@@ -346,7 +360,27 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (lane == 0) mbar_arrive(&p_full[x]);              // one arrival per warp
         }
         if (ok && !mbar_wait(&o_done[x], (n_tiles - 1) & 1)) { attn_give_up(8); failed = 1; ok = false; }
-        if (ok && !failed) {
+        if (ok && !failed && eff_splits > 1) {
+            // partial result of this split: O as it stands (relative to m), and (m, l) of the row
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const size_t slot = ((size_t)tile_id * a.heads + head_a + x) * a.splits + split;
+            float* dst = a.part_o + (slot * kRows + row) * kDim;
+#pragma unroll 1
+            for (int c = 0; c < kDim; c += 32) {
+                uint32_t o[32];
+                tmem_ld32(o_addr + c, o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < rows) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 4)
+                        *reinterpret_cast<uint4*>(dst + c + d) = make_uint4(o[d], o[d + 1], o[d + 2], o[d + 3]);
+                }
+            }
+            if (row < rows) {
+                a.part_ml[(slot * kRows + row) * 2] = m;
+                a.part_ml[(slot * kRows + row) * 2 + 1] = l;
+            }
+        } else if (ok && !failed) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.0f / l;
             bf16* dst = a.out + (size_t)(tok0 + row) * a.out_stride + (size_t)(head_a + x) * kDim;
@@ -375,6 +409,55 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
+// Adds the partial results of a query tile's key splits: out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+// One block per (query row, head), one thread per output dim, all loads asked for at
+// once; splits that got no key tile are left out by index; a tile that was not split needs nothing.
+constexpr int kMaxKeySplits = 16;
+constexpr int kMergeRows = 1;
+
+__global__ void __launch_bounds__(kDim)
+attn_tc_merge_kernel(const AttnArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int tile_id = blockIdx.x / (kRows / kMergeRows), row0 = (blockIdx.x % (kRows / kMergeRows)) * kMergeRows;
+    const int head = blockIdx.y, d = threadIdx.x, sub = 0;
+    const int4 td = a.tiles[tile_id];
+    const int tok0 = td.x, rows = td.y, pos0 = td.z;
+    const int pos_last = pos0 + rows - 1;
+    const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+    const int all_tiles = (pos_last - (lo0 & ~(kKeys - 1))) / kKeys + 1;
+    const int eff_splits = max(1, min(a.splits, (all_tiles + kMinSplitTiles / 2) / kMinSplitTiles));
+    if (eff_splits == 1) return;                                   // the one CTA wrote the result itself
+    const int per_split = (all_tiles + eff_splits - 1) / eff_splits;
+    const int n_valid = (all_tiles + per_split - 1) / per_split;
+    const size_t slot0 = ((size_t)tile_id * a.heads + head) * a.splits;
+    for (int row = row0 + sub; row < min(rows, row0 + kMergeRows); ++row) {
+        float pm[kMaxKeySplits], pl[kMaxKeySplits], po[kMaxKeySplits];
+#pragma unroll
+        for (int s = 0; s < kMaxKeySplits; ++s) {
+            if (s < n_valid) {
+                pm[s] = a.part_ml[((slot0 + s) * kRows + row) * 2];
+                pl[s] = a.part_ml[((slot0 + s) * kRows + row) * 2 + 1];
+                po[s] = a.part_o[((slot0 + s) * kRows + row) * kDim + d];
+            }
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < kMaxKeySplits; ++s)
+            if (s < n_valid) M = fmaxf(M, pm[s]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int s = 0; s < kMaxKeySplits; ++s) {
+            if (s < n_valid) {
+                const float f = pm[s] == -INFINITY ? 0.f : exp2f(pm[s] - M);
+                L += pl[s] * f;
+                O += po[s] * f;
+            }
+        }
+        a.out[(size_t)(tok0 + row) * a.out_stride + (size_t)head * kDim + d] = __float2bfloat16_rn(O / L);
+    }
+}
+
 }  // namespace
 
 // 1 if the tcgen05 prefill kernel takes this geometry.
@@ -388,7 +471,8 @@ LLM_API int llm_attention_tcgen05_supported(int heads, int kv_heads, int head_di
 LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int tokens, const void* cache, long long cache_pages,
                                           const int* block_table, int table_width, const int* tiles, int n_tiles,
                                           void* out, int out_stride, int heads, int kv_heads, int head_dim,
-                                          int page_size, int window, float scale, cudaStream_t stream) {
+                                          int page_size, int window, float scale, int splits, float* part_o,
+                                          float* part_ml, cudaStream_t stream) {
     if (n_tiles == 0) return 0;
     if (!llm_attention_tcgen05_supported(heads, kv_heads, head_dim, page_size))
         LLM_FAIL(-1, "attention_prefill_tcgen05: heads %d / kv_heads %d / head_dim %d / page %d not supported", heads,
@@ -417,7 +501,7 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int group = heads / kv_heads;
-    a.per_cta = (group >= 2 && (long long)n_tiles * kv_heads * ((group + 1) / 2) >= sms) ? 2 : 1;
+    a.per_cta = (group >= 2 && (long long)n_tiles * kv_heads * ((group + 1) / 2) * splits >= sms) ? 2 : 1;
     a.pairs = (group + a.per_cta - 1) / a.per_cta;
     const size_t smem = 6 * kTileBytes + 1024;
     static bool configured = false;
@@ -426,8 +510,17 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
         if (e != cudaSuccess) LLM_FAIL(-2, "attention_prefill_tcgen05: %s", cudaGetErrorString(e));
         configured = true;
     }
-    llm_launch(attn_prefill_tcgen05_kernel, dim3(n_tiles, kv_heads * a.pairs), kThreads, smem, stream, mq, mkv, a);
+    if (splits < 1 || splits > kMaxKeySplits) LLM_FAIL(-1, "attention_prefill_tcgen05: splits %d out of range (1..%d)", splits, kMaxKeySplits);
+    if (splits > 1 && (!part_o || !part_ml)) LLM_FAIL(-1, "attention_prefill_tcgen05: key splits need scratch");
+    a.splits = splits;
+    a.part_o = part_o;
+    a.part_ml = part_ml;
+    llm_launch(attn_prefill_tcgen05_kernel, dim3(n_tiles, kv_heads * a.pairs, splits), kThreads, smem, stream, mq, mkv, a);
     LLM_CHECK_LAUNCH("attention_prefill_tcgen05");
+    if (splits > 1) {
+        llm_launch(attn_tc_merge_kernel, dim3(n_tiles * (kRows / kMergeRows), heads), kDim, 0, stream, a);
+        LLM_CHECK_LAUNCH("attention_prefill_tcgen05 merge");
+    }
     return 0;
 }
 

@@ -21,7 +21,9 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from ..kernels import AttentionPlan
+from ..kernels import AttentionPlan, Kernels
+
+LONG_PREFILL = Kernels.LONG_PREFILL
 from .context import GroupMeta, StepContext, Workspace
 
 
@@ -307,7 +309,10 @@ class ModelRunner:
                           workspace=self.workspace, requests=[e.request for e in entries] + [None] * pad,
                           query_lens=qlens, starts=starts, slots_host=slots_b)
         if graphable:
-            key = (tuple(qlens), tuple(len(e.want) for e in entries) + (1,) * pad, tuple(sorted(widths.items())), plan.context_bound, fed)
+            # (a long context switches the prefill attention to key splits: such steps get graphs of their own)
+            long_prefill = any(n > 1 and end >= LONG_PREFILL for n, end in zip(qlens, seqlens))
+            key = (tuple(qlens), tuple(len(e.want) for e in entries) + (1,) * pad, tuple(sorted(widths.items())),
+                   plan.context_bound, fed, long_prefill)
             logits = self._forward_graphed(key, ctx, eager_runs=self.graph_after if decode_shaped else max(4, self.graph_after))
         else:
             logits = self.model.forward(ctx)

@@ -51,7 +51,8 @@ _SIGNATURES = {
                                   _c_float, _c_int, _c_int, _c_void_p],
     "llm_attention_tcgen05_supported": [_c_int, _c_int, _c_int, _c_int],
     "llm_attention_prefill_tcgen05": [_c_void_p, _c_int, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p,
-                                      _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+                                      _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                                      _c_void_p, _c_void_p, _c_void_p],
     "llm_attention_tcgen05_status": [],
     "llm_gemm_f32": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                      _c_void_p],
@@ -206,6 +207,7 @@ class Kernels:
         self.gemm_small_tokens = int(os.environ.get("IITJ_GEMM_SMALL_TOKENS", "128"))
         self.gemm_pair_mode = os.environ.get("IITJ_GEMM_PAIR", "swiglu")   # off | swiglu | all
         self.defer_sums = os.environ.get("IITJ_DEFER_SUMS", "1") == "1"     # k-split sums added by the reading kernel
+        self.attention_splits = os.environ.get("IITJ_ATTN_SPLITS")         # forces the key splits of prefill attention
         self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
         if os.environ.get("IITJ_PDL", "1") == "0":
             self.lib.llm_set_pdl(0)
@@ -375,10 +377,18 @@ class Kernels:
                     self.lib.llm_attention_tcgen05_supported(heads, kv_heads, head_dim, page_size):
                 if plan.big_tiles is None:
                     plan.big_tiles = torch.tensor(plan.big_rows, dtype=torch.int32).to(qkv.device)
+                splits = self.prefill_key_splits(plan.big_rows, heads, kv_heads, int(window))
+                part_o = part_ml = None
+                if splits > 1:
+                    n = len(plan.big_rows) * heads * splits * 128
+                    part_o = self._scratch("attn.tc_part_o", n * head_dim, qkv.device)
+                    part_ml = self._scratch("attn.tc_part_ml", n * 2, qkv.device)
                 self._call("llm_attention_prefill_tcgen05", _ptr(qkv), qkv.shape[1], tokens, _ptr(cache_layer),
                            cache_layer.shape[0], _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.big_tiles),
                            len(plan.big_rows), _ptr(out), out.shape[1], heads, kv_heads, head_dim, page_size, int(window),
-                           float(scale), self._stream())
+                           float(scale), splits, _ptr(part_o), _ptr(part_ml), self._stream())
+                if splits > 1:
+                    self.launches += 1
             elif plan.n_tiles:
                 self._call("llm_attention_prefill_bf16", _ptr(qkv), qkv.shape[1], _ptr(cache_layer),
                            _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.tiles), plan.n_tiles, _ptr(out),
@@ -404,6 +414,31 @@ class Kernels:
         return out
 
     # ---- matrix products -------------------------------------------------------------
+    def prefill_key_splits(self, big_rows, heads, kv_heads, window) -> int:
+        """CTAs along the keys of each 128-query tile of the tcgen05 prefill attention.  The kernel is at its best
+        with two heads per CTA and about 1.7 CTAs per SM; a short portion of a prompt against a long context has
+        too few query tiles for that, so its keys are shared out.  This is the number of CTAs the launch provides
+        per tile and head; the kernel uses as many of them as leave each about 16 key tiles of 128, by the tile's
+        own context (a captured graph thus follows a prompt as it grows).
+        Measured at 32 heads / 8 key-value heads: 512 queries over 16384 keys 260 -> 209 us with 4 splits, over
+        32768 keys 510 -> 352 us; 128 queries over 16384 keys 254 -> 86 us."""
+        if self.attention_splits is not None:
+            return max(1, min(16, int(self.attention_splits)))
+        longest = max(min(pos0 + rows, window + rows) if window > 0 else pos0 + rows for _, rows, pos0, _ in big_rows)
+        if longest < self.LONG_PREFILL:               # no tile would use a second split: no merge kernel either
+            return 1
+        group = heads // kv_heads
+        pair_ctas = len(big_rows) * kv_heads * ((group + 1) // 2)
+        splits = max(1, min(16, round(1.7 * self.sm_count / pair_ctas)))
+        if pair_ctas * splits < self.sm_count:        # too few even so: the kernel then runs one head per CTA
+            splits = max(1, min(16, self.sm_count // (len(big_rows) * heads)))
+        return splits
+
+    # Context from which a query tile's keys may be shared out over two CTAs (24 key tiles of 128).  A step's
+    # captured graph freezes whether its prefill attention launches splits at all, so the step function keeps
+    # shorter and longer contexts apart in its graph keys.
+    LONG_PREFILL = 3072
+
     def linear(self, x, weight, out, swiglu: bool = False, defer: bool = False):
         """out = x . weight^T; with swiglu, weight holds gate rows then up rows and
         out = silu(x . gate^T) * (x . up^T).  With `defer` the result may come back as a PartialSums (the product

@@ -321,6 +321,27 @@ def test_attention_bf16_same_result_in_any_batch(K):
     assert torch.equal(out1[0], out[41])
 
 
+@pytest.mark.parametrize("heads,kv_heads,page,window,splits", [(8, 2, 16, 0, 3), (3, 1, 16, 0, 2), (4, 4, 32, 0, 5),
+                                                               (4, 2, 16, 700, 4), (2, 1, 8, 0, 16)])
+def test_attention_tcgen05_key_splits(K, heads, kv_heads, page, window, splits):
+    """The keys of a query tile shared out over several CTAs whose partial results a merge kernel adds: short
+    portions against long contexts, more splits than some tiles have key tiles, a window that leaves early splits
+    without a visible key for late rows."""
+    lens, qlens = [3000, 1500, 200, 2100], [200, 130, 200, 1]
+    q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, 128, page, lens, qlens, 140)
+    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, 128, window)
+    old = K.attention_splits
+    try:
+        for forced in (splits, None):
+            K.attention_splits = forced
+            out = torch.zeros(q.shape[0], heads * 128, device="cuda", dtype=torch.bfloat16)
+            K.attention(q, cache, meta, out, heads, kv_heads, 128, window=window)
+            close(out, want, torch.bfloat16)
+    finally:
+        K.attention_splits = old
+    assert K.attention_status() == 0
+
+
 # ---- k-split partial sums added by the kernel that reads the result ------------------------
 @pytest.mark.parametrize("rows,width,splits", [(9, 264, 3), (1, 96, 2), (40, 4096, 8), (5, 100, 4)])
 def test_add_rmsnorm_partial_sums(K, rows, width, splits):
