@@ -15,8 +15,9 @@
 //             the same 128 features and writes silu(gate) * up (engine/model.py:210-211,
 //             251-252), so the [T, 2I] intermediate is never written.
 //   split-K   when a product has too few tiles to fill the GPU, the k range is split over
-//             CTAs; partial sums go to float32 scratch and llm_gemm_bf16_reduce adds them in
-//             split order (and applies SwiGLU, or rounds to bfloat16).
+//             CTAs; partial sums go to float32 scratch and splitk_reduce_kernel adds them in
+//             split order (and applies SwiGLU, or rounds to bfloat16), unless the caller leaves the
+//             sums to the kernel that reads the result (`defer`: llm_add_rmsnorm, llm_rope_store).
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in a status
 // word (llm_gemm_bf16_status), and the CTA falls through to its teardown (TMEM is freed).

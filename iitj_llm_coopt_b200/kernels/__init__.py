@@ -6,8 +6,11 @@ CUDA device of compute capability 10.x, or without a working build, `load()` rai
 
 Every wrapper takes torch tensors that live on the GPU, checks dtype, shape and layout,
 and launches on torch's current stream.  Matrix products in float32 always run this
-library's FMA kernel; in bfloat16 they run cuBLAS through torch (`torch.mm`), the library
-the reference's engine uses for them (engine/model.py:194, F.linear).
+library's FMA kernel.  In bfloat16 they run this library's tcgen05 kernels where those are
+the faster ones (every product of a decode step of up to 32 tokens; the fused SwiGLU product
+up to 128 tokens and, on the CTA-pair kernel, from 640 tokens), else cuBLAS through torch
+(`torch.mm`), the library the reference's engine uses for them (engine/model.py:194,
+F.linear); `gemm_policy` holds the measurements behind the choice.
 """
 from __future__ import annotations
 
