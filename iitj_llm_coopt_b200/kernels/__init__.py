@@ -83,6 +83,10 @@ def _need(cond, msg):
 
 
 def _check(t, name, dtype=None, dims=None):
+    # the usual case in one expression (this runs several times per kernel launch); the messages are made below
+    if type(t) is torch.Tensor and t.is_cuda and t.is_contiguous() and (dims is None or t.dim() == dims) and \
+            (dtype is None or (t.dtype is dtype if type(dtype) is torch.dtype else t.dtype in dtype)):
+        return
     _need(isinstance(t, torch.Tensor), f"{name}: expected a tensor")
     _need(t.is_cuda, f"{name}: tensor is on {t.device}, the kernels run on the GPU only")
     if dtype is not None:
