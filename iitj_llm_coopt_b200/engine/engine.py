@@ -19,6 +19,8 @@ from .policy import StaticPolicy
 from .runner import StepEntry
 from .scheduler import Plan, Scheduler, Sequence
 
+PLACEHOLDER = -1       # stands in a token list for the token that the step in flight is sampling
+
 COUNTERS = ("prompt_tokens_total", "generation_tokens_total", "num_preemptions_total",
             "request_success_total", "request_failure_total", "steps_total", "step_seconds_total")
 
@@ -98,16 +100,18 @@ class Engine:
     # ---- one step ------------------------------------------------------------------------
     # A step is launched (scheduler, step function, sampling kernel, copy of the ids to the host) and
     # collected (ids read, tokens appended, stop rules, finish and free).  Without lookahead `step()` does
-    # both.  With lookahead a launched step stays in flight, and the next `step()` first launches its
-    # successor -- when that needs no scheduling decision: nobody waits, every running sequence got a token
-    # in the step in flight, the pages fit -- with the input tokens taken from the sampled ids on the
-    # device; only then does it collect the step in flight.  The GPU so never waits for the host.  Stops by
-    # max_tokens and max_model_len are known beforehand; a stop by EOS is seen one step late, and the token
-    # the successor computed for that sequence is dropped.
+    # both.  With lookahead a launched step stays in flight, and the next `step()` first plans and launches
+    # its successor and only then collects the step in flight, so the GPU never waits for the host.  The
+    # successor is planned as if the step in flight had already handed every sequence its token: a
+    # placeholder stands in the token list, and the successor takes that token from the sampled ids on the
+    # device.  Stops by max_tokens and max_model_len are known beforehand (those sequences are left out); a
+    # stop by EOS is seen one step late, and the token the successor computed for that sequence is dropped.
+    # The successor is only launched when its decodes need no preemption; else the step in flight is
+    # collected first and the scheduler decides with everything known.
     def step(self) -> bool:
         prev = self._inflight
         if prev is not None:
-            nxt = self._launch_follow(prev) if self._can_follow(prev) else None
+            nxt = self._launch_ahead(prev) if self.lookahead and hasattr(prev["handle"], "ids") else None
             self._inflight = None
             self._collect(prev)
             self._inflight = nxt
@@ -131,7 +135,7 @@ class Engine:
             self._collect(rec)
         return True
 
-    def _launch(self, plan) -> dict:
+    def _launch(self, plan, prev_ids=None) -> dict:
         t0 = time.perf_counter()
         entries, sampled = [], []         # sampled: sequences whose last fed token wants logits
         for s, end in plan.chunks:
@@ -141,9 +145,12 @@ class Engine:
             if last:
                 sampled.append(s)
         for s in plan.decodes:
-            entries.append(StepEntry(s.seq_id, [s.tokens[-1]], [0]))
+            if s.tokens[-1] == PLACEHOLDER:       # the step in flight is about to sample it: fed on the device
+                entries.append(StepEntry(s.seq_id, [0], [0], source_rows=[s.pending_row]))
+            else:
+                entries.append(StepEntry(s.seq_id, [s.tokens[-1]], [0]))
             sampled.append(s)
-        logits = self.runner.step(entries)
+        logits = self.runner.step(entries, prev_ids=prev_ids) if prev_ids is not None else self.runner.step(entries)
         for s, end in plan.chunks:
             self.counters["prompt_tokens_total"] += end - s.num_computed
             s.num_computed = end
@@ -163,25 +170,44 @@ class Engine:
         """True if the sequence stops for length once `extra` more tokens are appended."""
         return s.num_generated + extra >= s.max_tokens or len(s.tokens) + extra >= self.max_model_len
 
-    def _can_follow(self, prev) -> bool:
-        if not self.lookahead or prev["handle"] is None or self.scheduler.waiting:
-            return False
-        got = {id(s) for s in prev["sampled"]}
-        return all(id(s) in got for s in self.scheduler.running)
+    def _launch_ahead(self, prev):
+        """Plans and launches the step after `prev` while `prev` is still in flight; None if that cannot be done
+        without knowing prev's tokens (then nothing has changed)."""
+        sched, cache = self.scheduler, self.cache
+        cont = [(i, s) for i, s in enumerate(prev["sampled"]) if not s.finished and not self._ends_by_length(s)]
+        ending = [s for s in prev["sampled"] if not s.finished and self._ends_by_length(s)]
+        running_before = list(sched.running)
+        saved = [(s, s.num_computed) for _, s in cont]
+        for i, s in cont:                          # as if prev had handed over its tokens
+            s.tokens.append(PLACEHOLDER)
+            s.num_computed = len(s.tokens) - 1
+            s.pending_row = i
+        for s in ending:                           # they finish when prev is collected: not to be planned
+            if s in sched.running:
+                sched.running.remove(s)
 
-    def _launch_follow(self, prev):
-        """The step after `prev` for the sequences that go on decoding, fed from prev's ids on the device."""
-        t0 = time.perf_counter()
-        rows = [(i, s) for i, s in enumerate(prev["sampled"]) if not s.finished and not self._ends_by_length(s)]
-        if not rows:
+        def undo():
+            for s, n in saved:
+                s.tokens.pop()
+                s.num_computed, s.pending_row = n, None
+            sched.running[:] = running_before
             return None
-        need = sum(self.cache.extra_pages_needed(s.seq_id, self.cache.num_tokens(s.seq_id) + 1) for _, s in rows)
-        if need > self.cache.num_free:
-            return None                   # pages are short: collect first, then the scheduler decides who gives way
-        entries = [StepEntry(s.seq_id, [0], [0], source_rows=[i]) for i, s in rows]
-        logits = self.runner.step(entries, prev_ids=prev["handle"].ids)
-        seqs = [s for _, s in rows]
-        return self._sample(logits, seqs, [s.num_generated + 1 for s in seqs], len(entries), t0)
+
+        decodes = [s for s in sched.running if s.remaining == 1]
+        need = sum(cache.extra_pages_needed(s.seq_id, len(s.tokens)) for s in decodes)
+        if need > cache.num_free:                  # somebody would have to give way: decide that with prev known
+            return undo()
+        waiting_before = len(sched.waiting)
+        sched.held_slots = len(running_before) - len(sched.running)     # the ending ones keep slot and pages until collected
+        try:
+            plan = sched._schedule_once()
+        finally:
+            sched.held_slots = 0
+        if not plan:
+            if len(sched.waiting) != waiting_before:
+                raise RuntimeError("the scheduler admitted a request without planning it")
+            return undo()
+        return self._launch(plan, prev_ids=prev["handle"].ids)
 
     def _collect(self, rec) -> None:
         sampled, handle = rec["sampled"], rec["handle"]
@@ -192,8 +218,16 @@ class Engine:
         for s, tok in zip(sampled, new_tokens):
             if s.finished:
                 continue                  # it ended at EOS one step ago; this token was computed in vain
-            kept = self._append(s, [tok])
-            s.num_computed = len(s.tokens) - 1      # everything but the newly sampled token is cached
+            if s.pending_row is not None:
+                # the step after this one is already in flight and counts on this token: it takes the
+                # placeholder's place; length stops were ruled out before, EOS is what can still end it
+                s.tokens[-1], s.pending_row = tok, None
+                kept = [tok]
+                if not s.ignore_eos and tok in self.eos_ids:
+                    s.finish_reason = "stop"
+            else:
+                kept = self._append(s, [tok])
+                s.num_computed = len(s.tokens) - 1      # everything but the newly sampled token is cached
             self.counters["generation_tokens_total"] += len(kept)
             if s.first_token_time is None:
                 s.first_token_time = now

@@ -48,6 +48,7 @@ class Sequence:
     finished: bool = False
     finish_reason: str | None = None
     num_preemptions: int = 0
+    pending_row: int | None = None      # row of the step in flight whose sampled id is this sequence's last token
 
     def __post_init__(self):
         self.prompt_len = self.prompt_len or len(self.tokens)
@@ -76,6 +77,7 @@ class Scheduler:
         self.counters = counters if counters is not None else {"num_preemptions_total": 0}
         self.waiting: deque = deque()
         self.running: list = []
+        self.held_slots = 0          # request slots held by sequences that are not in `running` (about to finish)
 
     def _preempt(self, seq) -> None:
         """Drop the victim's cache; it is recomputed from position 0 when re-admitted."""
@@ -129,7 +131,7 @@ class Scheduler:
                 budget -= end - s.num_computed
 
         # 3. admissions
-        while self.waiting and budget > 0 and len(self.running) < pol.max_num_seqs:
+        while self.waiting and budget > 0 and len(self.running) + self.held_slots < pol.max_num_seqs:
             reserve = int(pol.watermark * cache.num_pages) if self.running else 0
             i = pol.pick_next(self.waiting, self.engine)
             s = self.waiting[i]

@@ -199,7 +199,7 @@ def test_many_random_requests_under_pressure(lively_dirs, name, dtype):
     prompts = [[rng.randrange(cfg_d["vocab_size"]) for _ in range(rng.choice([1, 2, 3, 7, 16, 17, 40, 90, 150]))]
                for _ in range(40)]
     params = [SamplingParams(max_tokens=rng.randint(1, 30), ignore_eos=True) for _ in prompts]
-    pages = -(-(150 + 30) // page) * 2            # room for two of the longest requests; six may run
+    pages = -(-(150 + 30) // page) * 3 // 2       # room for one and a half of the longest requests; six may run
     llm = LLM(lively_dirs[name], dtype=dtype, page_size=page, num_pages=pages, max_num_seqs=6, max_num_batched_tokens=48)
     outs = llm.generate(prompts, params)
     cfg, w = plain.read_model_dir(lively_dirs[name], torch.float32)

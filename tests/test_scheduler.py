@@ -224,3 +224,107 @@ def test_callbacks_report_every_token_once():
     eng.run_until_done()
     assert [t for new, _ in seen for t in new] == s.tokens[5:]
     assert [fin for _, fin in seen] == [False] * 5 + [True]
+
+
+# ---- lookahead: the next step is planned and launched before the one in flight is read ---------------------
+class Handle:
+    def __init__(self, ids):
+        self.ids = ids
+
+
+class LaunchSampler(FakeSampler):
+    """A sampler with the launch/fetch pair: what `launch` returns stays "on the device" until it is fetched."""
+
+    def __init__(self):
+        self.unfetched = 0
+
+    def launch(self, logits, rows):
+        assert len(logits) == len(rows)
+        self.unfetched += 1
+        return Handle(list(logits))
+
+    def fetch(self, handle):
+        self.unfetched -= 1
+        return list(handle.ids)
+
+
+class FedRunner(FakeRunner):
+    """Takes tokens from the previous step's ids where an entry names their rows, as the device does."""
+
+    def __init__(self, cache):
+        super().__init__(cache)
+        self.fed = 0
+
+    def step(self, entries, prev_ids=None):
+        for e in entries:
+            if e.source_rows is not None:
+                assert prev_ids is not None
+                e.tokens = [prev_ids[r] if r >= 0 else t for t, r in zip(e.tokens, e.source_rows)]
+                self.fed += 1
+            assert all(t >= 0 for t in e.tokens), "a placeholder reached the step function"
+        return super().step(entries)
+
+
+def make_ahead(pages=64, page=4, max_seqs=8, budget=64, watermark=0.0, max_model_len=10_000, eos=()):
+    cache = CacheManager([NEED], page_size=page, num_pages=pages, max_requests=max_seqs)
+    runner = FedRunner(cache)
+    pol = StaticPolicy(max_num_seqs=max_seqs, max_batched_tokens=budget, watermark=watermark)
+    eng = Engine(runner, cache, LaunchSampler(), pol, max_model_len=max_model_len, eos_ids=eos, lookahead=True)
+    return eng, runner, cache
+
+
+def test_lookahead_generates_the_same_tokens_under_every_schedule():
+    prompts = [prompt(i, n) for i, n in enumerate([1, 9, 40, 64, 130, 7, 33])]
+    lens = [12, 1, 2, 30, 5, 12, 3]
+    want = [expected(p, n) for p, n in zip(prompts, lens)]
+    for pages, budget, max_seqs in [(400, 2048, 8), (60, 16, 8), (48, 7, 3), (45, 33, 8), (200, 1, 2), (400, 64, 1)]:
+        eng, runner, cache = make_ahead(pages=pages, page=4, budget=budget, max_seqs=max_seqs, watermark=0.01)
+        seqs = [eng.new_sequence(p, n, ignore_eos=True) for p, n in zip(prompts, lens)]
+        eng.run_until_done()
+        assert [s.tokens[s.prompt_len:] for s in seqs] == want, (pages, budget, max_seqs)
+        assert all(s.finished and s.pending_row is None for s in seqs)
+        assert runner.fed > 0, "no step was launched ahead"
+        assert eng.sampler.unfetched == 0
+        cache.check()
+        assert cache.num_free == pages
+
+
+def test_lookahead_admits_and_cuts_prompts_beside_fed_decodes():
+    eng, runner, cache = make_ahead(pages=200, budget=16, max_seqs=4)
+    a = eng.new_sequence(prompt(0, 5), 20, ignore_eos=True)
+    eng.step()                                      # a's prompt is in flight
+    b = eng.new_sequence(prompt(1, 40), 4, ignore_eos=True)
+    eng.step()                                      # launched ahead: a's first decode (fed) and b's first portion
+    assert runner.log[-1] == [(b.seq_id, 15, []), (a.seq_id, 1, [0])]
+    assert a.num_generated == 1 and a.tokens[-1] == expected(prompt(0, 5), 1)[0] and a.pending_row is None
+    eng.run_until_done()
+    assert a.tokens[5:] == expected(prompt(0, 5), 20) and b.tokens[40:] == expected(prompt(1, 40), 4)
+    cache.check()
+
+
+def test_lookahead_frees_a_slot_only_when_the_ending_request_is_collected():
+    """A request about to end by length still holds its slot while its last step is in flight: the step
+    launched ahead must not admit into it."""
+    eng, runner, cache = make_ahead(pages=64, budget=64, max_seqs=2)
+    seqs = [eng.new_sequence(prompt(i, 6), n, ignore_eos=True) for i, n in enumerate([2, 9, 3, 3])]
+    eng.run_until_done()
+    for i, (s, n) in enumerate(zip(seqs, [2, 9, 3, 3])):
+        assert s.tokens[6:] == expected(prompt(i, 6), n)
+    cache.check()
+    assert cache.num_free == 64
+
+
+def test_lookahead_drops_the_token_computed_past_an_eos():
+    p = prompt(3, 6)
+    full = expected(p, 40)
+    eos = full[5]
+    cut = full.index(eos) + 1
+    eng, runner, cache = make_ahead(eos=(eos,))
+    s1 = eng.new_sequence(p, 40)
+    s2 = eng.new_sequence(prompt(4, 9), 25, ignore_eos=True)
+    eng.run_until_done()
+    assert s1.tokens[6:] == full[:cut] and s1.finish_reason == "stop"
+    assert s2.tokens[9:] == expected(prompt(4, 9), 25)
+    assert eng.counters["generation_tokens_total"] == cut + 25
+    cache.check()
+    assert cache.num_free == 64
