@@ -123,6 +123,7 @@ class CacheManager:
         self.paged = [i for i, g in enumerate(self.groups) if isinstance(g, PagedGroup)]
         # per-request records
         self.stored: dict = {}            # request -> tokens whose keys/values (or state) are in the cache
+        self.room: dict = {}              # request -> tokens that the pages it holds can take (least over the groups)
         self.slot_of: dict = {}           # request -> state slot
         self.free_slots: deque = deque(range(max_requests))
         self._views: dict = {}
@@ -182,6 +183,7 @@ class CacheManager:
         self.slot_of[request] = self.free_slots.popleft()
         for gi in self.paged:
             self.groups[gi].tables[request] = []
+        self._set_room(request)
         return self.slot_of[request]
 
     def has(self, request) -> bool:
@@ -203,6 +205,7 @@ class CacheManager:
                     n += 1
         self.free_slots.append(self.slot_of.pop(request))
         del self.stored[request]
+        del self.room[request]
         return n
 
     # ---- capacity ------------------------------------------------------------------------
@@ -221,16 +224,23 @@ class CacheManager:
 
     def extra_pages_needed(self, request, total_tokens: int) -> int:
         """Largest number of new pages any group needs so the request can hold total_tokens."""
+        if total_tokens <= self.room.get(request, 0):
+            return 0
         return max((self.groups[gi].extra_pages(request, total_tokens) for gi in self.paged), default=0)
 
     def can_fit(self, request, total_tokens: int) -> bool:
+        if total_tokens <= self.room.get(request, 0):
+            return True
         return all(self.groups[gi].extra_pages(request, total_tokens) <= self.groups[gi].pool.num_free
                    for gi in self.paged)
 
     def ensure(self, request, total_tokens: int) -> None:
         """Grow the request's tables so they can hold total_tokens tokens; all groups or none."""
-        if request not in self.stored:
+        room = self.room.get(request)
+        if room is None:
             raise CacheError(f"request {request!r} is not admitted")
+        if total_tokens <= room:
+            return
         for gi in self.paged:
             g = self.groups[gi]
             need = g.extra_pages(request, total_tokens)
@@ -241,6 +251,10 @@ class CacheManager:
             table = g.tables[request]
             for _ in range(g.extra_pages(request, total_tokens)):
                 table.append(g.pool.take())
+        self._set_room(request)
+
+    def _set_room(self, request) -> None:
+        self.room[request] = min((len(self.groups[gi].tables[request]) * self.page_size for gi in self.paged), default=1 << 62)
 
     def advance(self, request, total_tokens: int) -> None:
         """Records that the cache now holds the request's first total_tokens tokens, and gives
@@ -274,6 +288,7 @@ class CacheManager:
                 if p >= 0:
                     g.pool.give(p)
         self.stored[request] = min(self.stored[request], total_tokens)
+        self._set_room(request)
 
     # ---- what the step function needs ----------------------------------------------------
     def table(self, group: int, request) -> list:
@@ -314,3 +329,7 @@ class CacheManager:
         if len(used) != len(set(used)) or set(used) & set(self.free_slots) or \
                 len(used) + len(self.free_slots) != self.max_requests:
             raise CacheError("state slots are inconsistent")
+        for request in self.stored:
+            want = min((len(self.groups[gi].tables[request]) * self.page_size for gi in self.paged), default=1 << 62)
+            if self.room.get(request) != want:
+                raise CacheError(f"request {request!r}: recorded room {self.room.get(request)} but its pages take {want}")

@@ -44,7 +44,10 @@ class Workspace:
         key = (name, dtype)
         flat = self._flat.get(key)
         if flat is None or flat.numel() < n:
-            flat = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            # grown to the next power of two (in steps of 64 Mi elements beyond that), so that a buffer whose
+            # size creeps up step by step (one more logits row) is allocated a few times, not every step
+            cap = 1 << max(n - 1, 0).bit_length() if n <= (1 << 26) else -(-n // (1 << 26)) * (1 << 26)
+            flat = torch.empty(cap, dtype=dtype, device=self.device)
             self._flat[key] = flat
             self.generation += 1
         return flat[:n].view(*shape)

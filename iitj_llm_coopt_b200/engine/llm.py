@@ -37,12 +37,13 @@ class RequestOutput:
 
 
 def workspace_bytes_estimate(spec, tokens: int, rows: int, itemsize: int) -> int:
-    """Rough size of the step's scratch tensors for `tokens` tokens and `rows` logits rows."""
+    """Rough size of the step's scratch tensors for `tokens` tokens and `rows` logits rows (twice what the
+    shapes need: the workspace grows its buffers to powers of two)."""
     widest = 0
     for layer in spec.layers:
         m, f = layer.mixer, layer.feed_forward
         widest = max(widest, (m.heads + 2 * m.kv_heads) * m.head_dim + m.heads * m.head_dim + 3 * f.inner + 3 * spec.width)
-    return tokens * (widest * itemsize + 4 * spec.width) + rows * spec.vocab * 4 + (64 << 20)
+    return 2 * (tokens * (widest * itemsize + 4 * spec.width) + rows * spec.vocab * 4) + (64 << 20)
 
 
 def build_engine(model: str | None = None, engine_config: EngineConfig | None = None, *, config=None,

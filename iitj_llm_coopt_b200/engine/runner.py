@@ -55,6 +55,7 @@ class ModelRunner:
         self._meta = None            # int32 device buffer the step's index arrays live in
         self._mirror: dict = {}      # (group, request) -> [np.int32 array, filled, the table it mirrors]
         self._copied = None          # event: the last host-to-device copy of the staging buffer is done
+        self._capture_stream = None  # side stream that graph captures are recorded on
         self.steps = 0
 
     # ---- page-table mirror -----------------------------------------------------------
@@ -126,12 +127,20 @@ class ModelRunner:
         graph = torch.cuda.CUDAGraph()
         # The garbage collector must not run inside the capture: collecting an older engine there would
         # destroy its graphs, which CUDA forbids while a capture is open and which voids the capture.
+        # The capture is opened by hand rather than with torch.cuda.graph(), which first waits for the whole
+        # device and empties the allocator's cache: a step may be in flight, and the step's buffers exist already.
         gc_was_on = gc.isenabled()
-        gc.collect()
         gc.disable()
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream()
+        self._capture_stream.wait_stream(torch.cuda.current_stream())
         try:
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                logits = self.model.forward(ctx)
+            with torch.cuda.stream(self._capture_stream):
+                graph.capture_begin(capture_error_mode="thread_local")
+                try:
+                    logits = self.model.forward(ctx)
+                finally:
+                    graph.capture_end()
         finally:
             if gc_was_on:
                 gc.enable()

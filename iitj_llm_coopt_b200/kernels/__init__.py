@@ -222,6 +222,7 @@ class Kernels:
         self._pair_counters: dict = {}
         self.scratch_generation = 0
         self._sm_count = None
+        self._device_index = None
 
     @property
     def sm_count(self) -> int:
@@ -245,9 +246,11 @@ class Kernels:
             raise KernelError(f"{name} failed ({rc}): {self.lib.llm_last_error().decode()}")
         self.launches += 1
 
-    @staticmethod
-    def _stream():
-        return torch.cuda.current_stream().cuda_stream
+    def _stream(self):
+        """The raw handle of the current CUDA stream (inside a graph capture: the capturing stream)."""
+        if self._device_index is None:
+            self._device_index = torch.cuda.current_device()
+        return torch._C._cuda_getCurrentRawStream(self._device_index)
 
     def set_pdl(self, on: bool) -> bool:
         """Programmatic dependent launch for all later launches of this library; returns the old setting."""
