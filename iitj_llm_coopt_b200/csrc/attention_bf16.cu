@@ -9,7 +9,12 @@
 //                        range of keys ("split"); the group's query heads are the rows of the
 //                        16-row MMA tile, so a key/value tile is read once for the whole group.
 //                        With more than one split the partial (max, sum, output) go to scratch
-//                        memory and attn_merge_kernel combines them.
+//                        memory and attn_merge_kernel combines them.  Its FUSED form takes the
+//                        float32 k-split partial sums of the qkv product instead of finished
+//                        queries: every CTA adds and rotates its group's queries itself, and
+//                        the CTA whose keys end with the token adds, rotates and stores the
+//                        token's key and value (engine/model.py:199-203) and uses them from
+//                        shared memory, so no kernel runs between the product and the attention.
 //
 // Replaces flash_attn_varlen_func with block_table (engine/model.py:204-207, 244-247).
 // Softmax statistics, the running output and all sums are float32; P is rounded to bfloat16
@@ -304,16 +309,29 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
 // ---------------------------------------------------------------------------------------
 // part_o [items, heads, max_splits, D] float32 (unnormalised, relative to the split's max),
 // part_ml [items, heads, max_splits, 2] float32 (max in the log2 domain, sum).
-template <int D>
+// What the FUSED form reads instead of finished queries.
+struct QkvParts {
+    const float* parts;        // [splits][tokens][(heads + 2 kv_heads) * D] float32 partial sums of the qkv product
+    int splits;
+    size_t split_stride;       // elements between two splits
+    const float* cos_table;    // [tokens][D / 2]
+    const float* sin_table;
+    const int* slots;          // [tokens] page * page_size + offset of each token's key and value
+    bf16* cache;               // the same cache layer, for the store
+};
+
+template <int D, bool FUSED>
 __global__ void __launch_bounds__(kThreads)
 attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
                    const int* __restrict__ block_table, int table_width, const int* __restrict__ items,
                    const int* __restrict__ token_request, const int* __restrict__ positions,
                    float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out, int out_stride,
                    int heads, int kv_heads, int page_size, int page_shift, int window, float sl, int keys_per_split,
-                   int max_splits) {
+                   int max_splits, const QkvParts f) {
     pdl_trigger();
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(16) bf16 q_new[FUSED ? 16 * D : 8];      // FUSED: the group's rotated queries
+    __shared__ __align__(16) bf16 kv_new[FUSED ? 2 * D : 8];      // FUSED: the token's rotated key, its value
     bf16* kv = reinterpret_cast<bf16*>(smem_raw);                 // [kStages][K,V][64][D]
     const int split = blockIdx.x, hk = blockIdx.y, item = blockIdx.z;
     const int tok = items[item];
@@ -350,9 +368,60 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     if (!waited) pdl_wait();
     // page ids of the tile that the first iteration will request, fetched one iteration ahead from here on
     if (kStages - 1 < n_tiles) tile_pages<D>(pg, table, c0 + (kStages - 1) * kTile, pos, page_size, page_shift);
+    const bool owner = FUSED && c1 == pos + 1;                    // this CTA's keys end with the token itself
+    if constexpr (FUSED) {
+        // Items of four neighbouring dims: per rotated head D/8 of them (dims i.. and i + D/2..), per value head D/4.
+        // The arithmetic is that of rope_store_sum_kernel, and the results are rounded to bfloat16 as it rounds
+        // them, so both routes hand the same queries, keys and values to the products below.
+        constexpr int half = D / 2, hp = D / 8, per_head = D / 4;
+        const float* row = f.parts + (size_t)tok * ((size_t)(heads + 2 * kv_heads) * D);
+        const int n_q = G * hp;
+        const int n_work = n_q + (owner ? hp + per_head : 0);
+        size_t kdst = 0;
+        if (owner) {
+            const int slot = f.slots[tok];
+            const int page = page_shift >= 0 ? slot >> page_shift : slot / page_size;
+            const int off = page_shift >= 0 ? slot & (page_size - 1) : slot % page_size;
+            kdst = (size_t)page * 2 * plane + (size_t)hk * page_size * D + (size_t)off * D;
+        }
+        for (int w = threadIdx.x; w < n_work; w += kThreads) {
+            if (w < n_q + hp) {
+                const bool is_q = w < n_q;
+                const int h = is_q ? hk * G + w / hp : heads + hk;
+                const int i = (w % hp) * 4;
+                const float4 a = sum_parts4(row + (size_t)h * D + i, f.splits, f.split_stride);
+                const float4 b = sum_parts4(row + (size_t)h * D + i + half, f.splits, f.split_stride);
+                const float4 c = *reinterpret_cast<const float4*>(f.cos_table + (size_t)tok * half + i);
+                const float4 sg = *reinterpret_cast<const float4*>(f.sin_table + (size_t)tok * half + i);
+                uint2 lo2, hi2;
+                lo2.x = pack_bf16(a.x * c.x - b.x * sg.x, a.y * c.y - b.y * sg.y);
+                lo2.y = pack_bf16(a.z * c.z - b.z * sg.z, a.w * c.w - b.w * sg.w);
+                hi2.x = pack_bf16(b.x * c.x + a.x * sg.x, b.y * c.y + a.y * sg.y);
+                hi2.y = pack_bf16(b.z * c.z + a.z * sg.z, b.w * c.w + a.w * sg.w);
+                bf16* dst = is_q ? q_new + (w / hp) * D : kv_new;
+                *reinterpret_cast<uint2*>(dst + i) = lo2;
+                *reinterpret_cast<uint2*>(dst + i + half) = hi2;
+                if (!is_q) {
+                    *reinterpret_cast<uint2*>(f.cache + kdst + i) = lo2;
+                    *reinterpret_cast<uint2*>(f.cache + kdst + i + half) = hi2;
+                }
+            } else {
+                const int i = (w - n_q - hp) * 4;
+                const float4 v = sum_parts4(row + (size_t)(heads + kv_heads + hk) * D + i, f.splits, f.split_stride);
+                uint2 v2;
+                v2.x = pack_bf16(v.x, v.y);
+                v2.y = pack_bf16(v.z, v.w);
+                *reinterpret_cast<uint2*>(kv_new + D + i) = v2;
+                *reinterpret_cast<uint2*>(f.cache + kdst + plane + i) = v2;
+            }
+        }
+        __syncthreads();
+    }
     // the group's query heads are rows 0 .. G-1 of the MMA tile; the other rows are zero
     uint32_t qa[D / 16][4];
-    const bf16* qrow0 = q + (size_t)tok * q_stride + (size_t)(hk * G + g) * D;
+    const bf16* qrow0;
+    if constexpr (FUSED) qrow0 = q_new + g * D;
+    else qrow0 = q + (size_t)tok * q_stride + (size_t)(hk * G + g) * D;
     const bf16* qrow1 = qrow0 + 8 * D;
 #pragma unroll
     for (int kt = 0; kt < D / 16; ++kt) {
@@ -375,6 +444,20 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                              page_size, page_shift, 2 * plane);
         cp_async_commit();
         if (nxt + 1 < n_tiles) tile_pages<D>(pg, table, c0 + (nxt + 1) * kTile, pos, page_size, page_shift);
+        if constexpr (FUSED) if (owner && it == n_tiles - 1) {
+            // the copy fetched the token's slot as it was before this step: its row, and the rows after it (which
+            // repeat it and are masked), get the key and value computed above
+            constexpr int CH = D / 8;
+            const int r_new = pos - (c0 + it * kTile);
+            bf16* kt = stage_k(it % kStages);
+            bf16* vt = stage_v(it % kStages);
+            for (int i = threadIdx.x; i < (kTile - r_new) * CH; i += kThreads) {
+                const int r = r_new + i / CH, c = i % CH;
+                *reinterpret_cast<uint4*>(kt + tile_off<D>(r, c)) = *reinterpret_cast<const uint4*>(kv_new + c * 8);
+                *reinterpret_cast<uint4*>(vt + tile_off<D>(r, c)) = *reinterpret_cast<const uint4*>(kv_new + D + c * 8);
+            }
+            __syncthreads();
+        }
         const int k0 = c0 + it * kTile + warp * 16;               // this warp's 16 keys of the tile
         if (k0 < c1) {
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -500,7 +583,7 @@ int page_shift_of(int page_size) {
 }
 
 template <typename K> int set_smem(K kernel, size_t bytes, const char* name) {
-    if (bytes > 48 * 1024) {
+    if (bytes + 8 * 1024 > 48 * 1024) {        // (a kernel's static shared memory counts toward the 48 KiB that need no opt-in)
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
         if (e != cudaSuccess) LLM_FAIL(-2, "%s: %s", name, cudaGetErrorString(e));
     }
@@ -540,11 +623,49 @@ LLM_API int llm_attention_prefill_bf16(const void* q, int q_stride, const void* 
 
 // items: [n_items] token rows of the decoded tokens.  part_o needs n_items*heads*max_splits*head_dim floats,
 // part_ml n_items*heads*max_splits*2 floats (both unused when max_splits == 1).
+namespace {
+int launch_decode(const void* q, int q_stride, const void* cache, const int* block_table, int table_width, const int* items,
+                  int n_items, const int* token_request, const int* positions, float* part_o, float* part_ml, void* out,
+                  int out_stride, int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
+                  int keys_per_split, int max_splits, const QkvParts* fused, cudaStream_t stream);
+}
+
 LLM_API int llm_attention_decode_bf16(const void* q, int q_stride, const void* cache, const int* block_table,
                                       int table_width, const int* items, int n_items, const int* token_request,
                                       const int* positions, float* part_o, float* part_ml, void* out, int out_stride,
                                       int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
                                       int keys_per_split, int max_splits, cudaStream_t stream) {
+    return launch_decode(q, q_stride, cache, block_table, table_width, items, n_items, token_request, positions, part_o,
+                         part_ml, out, out_stride, heads, kv_heads, head_dim, page_size, window, scale, keys_per_split,
+                         max_splits, nullptr, stream);
+}
+
+// The same for single decoded tokens whose qkv product was left as k-split partial sums: `parts`
+// [splits][tokens][(heads + 2 kv_heads) * head_dim] float32 (`split_stride` elements apart, at most 8 splits),
+// cos / sin [tokens][head_dim / 2] of the tokens' positions (all dims rotated), `slots` [tokens] where each token's
+// key and value go in `cache`.  Adds the parts, rotates queries and keys, stores key and value, and attends, in
+// one kernel.  Every token of the step must be one of `items` (a token left out would never be stored).
+LLM_API int llm_attention_decode_bf16_fused(const float* parts, int splits, long long split_stride, const float* cos_table,
+                                            const float* sin_table, const int* slots, void* cache, const int* block_table,
+                                            int table_width, const int* items, int n_items, const int* token_request,
+                                            const int* positions, float* part_o, float* part_ml, void* out, int out_stride,
+                                            int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
+                                            int keys_per_split, int max_splits, cudaStream_t stream) {
+    if (!parts || !cos_table || !sin_table || !slots) LLM_FAIL(-1, "attention_decode_bf16_fused: parts, tables and slots are needed");
+    if (splits < 1 || splits > kMaxParts || split_stride % 4 || ((heads + 2 * kv_heads) * head_dim) % 4)
+        LLM_FAIL(-1, "attention_decode_bf16_fused: 1 to %d splits with a stride that is a multiple of 4 (got %d, %lld)",
+                 kMaxParts, splits, split_stride);
+    QkvParts f{parts, splits, (size_t)split_stride, cos_table, sin_table, slots, (bf16*)cache};
+    return launch_decode(nullptr, 0, cache, block_table, table_width, items, n_items, token_request, positions, part_o,
+                         part_ml, out, out_stride, heads, kv_heads, head_dim, page_size, window, scale, keys_per_split,
+                         max_splits, &f, stream);
+}
+
+namespace {
+int launch_decode(const void* q, int q_stride, const void* cache, const int* block_table, int table_width, const int* items,
+                  int n_items, const int* token_request, const int* positions, float* part_o, float* part_ml, void* out,
+                  int out_stride, int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
+                  int keys_per_split, int max_splits, const QkvParts* fused, cudaStream_t stream) {
     if (n_items == 0) return 0;
     if (!llm_attention_bf16_supported(heads, kv_heads, head_dim))
         LLM_FAIL(-1, "attention_decode_bf16: heads %d / kv_heads %d / head_dim %d not supported", heads, kv_heads, head_dim);
@@ -561,7 +682,8 @@ LLM_API int llm_attention_decode_bf16(const void* q, int q_stride, const void* c
         if (set_smem(kern, smem, "attention_decode_bf16")) return -2;
         llm_launch(kern, grid, kThreads, smem, stream, (const bf16*)q, q_stride, (const bf16*)cache, block_table, table_width, items,
                                                token_request, positions, part_o, part_ml, (bf16*)out, out_stride, heads,
-                                               kv_heads, page_size, page_shift, window, sl, keys_per_split, max_splits);
+                                               kv_heads, page_size, page_shift, window, sl, keys_per_split, max_splits,
+                                               fused ? *fused : QkvParts{});
         LLM_CHECK_LAUNCH("attention_decode_bf16");
         if (max_splits > 1) {
             llm_launch(merge, dim3(n_items, heads), D, 0, stream, part_o, part_ml, items, positions, (bf16*)out, out_stride, heads,
@@ -570,9 +692,13 @@ LLM_API int llm_attention_decode_bf16(const void* q, int q_stride, const void* c
         }
         return 0;
     };
-    return head_dim == 64 ? launch(attn_decode_kernel<64>, attn_merge_kernel<64>, 64)
-                          : launch(attn_decode_kernel<128>, attn_merge_kernel<128>, 128);
+    if (fused)
+        return head_dim == 64 ? launch(attn_decode_kernel<64, true>, attn_merge_kernel<64>, 64)
+                              : launch(attn_decode_kernel<128, true>, attn_merge_kernel<128>, 128);
+    return head_dim == 64 ? launch(attn_decode_kernel<64, false>, attn_merge_kernel<64>, 64)
+                          : launch(attn_decode_kernel<128, false>, attn_merge_kernel<128>, 128);
 }
+}  // namespace
 
 // ---------------------------------------------------------------------------------------
 // The same decode attention with its scratch inside the library (see llm_no_alloc.h).

@@ -65,6 +65,23 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
     return warp_sum(t);
 }
 
+// ---- partial sums of a k-split matrix product ---------------------------------------------
+// Sum of up to kMaxParts partial sums of four neighbouring elements, all loads in flight at once; the parts are
+// added in split order, so every kernel that reads a deferred sum gets the same value.
+constexpr int kMaxParts = 8;
+
+__device__ __forceinline__ float4 sum_parts4(const float* p, int splits, size_t split_stride) {
+    float4 e[kMaxParts];
+#pragma unroll
+    for (int k = 0; k < kMaxParts; ++k)
+        if (k < splits) e[k] = *reinterpret_cast<const float4*>(p + (size_t)k * split_stride);
+    float4 a = e[0];
+#pragma unroll
+    for (int k = 1; k < kMaxParts; ++k)
+        if (k < splits) { a.x += e[k].x; a.y += e[k].y; a.z += e[k].z; a.w += e[k].w; }
+    return a;
+}
+
 // ---- programmatic dependent launch ---------------------------------------------------------
 // Every kernel of this library is launched with the "programmatic stream serialization"
 // attribute (unless llm_set_pdl(0)): its CTAs may be scheduled while the kernel before it in

@@ -103,21 +103,6 @@ template <> struct Vec4<__nv_bfloat16> {
     }
 };
 
-// Sum of up to kMaxParts partial sums of four neighbouring elements, all loads in flight at once.
-constexpr int kMaxParts = 8;
-
-__device__ __forceinline__ float4 sum_parts4(const float* p, int splits, size_t split_stride) {
-    float4 e[kMaxParts];
-#pragma unroll
-    for (int k = 0; k < kMaxParts; ++k)
-        if (k < splits) e[k] = *reinterpret_cast<const float4*>(p + (size_t)k * split_stride);
-    float4 a = e[0];
-#pragma unroll
-    for (int k = 1; k < kMaxParts; ++k)
-        if (k < splits) { a.x += e[k].x; a.y += e[k].y; a.z += e[k].z; a.w += e[k].w; }
-    return a;
-}
-
 template <typename TD, typename TW, int PER_THREAD>
 __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                        const int* __restrict__ rows, const TW* __restrict__ weight,

@@ -52,6 +52,9 @@ _SIGNATURES = {
     "llm_attention_decode_bf16": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                   _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                   _c_float, _c_int, _c_int, _c_void_p],
+    "llm_attention_decode_bf16_fused": [_c_void_p, _c_int, ctypes.c_longlong, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                        _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p],
     "llm_attention_tcgen05_supported": [_c_int, _c_int, _c_int, _c_int],
     "llm_attention_prefill_tcgen05": [_c_void_p, _c_int, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p,
                                       _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
@@ -214,6 +217,7 @@ class Kernels:
         self.gemm_small_tokens = int(os.environ.get("IITJ_GEMM_SMALL_TOKENS", "128"))
         self.gemm_pair_mode = os.environ.get("IITJ_GEMM_PAIR", "swiglu")   # off | swiglu | all
         self.defer_sums = os.environ.get("IITJ_DEFER_SUMS", "1") == "1"     # k-split sums added by the reading kernel
+        self.fuse_decode = os.environ.get("IITJ_FUSE_DECODE", "1") != "0"   # rope + cache write inside decode attention
         self.attention_splits = os.environ.get("IITJ_ATTN_SPLITS")         # forces the key splits of prefill attention
         self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
         if os.environ.get("IITJ_PDL", "1") == "0":
@@ -421,6 +425,56 @@ class Kernels:
                    meta.block_table.shape[1], _ptr(meta.token_request), _ptr(meta.positions), _ptr(out),
                    out.shape[1], DTYPE_CODE[qkv.dtype], tokens, heads, kv_heads, head_dim, page_size,
                    int(window), float(scale), self._stream())
+        return out
+
+    def can_fuse_decode(self, qkv, meta, cache_layer, heads, kv_heads, head_dim) -> bool:
+        """True if `attention_decode_fused` takes this step: every token is a single decoded token, the qkv
+        product was left as at most eight partial sums, bfloat16 cache, a shape of the tensor-core kernel."""
+        if not (self.fuse_decode and isinstance(qkv, PartialSums) and 1 <= qkv.splits <= 8 and qkv.stride % 4 == 0):
+            return False
+        if cache_layer is None or cache_layer.dtype != torch.bfloat16 or qkv.out.dtype != torch.bfloat16:
+            return False
+        if not self.lib.llm_attention_bf16_supported(heads, kv_heads, head_dim):
+            return False
+        plan = attention_plan(meta, cache_layer.device)
+        return plan.n_tiles == 0 and plan.n_items == qkv.out.shape[0]
+
+    def attention_decode_fused(self, qkv, tables, slots, cache_layer, meta, out, heads, kv_heads, head_dim,
+                               window: int = 0, scale: float = 0.0):
+        """Decode attention straight from the qkv product's partial sums (`can_fuse_decode` holds): adds the
+        parts, rotates queries and keys with `tables` (cos, sin of `rope_tables`; every dim rotated), stores each
+        token's key and value at `slots`, attends over the paged cache.  One kernel (and the merge of key
+        splits) in place of rope_store + attention."""
+        cos, sin = tables
+        tokens = qkv.out.shape[0]
+        _check(qkv.parts, "attention_decode_fused.parts", torch.float32, 3)
+        _check(cos, "attention_decode_fused.cos", torch.float32, 2)
+        _check(sin, "attention_decode_fused.sin", torch.float32, 2)
+        _check(slots, "attention_decode_fused.slots", torch.int32, 1)
+        _check(cache_layer, "attention_decode_fused.cache", torch.bfloat16, 5)
+        _check(out, "attention_decode_fused.out", torch.bfloat16, 2)
+        _need(qkv.out.shape[1] == (heads + 2 * kv_heads) * head_dim, "attention_decode_fused: qkv width is not (heads+2*kv_heads)*head_dim")
+        _need(cos.shape == (tokens, head_dim // 2) and sin.shape == cos.shape, "attention_decode_fused: tables must be [tokens, head_dim/2]")
+        _need(slots.shape[0] == tokens and out.shape == (tokens, heads * head_dim), "attention_decode_fused: one slot and one output row per token")
+        _need(cache_layer.shape[1] == 2 and cache_layer.shape[2] == kv_heads and cache_layer.shape[4] == head_dim,
+              f"attention_decode_fused.cache: shape {tuple(cache_layer.shape)} does not fit kv_heads/head_dim")
+        _need(meta.token_request.shape[0] == tokens and meta.positions.shape[0] == tokens,
+              "attention_decode_fused: one token_request and one position per token")
+        if not scale:
+            scale = 1.0 / math.sqrt(head_dim)
+        plan = attention_plan(meta, out.device)
+        _need(plan.n_tiles == 0 and plan.n_items == tokens, "attention_decode_fused: every token must be a single decoded token")
+        kps, splits = plan.split(kv_heads, int(window), self.sm_count, head_dim, getattr(plan, 'context_bound', None))
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = self._scratch("attn.part_o", plan.n_items * heads * splits * head_dim, out.device)
+            part_ml = self._scratch("attn.part_ml", plan.n_items * heads * splits * 2, out.device)
+        self._call("llm_attention_decode_bf16_fused", _ptr(qkv.parts), qkv.splits, qkv.stride, _ptr(cos), _ptr(sin), _ptr(slots),
+                   _ptr(cache_layer), _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.items), plan.n_items,
+                   _ptr(meta.token_request), _ptr(meta.positions), _ptr(part_o), _ptr(part_ml), _ptr(out), out.shape[1],
+                   heads, kv_heads, head_dim, cache_layer.shape[3], int(window), float(scale), kps, splits, self._stream())
+        if splits > 1:
+            self.launches += 1      # the merge kernel
         return out
 
     # ---- matrix products -------------------------------------------------------------

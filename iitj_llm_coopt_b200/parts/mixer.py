@@ -49,11 +49,22 @@ class PagedAttention(Part):
         qkv = ctx.buffer("attn.qkv", (t, self.qkv_width), self.dtype)
         # a position encoding that says so takes the product's k-split partial sums and adds them as it reads
         qkv = self.k.linear(x, self.qkv, qkv, defer=getattr(self.position, "takes_partial_sums", False))
-        rotated = self.position.encode_and_store(ctx, qkv, view, meta.slots if call.write else None,
-                                                 self.heads, self.kv_heads)
-        qkv = rotated if rotated is not None else materialize(qkv)
         attn = ctx.buffer("attn.ctx", (t, self.heads * self.head_dim), self.dtype)
-        self.k.attention(qkv, view, meta, attn, self.heads, self.kv_heads, self.head_dim,
-                         window=self.window, scale=self.scale)
+        # A step of single decoded tokens whose position encoding hands over its tables: the attention kernel adds
+        # the product's parts, rotates, stores key and value, and attends (one kernel boundary less per layer).
+        tables = None
+        fused = getattr(self.k, "can_fuse_decode", None)
+        if call.write and fused is not None and hasattr(self.position, "decode_tables") and \
+                fused(qkv, meta, view, self.heads, self.kv_heads, self.head_dim):
+            tables = self.position.decode_tables(ctx)
+        if tables is not None:
+            self.k.attention_decode_fused(qkv, tables, meta.slots, view, meta, attn, self.heads, self.kv_heads,
+                                          self.head_dim, window=self.window, scale=self.scale)
+        else:
+            rotated = self.position.encode_and_store(ctx, qkv, view, meta.slots if call.write else None,
+                                                     self.heads, self.kv_heads)
+            qkv = rotated if rotated is not None else materialize(qkv)
+            self.k.attention(qkv, view, meta, attn, self.heads, self.kv_heads, self.head_dim,
+                             window=self.window, scale=self.scale)
         out = ctx.buffer("attn.out", (t, self.width), self.dtype)
         return self.k.linear(attn, self.o, out, defer=True)

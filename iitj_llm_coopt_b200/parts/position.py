@@ -60,6 +60,11 @@ class RotaryEmbedding(Part):
         return self.k.rope_store(qkv, ctx.positions, self.inv_freq, slots, cache_view, heads, kv_heads,
                                  self.head_dim, self.rotary_dim, tables=self.tables(ctx) if self.rotary_dim else None)
 
+    def decode_tables(self, ctx):
+        """(cos, sin) for a mixer whose decode kernel rotates and stores by itself, or None if this encoding
+        cannot be handed over like that (only part of the head is rotated)."""
+        return self.tables(ctx) if self.rotary_dim == self.head_dim else None
+
 
 class NoPosition(Part):
     graph_safe = True

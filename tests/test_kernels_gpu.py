@@ -526,3 +526,51 @@ def test_attention_tcgen05_far_key_and_page_edges(K):
         close(out, want, torch.bfloat16)
         assert (out.float() - 3.0).abs().max() < 0.1
     assert K.attention_status() == 0
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,window,splits", [
+    (8, 2, 128, 16, 0, 3), (32, 8, 128, 16, 0, 6), (16, 1, 64, 16, 0, 1), (6, 2, 64, 8, 0, 8), (4, 4, 128, 32, 0, 2),
+    (8, 2, 128, 16, 300, 4), (3, 1, 64, 4, 0, 5)])
+def test_attention_decode_fused(K, heads, kv_heads, head_dim, page, window, splits):
+    """Decode attention that takes the qkv product's partial sums: adds them, rotates, stores the token's key and
+    value and attends.  Against the plain rotation, store and attention; the slot of each token holds a
+    huge stale value beforehand, which must neither be read nor survive."""
+    from iitj_llm_coopt_b200.kernels import PartialSums
+    lens = [700, 300, 1000, 257, 64, 65, 1, 1500, 128, 129]
+    _, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lens, [1] * len(lens), 170)
+    tokens, width = len(lens), (heads + 2 * kv_heads) * head_dim
+    parts = rnd((splits, tokens, width), torch.float32, 171, 0.6)
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, head_dim, 2).float() / head_dim))).cuda()
+    pos = meta.positions.long()
+    slots = (meta.block_table[torch.arange(tokens, device="cuda"), pos // page].long() * page + pos % page).to(torch.int32)
+    meta.slots = slots
+    cache[(slots // page).long(), :, :, (slots % page).long(), :] = 3.0e4          # stale: would swamp everything
+    want_cache = cache.clone()
+    roped = R.ref_rope(parts.sum(0), meta.positions, inv_freq, heads, kv_heads, head_dim, head_dim).to(torch.bfloat16)
+    R.ref_store(want_cache, roped, slots, heads, kv_heads, head_dim)
+    want = R.ref_paged_attention(roped, want_cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads,
+                                 head_dim, window)
+    cos = torch.empty(tokens, head_dim // 2, device="cuda", dtype=torch.float32)
+    sin = torch.empty_like(cos)
+    K.rope_tables(meta.positions, inv_freq, cos, sin)
+    qkv = PartialSums(K, parts, torch.zeros(tokens, width, device="cuda", dtype=torch.bfloat16))
+    assert K.can_fuse_decode(qkv, meta, cache, heads, kv_heads, head_dim)
+    out = torch.empty(tokens, heads * head_dim, device="cuda", dtype=torch.bfloat16)
+    K.attention_decode_fused(qkv, (cos, sin), slots, cache, meta, out, heads, kv_heads, head_dim, window=window)
+    close(out, want, torch.bfloat16)
+    close(cache, want_cache, torch.bfloat16)
+    # the unfused route (rope_store, then attention) gives the same keys and values, bit for bit
+    cache2 = want_cache.clone()
+    cache2[(slots // page).long(), :, :, (slots % page).long(), :] = 3.0e4
+    K.rope_store(PartialSums(K, parts, torch.zeros(tokens, width, device="cuda", dtype=torch.bfloat16)), meta.positions,
+                 inv_freq, slots, cache2, heads, kv_heads, head_dim, head_dim, tables=(cos, sin))
+    assert torch.equal(cache2, cache)
+
+
+def test_attention_decode_fused_is_refused_for_mixed_steps(K):
+    from iitj_llm_coopt_b200.kernels import PartialSums
+    _, cache, meta = _paged_case(torch.bfloat16, 4, 2, 128, 16, [70, 33], [5, 1], 180)
+    parts = rnd((2, 6, 8 * 128), torch.float32, 181)
+    qkv = PartialSums(K, parts, torch.zeros(6, 8 * 128, device="cuda", dtype=torch.bfloat16))
+    assert not K.can_fuse_decode(qkv, meta, cache, 4, 2, 128)
+    assert not K.can_fuse_decode(qkv.out, meta, cache, 4, 2, 128)
