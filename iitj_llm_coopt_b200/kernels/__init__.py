@@ -215,6 +215,7 @@ class Kernels:
         # SwiGLU boundary, IITJ_PDL=0 switches programmatic dependent launch off (all for measurements)
         self.gemm_backend = os.environ.get("IITJ_GEMM_BACKEND", "auto")
         self.gemm_small_tokens = int(os.environ.get("IITJ_GEMM_SMALL_TOKENS", "128"))
+        self.gemm_plain_tokens = int(os.environ.get("IITJ_GEMM_PLAIN_TOKENS", "128"))   # plain products: tcgen05 up to here
         self.gemm_pair_mode = os.environ.get("IITJ_GEMM_PAIR", "swiglu")   # off | swiglu | all
         self.defer_sums = os.environ.get("IITJ_DEFER_SUMS", "1") == "1"     # k-split sums added by the reading kernel
         self.fuse_decode = os.environ.get("IITJ_FUSE_DECODE", "1") != "0"   # rope + cache write inside decode attention
@@ -592,7 +593,11 @@ class Kernels:
         the 256-row side) or "cublas".  Measured on B200 at the 8B shapes, in CUDA graphs with cold weights:
         up to 32 tokens the tcgen05 product with two or three CTAs per SM and up to eight k-splits matches
         or beats cuBLAS for every shape of the model (and its weight prefetch overlaps the kernel before
-        it); its fused SwiGLU form holds up to 128 tokens.  From about 640 tokens the pair kernel's fused
+        it); from there to 128 tokens it is 5-17 % behind by itself, but its k-split sums are added by the
+        kernels that read them and the decode attention takes them with the rotation fused in, so the whole
+        decode step is 3-5 % faster with it (batch 48 / 64 / 128 at 8192-token contexts: 12.4 -> 11.8, 15.3 ->
+        14.9, 27.7 -> 26.9 ms); beyond 128 tokens cuBLAS wins (batch 192: 14.6 against 15.2 ms).  The fused
+        SwiGLU form holds up to 128 tokens.  From about 640 tokens the pair kernel's fused
         SwiGLU product beats cuBLAS plus a separate activation kernel (2048 tokens: 330 against 365 us).  Its
         plain products stay about 7 % behind cuBLAS, which halves its operand traffic with multicast loads
         that this library does not use, so those stay on cuBLAS (IITJ_GEMM_PAIR=all moves them over)."""
@@ -600,7 +605,7 @@ class Kernels:
             return "cublas"
         if self.gemm_backend != "auto":
             return self.gemm_backend
-        if tokens <= (self.gemm_small_tokens if swiglu else min(32, self.gemm_small_tokens)):
+        if tokens <= (self.gemm_small_tokens if swiglu else min(self.gemm_plain_tokens, self.gemm_small_tokens)):
             return "tcgen05"
         if tokens >= 640 and (self.gemm_pair_mode == "all" or (swiglu and self.gemm_pair_mode == "swiglu")):
             return "pair"
