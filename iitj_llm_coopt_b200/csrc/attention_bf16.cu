@@ -172,9 +172,13 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* qtile = reinterpret_cast<bf16*>(smem_raw);              // [64][D]
     bf16* kv = qtile + kTile * D;                                 // [2 stages][K,V][64][D]
-    const int4 td = tiles[blockIdx.x];
+    // Blocks are handed out with x running fastest: the block's number in that order is cut so that all heads of
+    // one query tile follow each other, tiles taken from the end of the list (the host sorts it by context), so
+    // the tiles with the most keys start first and the short ones fill the gaps at the end of the launch.
+    const unsigned lin = blockIdx.x + gridDim.x * blockIdx.y;
+    const int4 td = tiles[gridDim.x - 1 - lin / gridDim.y];
     const int tok0 = td.x, rows = td.y, pos0 = td.z, req = td.w;
-    const int h = blockIdx.y, hk = h / (heads / kv_heads);
+    const int h = (int)(lin % gridDim.y), hk = h / (heads / kv_heads);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const int* table = block_table + (size_t)req * table_width;
     const size_t plane = (size_t)kv_heads * page_size * D;

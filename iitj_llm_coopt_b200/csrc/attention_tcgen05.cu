@@ -141,16 +141,21 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __shared__ volatile int failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int4 td = a.tiles[gridDim.x - 1 - blockIdx.x];           // longest tiles (latest queries) first
+    // Blocks are handed out with x running fastest: the block's number in that order is cut so that all heads of
+    // one query tile follow each other, and the tiles are taken from the end of the list (sorted by context on the
+    // host): the tiles with the most keys start first, the short ones fill the gaps at the end of the launch.
+    const unsigned lin = blockIdx.x + gridDim.x * blockIdx.y;
+    const int tile_id = (int)gridDim.x - 1 - (int)(lin / gridDim.y), by = (int)(lin % gridDim.y);
+    const int4 td = a.tiles[tile_id];
     const int tok0 = td.x, rows = td.y, pos0 = td.z, req = td.w;
     const int group = a.heads / a.kv_heads;
-    const int hk = blockIdx.y / a.pairs, pr = blockIdx.y - hk * a.pairs;
+    const int hk = by / a.pairs, pr = by - hk * a.pairs;
     const int head_a = hk * group + a.per_cta * pr;
     const int n_heads = (a.per_cta == 2 && 2 * pr + 1 < group) ? 2 : 1;      // heads this CTA serves
     const int pos_last = pos0 + rows - 1;
     const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
     // this CTA's share of the query tile's key tiles (all of them without splits)
-    const int tile_id = gridDim.x - 1 - blockIdx.x, split = blockIdx.z;
+    const int split = blockIdx.z;
     const int k_first = lo0 & ~(kKeys - 1);
     const int all_tiles = (pos_last - k_first) / kKeys + 1;
     // the launch allows a.splits CTAs per tile and head; a tile uses as many as leave each about 16 key tiles or more

@@ -148,6 +148,10 @@ class AttentionPlan:
                 for s in range(0, n, 2 * self.TILE):        # 128-query tiles of the tcgen05 kernel
                     big_rows.append((row + s, min(2 * self.TILE, n - s), total - n + s, b))
             row += n
+        # shortest contexts first: the prefill kernels walk these lists from their ends, so that the tiles with the most
+        # keys start first and the short ones fill the gaps at the end of the launch
+        big_rows.sort(key=lambda r: r[2] + r[1])
+        tile_rows.sort(key=lambda r: r[2] + r[1])
         self.big_rows, self.big_tiles = big_rows, None
         self.n_items, self.n_tiles = len(item_rows), len(tile_rows)
         self.items, self.tiles = items, tiles
