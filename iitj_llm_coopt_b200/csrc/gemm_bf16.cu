@@ -14,6 +14,10 @@
 //   SWIGLU    W holds gate rows then up rows; the CTA keeps two accumulators (gate, up) for
 //             the same 128 features and writes silu(gate) * up (engine/model.py:210-211,
 //             251-252), so the [T, 2I] intermediate is never written.
+//   HALF      the SwiGLU product of at most 16 tokens: the 128 MMA rows are 64 gate rows and the 64 up rows
+//             of the same features (two TMA boxes per stage), one accumulator; the epilogue warps that hold
+//             the up rows hand them to the warps with the gate rows through shared memory.  Twice as many
+//             CTAs as the form above, so the k range needs no split and no kernel adds partial sums.
 //   split-K   when a product has too few tiles to fill the GPU, the k range is split over
 //             CTAs; partial sums go to float32 scratch and splitk_reduce_kernel adds them in
 //             split order (and applies SwiGLU, or rounds to bfloat16), unless the caller leaves the
@@ -52,13 +56,15 @@ struct GemmArgs {
     int stages;
 };
 
-template <int N_TOK, bool SWIGLU>
+template <int N_TOK, bool SWIGLU, bool HALF = false>
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs a) {
+    static_assert(!HALF || (SWIGLU && N_TOK == 16), "the half-tile form is the SwiGLU product of at most 16 tokens");
     constexpr int kABytes = kFeatTile * kBlockK * 2;               // 16 KiB per weight tile
     constexpr int kBBytes = N_TOK * kBlockK * 2;
-    constexpr int kStageBytes = (SWIGLU ? 2 : 1) * kABytes + kBBytes;
-    constexpr int kTmemCols = (SWIGLU ? 2 : 1) * N_TOK < 32 ? 32 : (SWIGLU ? 2 : 1) * N_TOK;
+    constexpr int kWTiles = (SWIGLU && !HALF) ? 2 : 1;             // weight tiles (and accumulators) per stage
+    constexpr int kStageBytes = kWTiles * kABytes + kBBytes;
+    constexpr int kTmemCols = kWTiles * N_TOK < 32 ? 32 : kWTiles * N_TOK;
     static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns must be a power of two up to 512");
 
     extern __shared__ unsigned char smem_raw[];
@@ -68,7 +74,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __shared__ volatile int failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int feat0 = blockIdx.x * kFeatTile, split = blockIdx.y, tok0 = blockIdx.z * N_TOK;
+    const int feat0 = blockIdx.x * (HALF ? kFeatTile / 2 : kFeatTile), split = blockIdx.y, tok0 = blockIdx.z * N_TOK;
     const int kb0 = (int)((long long)split * a.k_blocks / a.splits), kb1 = (int)((long long)(split + 1) * a.k_blocks / a.splits);
     const int n_kb = kb1 - kb0;
     const int stages = a.stages;
@@ -99,11 +105,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             mbar_expect_tx(&full_bar[i], kStageBytes);
             const int k = (kb0 + i) * kBlockK;
             tma_load_2d(st, &map_w, &full_bar[i], k, feat0);
-            if (SWIGLU) tma_load_2d(st + kABytes, &map_w, &full_bar[i], k, a.up_row_offset + feat0);
+            if (SWIGLU) tma_load_2d(st + (HALF ? kABytes / 2 : kABytes), &map_w, &full_bar[i], k, a.up_row_offset + feat0);
         }
         pdl_wait();
         for (int i = 0; i < pre; ++i)
-            tma_load_2d(tiles + (size_t)i * kStageBytes + (SWIGLU ? 2 : 1) * kABytes, &map_x, &full_bar[i],
+            tma_load_2d(tiles + (size_t)i * kStageBytes + kWTiles * kABytes, &map_x, &full_bar[i],
                         (kb0 + i) * kBlockK, tok0);
         for (int i = pre; i < n_kb; ++i) {
             const int s = i % stages;
@@ -112,8 +118,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             mbar_expect_tx(&full_bar[s], kStageBytes);
             const int k = (kb0 + i) * kBlockK;
             tma_load_2d(st, &map_w, &full_bar[s], k, feat0);
-            if (SWIGLU) tma_load_2d(st + kABytes, &map_w, &full_bar[s], k, a.up_row_offset + feat0);
-            tma_load_2d(st + (SWIGLU ? 2 : 1) * kABytes, &map_x, &full_bar[s], k, tok0);
+            if (SWIGLU) tma_load_2d(st + (HALF ? kABytes / 2 : kABytes), &map_w, &full_bar[s], k, a.up_row_offset + feat0);
+            tma_load_2d(st + kWTiles * kABytes, &map_x, &full_bar[s], k, tok0);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ---------------------------------------------------------------------
@@ -124,13 +130,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (!mbar_wait(&full_bar[s], (i / stages) & 1)) { give_up(2); failed = 1; ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             unsigned char* st = tiles + (size_t)s * kStageBytes;
-            const uint64_t da = umma_desc(st), db = umma_desc(st + (SWIGLU ? 2 : 1) * kABytes);
-            const uint64_t da2 = SWIGLU ? umma_desc(st + kABytes) : 0;
+            const uint64_t da = umma_desc(st), db = umma_desc(st + kWTiles * kABytes);
+            const uint64_t da2 = kWTiles == 2 ? umma_desc(st + kABytes) : 0;
 #pragma unroll
             for (int k = 0; k < kBlockK / 16; ++k) {
                 const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
                 umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);          // +32 bytes per K step of 16
-                if (SWIGLU) umma_f16(tmem_base + N_TOK, da2 + 2 * k, db + 2 * k, idesc, acc);
+                if (kWTiles == 2) umma_f16(tmem_base + N_TOK, da2 + 2 * k, db + 2 * k, idesc, acc);
             }
             umma_commit(&empty_bar[s]);           // the stage is free once these MMAs have read it
         }
@@ -140,6 +146,34 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int quarter = warp & 3;             // a warp may only read TMEM lanes [32 * (warp % 4), +32)
         const int feat = feat0 + quarter * 32 + lane;
         pdl_wait();                               // nothing is stored before the previous kernel has finished
+        if constexpr (HALF) {
+            // lanes 0-63 of the accumulator are gate rows, lanes 64-127 the up rows of the same 64 features
+            __shared__ float up_rows[N_TOK * (kFeatTile / 2)];
+            const bool ok = n_kb > 0 && mbar_wait(&accum_bar, 0) && !failed;
+            if (!ok && n_kb > 0 && !failed) give_up(3);
+            uint32_t g[16];
+            const int f = (quarter & 1) * 32 + lane;              // feature of this lane inside the tile
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16), g);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (quarter >= 2) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) up_rows[c * (kFeatTile / 2) + f] = __uint_as_float(g[c]);
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps, whatever happened above
+            if (ok && quarter < 2 && feat0 + f < a.n_feat) {
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const int tok = tok0 + c;
+                    if (tok >= a.tokens) break;
+                    const float gv = __uint_as_float(g[c]);
+                    const float v = gv / (1.0f + expf(-gv)) * up_rows[c * (kFeatTile / 2) + f];
+                    ((bf16*)a.out)[(size_t)tok * a.ldc + feat0 + f] = __float2bfloat16_rn(v);
+                }
+            }
+        } else
         if (n_kb > 0 && mbar_wait(&accum_bar, 0) && !failed) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -270,9 +304,9 @@ int llm_tensor_map_2d(const void* ptr, uint64_t rows, uint64_t cols, uint32_t bo
 
 namespace {
 
-template <int N_TOK, bool SWIGLU>
+template <int N_TOK, bool SWIGLU, bool HALF = false>
 int launch_tile(const CUtensorMap& mw, const CUtensorMap& mx, GemmArgs a, dim3 grid, cudaStream_t stream) {
-    constexpr int stage_bytes = (SWIGLU ? 2 : 1) * kFeatTile * kBlockK * 2 + N_TOK * kBlockK * 2;
+    constexpr int stage_bytes = ((SWIGLU && !HALF) ? 2 : 1) * kFeatTile * kBlockK * 2 + N_TOK * kBlockK * 2;
     // shared memory for the ring: 200 KiB (one CTA per SM), or about half of it when the caller wants two
     // CTAs per SM (more CTAs in flight for products with few tiles)
     int stages = ((a.stages > 0 ? a.stages : 200) * 1024) / stage_bytes;
@@ -280,7 +314,7 @@ int launch_tile(const CUtensorMap& mw, const CUtensorMap& mx, GemmArgs a, dim3 g
     if (stages < 2) stages = 2;
     a.stages = stages;
     const size_t smem = (size_t)stages * stage_bytes + 1024;
-    auto kern = gemm_tn_kernel<N_TOK, SWIGLU>;
+    auto kern = gemm_tn_kernel<N_TOK, SWIGLU, HALF>;
     static size_t configured = 0;              // largest size set so far, one per instantiation
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -305,8 +339,9 @@ LLM_API int llm_gemm_bf16_token_tile(int tokens) {
 // unless `defer` is set: then the partial sums [splits][tokens][n] stay in scratch for the kernel that reads
 // the result (llm_add_rmsnorm, llm_rope_store) and `out` is not written.
 // smem_kb: shared memory of one CTA's ring in KiB (0 = 200: one CTA per SM; about 100 lets two CTAs share an SM).
+// half: the SwiGLU product of at most 16 tokens with 64 gate and 64 up rows per CTA (n % 64 == 0, no split).
 LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, int tokens, int n, int K, int ldc,
-                          int swiglu, int splits, float* scratch, int smem_kb, int defer, cudaStream_t stream) {
+                          int swiglu, int splits, float* scratch, int smem_kb, int defer, int half, cudaStream_t stream) {
     if (tokens == 0 || n == 0) return 0;
     if (K % 8) LLM_FAIL(-1, "gemm_bf16: K %d must be a multiple of 8", K);
     if (swiglu && out_f32) LLM_FAIL(-1, "gemm_bf16: the SwiGLU variant writes bfloat16");
@@ -317,8 +352,10 @@ LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, 
     if (splits > 1 && (n % 4)) LLM_FAIL(-1, "gemm_bf16: split-K needs n %% 4 == 0");
     const int w_rows = swiglu ? 2 * n : n;
     const int tile = llm_gemm_bf16_token_tile(tokens);
+    if (half && (!swiglu || tile != 16 || n % (kFeatTile / 2) || splits != 1))
+        LLM_FAIL(-1, "gemm_bf16: the half-tile form is the unsplit SwiGLU product of at most 16 tokens with n %% 64 == 0");
     CUtensorMap mw, mx;
-    if (int rc = llm_tensor_map_2d(w, w_rows, K, kFeatTile, kBlockK, &mw)) return rc;
+    if (int rc = llm_tensor_map_2d(w, w_rows, K, half ? kFeatTile / 2 : kFeatTile, kBlockK, &mw)) return rc;
     if (int rc = llm_tensor_map_2d(x, tokens, K, tile, kBlockK, &mx)) return rc;
     GemmArgs a;
     a.out = splits > 1 ? (void*)scratch : out;
@@ -330,9 +367,13 @@ LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, 
     a.k_blocks = k_blocks;
     a.splits = splits;
     a.stages = smem_kb;          // launch_tile turns the budget into a stage count
-    dim3 grid((n + kFeatTile - 1) / kFeatTile, splits, (tokens + tile - 1) / tile);
+    dim3 grid(half ? n / (kFeatTile / 2) : (n + kFeatTile - 1) / kFeatTile, splits, (tokens + tile - 1) / tile);
     if (grid.y > 65535 || grid.z > 65535) LLM_FAIL(-1, "gemm_bf16: grid out of range");
     int rc;
+    if (half) {
+        rc = launch_tile<16, true, true>(mw, mx, a, grid, stream);
+        return rc;
+    }
 #define LLM_GEMM_CASE(T)                                                                       \
     case T: rc = swiglu ? launch_tile<T, true>(mw, mx, a, grid, stream) : launch_tile<T, false>(mw, mx, a, grid, stream); break;
     switch (tile) {

@@ -64,7 +64,7 @@ _SIGNATURES = {
                      _c_void_p],
     "llm_gemm_bf16_token_tile": [_c_int],
     "llm_gemm_bf16": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
-                      _c_int, _c_int, _c_void_p],
+                      _c_int, _c_int, _c_int, _c_void_p],
     "llm_gemm_bf16_status": [],
     "llm_gemm_bf16_pair": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                            _c_void_p, _c_void_p],
@@ -222,6 +222,8 @@ class Kernels:
         self.gemm_plain_tokens = int(os.environ.get("IITJ_GEMM_PLAIN_TOKENS", "128"))   # plain products: tcgen05 up to here
         self.gemm_pair_mode = os.environ.get("IITJ_GEMM_PAIR", "swiglu")   # off | swiglu | all
         self.defer_sums = os.environ.get("IITJ_DEFER_SUMS", "1") == "1"     # k-split sums added by the reading kernel
+        self.swiglu_half_tokens = int(os.environ.get("IITJ_SWIGLU_HALF_TOKENS", "8"))   # half-tile SwiGLU product up to here
+        self.swiglu_half_smem_kb = int(os.environ.get("IITJ_SWIGLU_HALF_KB", "100"))
         self.fuse_decode = os.environ.get("IITJ_FUSE_DECODE", "1") != "0"   # rope + cache write inside decode attention
         self.attention_splits = os.environ.get("IITJ_ATTN_SPLITS")         # forces the key splits of prefill attention
         self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
@@ -528,6 +530,9 @@ class Kernels:
         tokens, k = x.shape
         policy = self.gemm_policy(tokens, n, k, swiglu)
         if policy == "tcgen05":
+            if swiglu and tokens <= self.swiglu_half_tokens and n % 64 == 0:
+                # a handful of tokens: 64 gate + 64 up rows per CTA, twice the CTAs, no k-split and no kernel after it
+                return self.gemm_tcgen05(x, weight, out, True, 1, self.swiglu_half_smem_kb, half=True)
             splits, smem_kb = self.gemm_plan(tokens, n, k, swiglu)
             return self.gemm_tcgen05(x, weight, out, swiglu, splits, smem_kb, defer=defer and not swiglu and self.defer_sums)
         if policy == "pair":
@@ -541,9 +546,11 @@ class Kernels:
             torch.mm(x, weight.t(), out=out)
         return out
 
-    def gemm_tcgen05(self, x, weight, out, swiglu: bool = False, splits: int = 1, smem_kb: int = 0, defer: bool = False):
+    def gemm_tcgen05(self, x, weight, out, swiglu: bool = False, splits: int = 1, smem_kb: int = 0, defer: bool = False,
+                     half: bool = False):
         """out = x . weight^T on this library's tcgen05 kernel (bfloat16 in, bfloat16 or float32 out).  With `defer`
-        and more than one split the partial sums are returned as a PartialSums instead of being added here."""
+        and more than one split the partial sums are returned as a PartialSums instead of being added here.
+        `half`: the SwiGLU product of at most 16 tokens with 64 gate and 64 up rows per CTA (unsplit, n % 64 == 0)."""
         _check(x, "gemm.x", torch.bfloat16, 2)
         _check(weight, "gemm.weight", torch.bfloat16, 2)
         _check(out, "gemm.out", (torch.bfloat16, torch.float32), 2)
@@ -557,7 +564,7 @@ class Kernels:
         defer = bool(defer and splits > 1 and not swiglu)
         self._call("llm_gemm_bf16", _ptr(x), _ptr(weight), _ptr(out), 1 if out.dtype == torch.float32 else 0, tokens,
                    n, k, out.shape[1], 1 if swiglu else 0, splits, _ptr(scratch), int(smem_kb), 1 if defer else 0,
-                   self._stream())
+                   1 if half else 0, self._stream())
         if defer:
             return PartialSums(self, scratch[:splits * tokens * n].view(splits, tokens, n), out)
         if splits > 1:

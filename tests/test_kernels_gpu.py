@@ -436,6 +436,21 @@ def test_gemm_tcgen05_swiglu(K, tokens, n, k, splits):
     assert K.gemm_status() == 0
 
 
+@pytest.mark.parametrize("tokens,n,k", [(1, 64, 64), (8, 192, 1024), (16, 448, 4104), (5, 1024, 200), (3, 14336, 4096)])
+def test_gemm_tcgen05_swiglu_half_tiles(K, tokens, n, k):
+    """The SwiGLU product of a few tokens with 64 gate rows and 64 up rows in one 128-row MMA tile."""
+    x, w = rnd((tokens, k), torch.bfloat16, 304), rnd((2 * n, k), torch.bfloat16, 305, 0.2)
+    for kb in (0, 100, 66):
+        out = torch.full((tokens, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+        before = K.launches
+        K.gemm_tcgen05(x, w, out, swiglu=True, smem_kb=kb, half=True)
+        assert K.launches - before == 1
+        close(out, R.ref_linear(x, w, swiglu=True), torch.bfloat16, 0.5)
+    assert K.gemm_status() == 0
+    with pytest.raises(Exception):
+        K.gemm_tcgen05(rnd((17, k), torch.bfloat16, 1), w, torch.zeros(17, n, device="cuda", dtype=torch.bfloat16), swiglu=True, half=True)
+
+
 def test_gemm_tcgen05_row_does_not_depend_on_batch(K):
     """With the same split count a token's row is bitwise the same alone and among others."""
     x, w = rnd((50, 264), torch.bfloat16, 106), rnd((200, 264), torch.bfloat16, 107, 0.05)
