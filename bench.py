@@ -279,7 +279,10 @@ def main() -> int:
 
         budget = engine.policy.max_batched_tokens
         engine.policy.max_batched_tokens = B * C          # all prompts in one prefill step, then decode steps only
-        WE, KE = W, max(K, 64)                     # untimed decode steps (graph capture among them), timed ones
+        # untimed decode steps, then timed ones.  The untimed ones take in the three eager sightings of the step's
+        # shape, its capture into a graph, and the clocks' recovery from the prompts' prefill (65k tokens at full
+        # power), which the first dozen decode steps still show.
+        WE, KE = max(W, 24), max(K, 64)
         seqs = [engine.new_sequence(p, WE + KE + 1, 0.0, True, None, on_out) for p in prompts]
         engine.run_until_done()
         torch.cuda.synchronize()
