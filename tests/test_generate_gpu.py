@@ -237,3 +237,50 @@ def test_padded_decode_batches(lively_dirs, name, dtype):
             assert margins_ok(cfg, w, p, o.token_ids, 0.05)
     runner = llm.engine.runner
     assert runner.padded_steps > 0 and runner.graph_replays > 0
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("D", "bfloat16")])
+def test_lookahead_changes_no_token(lively_dirs, name, dtype):
+    """The same requests with and without launching steps ahead: greedy and temperature rows, a request that stops
+    at an end-of-sequence token among others that go on, a tight pool and a roomy one.  Token for token the same."""
+    import random, shutil, tempfile
+    cfg_d, seed, page = CONFIGS[name]
+    rng = random.Random(77 + seed)
+    prompts = [[rng.randrange(cfg_d["vocab_size"]) for _ in range(rng.choice([1, 3, 9, 30, 64, 100]))] for _ in range(14)]
+    params = [SamplingParams(max_tokens=rng.randint(1, 24), temperature=0.7 if i % 3 == 0 else 0.0, seed=300 + i)
+              for i in range(len(prompts))]
+    d = tempfile.mkdtemp()
+    try:
+        shutil.copy(os.path.join(lively_dirs[name], "model.safetensors"), d)
+        raw = json.load(open(os.path.join(lively_dirs[name], "config.json")))
+        # an end-of-sequence id that greedy decoding of the first prompts meets early
+        probe = LLM(lively_dirs[name], dtype=dtype, page_size=page, num_pages=128, lookahead=False)
+        first = probe.generate(prompts[:4], SamplingParams(max_tokens=12, ignore_eos=True))
+        raw["eos_token_id"] = first[1].token_ids[5]
+        del probe
+        json.dump(raw, open(os.path.join(d, "config.json"), "w"))
+        runs = {}
+        for ahead in (False, True):
+            for pages, budget, seqs in ((128, 512, 8), (-(-130 // page) * 2, 24, 3)):
+                llm = LLM(d, dtype=dtype, page_size=page, num_pages=pages, max_num_seqs=seqs, max_num_batched_tokens=budget,
+                          seed=9, lookahead=ahead)
+                outs = llm.generate(prompts, params)
+                runs[(ahead, pages)] = [(o.token_ids, o.finish_reason) for o in outs]
+                assert llm.engine.lookahead == ahead
+                llm.engine.cache.check()
+                assert llm.engine.cache.num_free == pages
+                del llm
+        keys = list(runs)
+        if dtype == "float32":
+            assert all(runs[k] == runs[keys[0]] for k in keys)
+        else:
+            # bfloat16: another schedule means other batch sizes, other k-splits and other rounding, so a near-tie may
+            # fall the other way; greedy rows must follow the plain implementation wherever its margin is clear
+            cfg, w = plain.read_model_dir(lively_dirs[name], torch.float32)
+            for k in keys:
+                for i, (p, sp) in enumerate(zip(prompts, params)):
+                    if sp.temperature == 0.0:
+                        assert margins_ok(cfg, w, p, runs[k][i][0], 0.05), (k, i)
+        assert any(reason == "stop" for _, reason in runs[keys[0]])
+    finally:
+        shutil.rmtree(d)
