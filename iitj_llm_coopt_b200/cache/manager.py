@@ -26,6 +26,7 @@ from __future__ import annotations
 from collections import deque
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 
@@ -73,6 +74,17 @@ class PagedGroup:
     page_size: int
     tables: dict = field(default_factory=dict)      # request -> [page id or -1]
     storage: torch.Tensor | None = None             # [entries, pages, 2, kv_heads, page_size, head_dim]
+    # The tables once more, as the step function copies them to the device: row s holds the page ids of the
+    # request in state slot s (0 where it has no page, or gave it back), the last row is the padding row.
+    matrix: np.ndarray | None = None                # [max_requests + 1, columns] int32
+    lengths: np.ndarray | None = None               # [max_requests + 1] int32: len(tables[request]) by slot
+
+    def columns(self, n: int) -> None:
+        """Makes room for tables of n pages."""
+        if n > self.matrix.shape[1]:
+            grown = np.zeros((self.matrix.shape[0], max(n, 2 * self.matrix.shape[1])), dtype=np.int32)
+            grown[:, :self.matrix.shape[1]] = self.matrix
+            self.matrix = grown
 
     def pages_for(self, tokens: int) -> int:
         return -(-tokens // self.page_size)
@@ -121,6 +133,13 @@ class CacheManager:
             self.entry_group.append((g, len(self.groups[g].entries)))
             self.groups[g].entries.append(entry)
         self.paged = [i for i, g in enumerate(self.groups) if isinstance(g, PagedGroup)]
+        self.windowed = any(self.groups[i].need.window > 0 for i in self.paged)
+        for i in self.paged:
+            g = self.groups[i]
+            g.matrix = np.zeros((max_requests + 1, 16), dtype=np.int32)
+            g.matrix[max_requests, 0] = num_pages            # the padding row: one page, the padding page
+            g.lengths = np.zeros(max_requests + 1, dtype=np.int32)
+            g.lengths[max_requests] = 1
         # per-request records
         self.stored: dict = {}            # request -> tokens whose keys/values (or state) are in the cache
         self.room: dict = {}              # request -> tokens that the pages it holds can take (least over the groups)
@@ -183,6 +202,7 @@ class CacheManager:
         self.slot_of[request] = self.free_slots.popleft()
         for gi in self.paged:
             self.groups[gi].tables[request] = []
+            self.groups[gi].lengths[self.slot_of[request]] = 0
         self._set_room(request)
         return self.slot_of[request]
 
@@ -197,12 +217,16 @@ class CacheManager:
         if request not in self.stored:
             raise CacheError(f"request {request!r} is not admitted (released twice?)")
         n = 0
+        slot = self.slot_of[request]
         for gi in self.paged:
             g = self.groups[gi]
-            for p in g.tables.pop(request):
+            table = g.tables.pop(request)
+            for p in table:
                 if p >= 0:
                     g.pool.give(p)
                     n += 1
+            g.matrix[slot, :len(table)] = 0
+            g.lengths[slot] = 0
         self.free_slots.append(self.slot_of.pop(request))
         del self.stored[request]
         del self.room[request]
@@ -246,11 +270,17 @@ class CacheManager:
             need = g.extra_pages(request, total_tokens)
             if need > g.pool.num_free:
                 raise OutOfPages(f"request {request!r} needs {need} pages in group {gi}, {g.pool.num_free} free")
+        slot = self.slot_of[request]
         for gi in self.paged:
             g = self.groups[gi]
             table = g.tables[request]
+            old = len(table)
             for _ in range(g.extra_pages(request, total_tokens)):
                 table.append(g.pool.take())
+            if len(table) > old:
+                g.columns(len(table))
+                g.matrix[slot, old:len(table)] = table[old:]
+                g.lengths[slot] = len(table)
         self._set_room(request)
 
     def _set_room(self, request) -> None:
@@ -261,11 +291,12 @@ class CacheManager:
         back the pages that a window has passed."""
         if total_tokens < self.stored[request]:
             raise CacheError("advance cannot go backwards; use truncate")
-        for gi in self.paged:
-            g = self.groups[gi]
-            if g.pages_for(total_tokens) > len(g.tables[request]):
-                raise CacheError(f"request {request!r}: {total_tokens} tokens exceed its reserved pages")
+        if total_tokens > self.room[request]:
+            raise CacheError(f"request {request!r}: {total_tokens} tokens exceed its reserved pages")
         self.stored[request] = total_tokens
+        if not self.windowed:
+            return
+        slot = self.slot_of[request]
         for gi in self.paged:
             g = self.groups[gi]
             table = g.tables[request]
@@ -273,6 +304,21 @@ class CacheManager:
                 if table[lp] >= 0:
                     g.pool.give(table[lp])
                     table[lp] = -1
+                    g.matrix[slot, lp] = 0
+
+    def advance_all(self, requests: list, totals: list) -> None:
+        """`advance` for every request of a step."""
+        if self.windowed:
+            for request, total in zip(requests, totals):
+                self.advance(request, total)
+            return
+        stored, room = self.stored, self.room
+        for request, total in zip(requests, totals):
+            if total < stored[request]:
+                raise CacheError("advance cannot go backwards; use truncate")
+            if total > room[request]:
+                raise CacheError(f"request {request!r}: {total} tokens exceed its reserved pages")
+            stored[request] = total
 
     def truncate(self, request, total_tokens: int) -> None:
         """Forget tokens beyond total_tokens and give back the trailing pages
@@ -283,10 +329,14 @@ class CacheManager:
             keep = g.pages_for(total_tokens)
             if any(p < 0 for p in table[g.first_needed_page(total_tokens):keep]):
                 raise CacheError("truncate would need pages that a window already gave back")
+            old = len(table)
             while len(table) > keep:
                 p = table.pop()
                 if p >= 0:
                     g.pool.give(p)
+            if old > keep:
+                g.matrix[self.slot_of[request], keep:old] = 0
+                g.lengths[self.slot_of[request]] = keep
         self.stored[request] = min(self.stored[request], total_tokens)
         self._set_room(request)
 
@@ -325,6 +375,15 @@ class CacheManager:
                 raise CacheError(f"group {gi}: {g.pool.num_pages - len(free) - len(in_tables)} pages are lost")
             if set(g.tables) != set(self.stored):
                 raise CacheError(f"group {gi}: tables exist for other requests than the admitted ones")
+            rows = np.zeros_like(g.matrix)
+            rows[self.max_requests, 0] = self.num_pages
+            sizes = np.zeros_like(g.lengths)
+            sizes[self.max_requests] = 1
+            for request, table in g.tables.items():
+                rows[self.slot_of[request], :len(table)] = [max(p, 0) for p in table]
+                sizes[self.slot_of[request]] = len(table)
+            if not (np.array_equal(rows, g.matrix) and np.array_equal(sizes, g.lengths)):
+                raise CacheError(f"group {gi}: the table matrix differs from the tables")
         used = list(self.slot_of.values())
         if len(used) != len(set(used)) or set(used) & set(self.free_slots) or \
                 len(used) + len(self.free_slots) != self.max_requests:

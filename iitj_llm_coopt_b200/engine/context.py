@@ -35,9 +35,22 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._flat: dict = {}
+        self._views: dict = {}   # (name, dtype, shape) -> the view handed out last time (same storage, same shape)
         self.generation = 0      # bumped whenever a buffer is (re)allocated: captured graphs then hold stale addresses
 
     def get(self, name: str, shape, dtype) -> torch.Tensor:
+        # every layer of every step asks for the same few (name, shape) pairs: the view is made once
+        vkey = (name, dtype, shape if type(shape) is tuple else tuple(shape))
+        view = self._views.get(vkey)
+        if view is not None:
+            return view
+        view = self._make(name, vkey[2], dtype)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[vkey] = view
+        return view
+
+    def _make(self, name: str, shape, dtype) -> torch.Tensor:
         n = 1
         for s in shape:
             n *= int(s)
@@ -49,6 +62,7 @@ class Workspace:
             cap = 1 << max(n - 1, 0).bit_length() if n <= (1 << 26) else -(-n // (1 << 26)) * (1 << 26)
             flat = torch.empty(cap, dtype=dtype, device=self.device)
             self._flat[key] = flat
+            self._views.clear()      # views of the old storage must not be handed out again
             self.generation += 1
         return flat[:n].view(*shape)
 

@@ -53,42 +53,18 @@ class ModelRunner:
         self.workspace = Workspace(device)
         self._pinned = None          # int32 staging buffer (host, pinned)
         self._meta = None            # int32 device buffer the step's index arrays live in
-        self._mirror: dict = {}      # (group, request) -> [np.int32 array, filled, the table it mirrors]
         self._copied = None          # event: the last host-to-device copy of the staging buffer is done
         self._capture_stream = None  # side stream that graph captures are recorded on
         self.steps = 0
 
-    # ---- page-table mirror -----------------------------------------------------------
-    def _table_row(self, group: int, request) -> np.ndarray:
-        table = self.cache.table(group, request)
-        n = len(table)
-        rec = self._mirror.get((group, request))
-        if rec is None or rec[2] is not table:
-            rec = [np.zeros(max(16, 2 * n), dtype=np.int32), 0, table]
-            self._mirror[(group, request)] = rec
-        arr, filled, _ = rec
-        if n > arr.shape[0]:
-            grown = np.zeros(2 * n, dtype=np.int32)
-            grown[:filled] = arr[:filled]
-            rec[0] = arr = grown
-        if n < filled:
-            rec[1] = filled = n
-        if n > filled:
-            arr[filled:n] = [max(p, 0) for p in table[filled:n]]
-            rec[1] = n
-        return arr[:n]
-
     def forget(self, request) -> None:
-        """Drop what the runner remembers about a request that was released."""
-        for gi in self.cache.paged:
-            self._mirror.pop((gi, request), None)
+        """Told when a request was released.  The runner keeps nothing per request (the cache manager holds the
+        block tables in the form the device wants), so there is nothing to drop."""
 
     # ---- staging ---------------------------------------------------------------------
     def _stage(self, total: int):
         if self._copied is not None:
             self._copied.synchronize()     # the staging buffer is about to be overwritten
-        if len(self._mirror) > 8 * self.cache.max_requests + 64:
-            self._mirror = {k: v for k, v in self._mirror.items() if self.cache.has(k[1])}
         if self._pinned is None or self._pinned.numel() < total:
             cap = max(4096, 2 * total)
             self._pinned = torch.empty(cap, dtype=torch.int32).pin_memory() if torch.cuda.is_available() \
@@ -168,28 +144,29 @@ class ModelRunner:
         if not entries:
             return None
         cache = self.cache
-        seen = set()
-        starts, qlens, seqlens, slots_b = [], [], [], []
+        stored, room, slot_of = cache.stored, cache.room, cache.slot_of
+        starts, qlens, slots_b = [], [], []
+        N = 0
         for e in entries:
-            if e.request in seen:
-                raise ValueError(f"request {e.request!r} appears twice in one step")
-            seen.add(e.request)
-            n = len(e.tokens)
+            r, n = e.request, len(e.tokens)
             if n == 0:
-                raise ValueError(f"request {e.request!r} brings no tokens")
-            start = cache.num_tokens(e.request)
-            cache.ensure(e.request, start + n)     # a no-op when the scheduler has reserved
+                raise ValueError(f"request {r!r} brings no tokens")
+            start = stored[r]
+            if start + n > room[r]:
+                cache.ensure(r, start + n)         # (the scheduler has reserved already: this is the replay's path)
             starts.append(start)
             qlens.append(n)
-            seqlens.append(start + n)
-            slots_b.append(cache.state_slot(e.request))
+            slots_b.append(slot_of[r])
             for w in e.want:
                 if not 0 <= w < n:
-                    raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
-        T, B = sum(qlens), len(entries)
-        N = sum(len(e.want) for e in entries)
+                    raise ValueError(f"request {r!r}: wanted place {w} is outside its {n} tokens")
+            N += len(e.want)
+        B = len(entries)
+        if len(set(slots_b)) != B:
+            twice = next(e.request for i, e in enumerate(entries) if slots_b[i] in slots_b[:i])
+            raise ValueError(f"request {twice!r} appears twice in one step")
+        T = sum(qlens)
         groups = cache.paged
-        rows = {g: [self._table_row(g, e.request) for e in entries] for g in groups}
         # A decode step (one token and one wanted row per request) is padded to the next batch size of a short
         # ladder, so that batches which shrink by a request every few steps still meet captured graphs.  A padding
         # row is a one-token request at position 0 whose block table and state slot are the cache's padding page
@@ -201,22 +178,22 @@ class ModelRunner:
             self.padded_steps += 1
             starts += [0] * pad
             qlens += [1] * pad
-            seqlens += [1] * pad
             slots_b += [cache.pad_slot] * pad
-            pad_row = np.asarray([cache.pad_page], dtype=np.int32)
-            for g in groups:
-                rows[g] += [pad_row] * pad
             T, B, N = T + pad, B + pad, N + pad
-        widths = {g: max(1, max(r.shape[0] for r in rows[g])) for g in groups}
+        decode_shaped = T == B and N == B
+        q, st = np.asarray(qlens, dtype=np.int64), np.asarray(starts, dtype=np.int64)
+        slot_rows = np.asarray(slots_b, dtype=np.int64)
+        seqlens = (st + q).tolist()
+        # the block tables come from the cache manager's matrix (one row per state slot) in one gather per group
+        widths = {g: max(1, int(cache.groups[g].lengths[slot_rows].max())) for g in groups}
         # A step whose shape (tokens per request, wanted rows, table width) has been seen before can be
         # replayed from a captured graph if the index arrays keep their places, so the block tables are
         # padded to a power of two of pages.  Decode steps repeat at once; prompt portions of the same
         # length (a chunked prefill under a token budget) repeat too.
         graphable = self.use_graphs
-        decode_shaped = T == B and N == B
         if graphable:
             widths = {g: max(16, 1 << (w - 1).bit_length()) for g, w in widths.items()}
-        plan = AttentionPlan(qlens, seqlens, self.device, items=False, tiles=False)
+        plan = AttentionPlan(qlens, seqlens, self.device, items=False, tiles=False, total_tokens=T)
         if graphable and plan.n_items:
             # the split choice of decode attention is frozen into a graph: fix it by an upper bound of
             # the contexts, in steps of 512 tokens, and capture anew when the batch outgrows the bound
@@ -253,40 +230,50 @@ class ModelRunner:
         ids = np.zeros(T, dtype=np.int64)
         ids[:T - pad] = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=T - pad)
         if fed:
-            src = np.concatenate([np.asarray(e.source_rows if e.source_rows is not None else [-1] * len(e.tokens),
-                                             dtype=np.int64) for e in entries] + [np.full(pad, -1, dtype=np.int64)])
+            src = np.full(T, -1, dtype=np.int64)
+            if decode_shaped:
+                src[:T - pad] = [e.source_rows[0] if e.source_rows is not None else -1 for e in entries]
+            else:
+                src[:T - pad] = [r for e in entries
+                                 for r in (e.source_rows if e.source_rows is not None else [-1] * len(e.tokens))]
             put("token_src", src)
             ids = np.where(src >= 0, 0, ids)          # placeholders: the device fills them in
         if ids.min() < 0 or ids.max() >= self.vocab:
             raise ValueError(f"token id out of range [0, {self.vocab}) in this step")
         put("token_ids", ids)
         cu = np.zeros(B + 1, dtype=np.int64)
-        np.cumsum(qlens, out=cu[1:])
-        put("positions", np.concatenate([np.arange(s, s + n) for s, n in zip(starts, qlens)]))
-        put("token_request", np.repeat(np.arange(B), qlens))
+        np.cumsum(q, out=cu[1:])
+        if T == B:
+            token_request, positions = np.arange(B), st
+        else:
+            token_request = np.repeat(np.arange(B), q)
+            positions = np.arange(T) - np.repeat(cu[:-1] - st, q)
+        put("positions", positions)
+        put("token_request", token_request)
         put("cu_seqlens", cu)
         put("seq_lens", seqlens)
-        put("logit_rows", [int(cu[b]) + w for b, e in enumerate(entries) for w in e.want] + [int(cu[B - pad + i]) for i in range(pad)])
-        put("state_slots", slots_b)
-        put("first_portion", [1 if s == 0 else 0 for s in starts])
+        if decode_shaped:
+            put("logit_rows", cu[:-1])
+        else:
+            first = cu.tolist()
+            put("logit_rows", [first[b] + w for b, e in enumerate(entries) for w in e.want])
+        put("state_slots", slot_rows)
+        put("first_portion", st == 0)
         if plan.n_items:
             put("attn_items", plan.item_rows)
         if plan.n_tiles:
             put("attn_tiles", np.asarray(plan.tile_rows, dtype=np.int64).reshape(-1))
             put("attn_big_tiles", np.asarray(plan.big_rows, dtype=np.int64).reshape(-1))
         ps = cache.page_size
-        slots_host = {}
+        page_of, offset_in = positions // ps, positions % ps
         for g in groups:
-            slots = np.concatenate([
-                rows[g][b][np.arange(s, s + n) // ps].astype(np.int64) * ps + np.arange(s, s + n) % ps
-                for b, (s, n) in enumerate(zip(starts, qlens))])
-            put(f"slots{g}", slots)
-            slots_host[g] = slots
+            matrix = cache.groups[g].matrix
             o, _ = layout[f"table{g}"]
             tab = host[o:o + B * widths[g]].reshape(B, widths[g])
-            tab[:] = 0
-            for b, r in enumerate(rows[g]):
-                tab[b, :r.shape[0]] = r
+            cols = min(widths[g], matrix.shape[1])
+            tab[:, :cols] = matrix[slot_rows, :cols]
+            tab[:, cols:] = 0
+            put(f"slots{g}", tab[token_request, page_of].astype(np.int64) * ps + offset_in)
         self._meta[:off].copy_(self._pinned[:off], non_blocking=True)
         if self._meta.is_cuda:
             if self._copied is None:
@@ -319,14 +306,13 @@ class ModelRunner:
                           query_lens=qlens, starts=starts, slots_host=slots_b)
         if graphable:
             # (a long context switches the prefill attention to key splits: such steps get graphs of their own)
-            long_prefill = any(n > 1 and end >= LONG_PREFILL for n, end in zip(qlens, seqlens))
-            key = (tuple(qlens), tuple(len(e.want) for e in entries) + (1,) * pad, tuple(sorted(widths.items())),
-                   plan.context_bound, fed, long_prefill)
+            long_prefill = not decode_shaped and any(n > 1 and end >= LONG_PREFILL for n, end in zip(qlens, seqlens))
+            shape = ("decode", B) if decode_shaped else (tuple(qlens), tuple(len(e.want) for e in entries))
+            key = (shape, tuple(sorted(widths.items())), plan.context_bound, fed, long_prefill)
             logits = self._forward_graphed(key, ctx, eager_runs=self.graph_after if decode_shaped else max(4, self.graph_after))
         else:
             logits = self.model.forward(ctx)
-        for e, end in zip(entries, seqlens):
-            cache.advance(e.request, end)
+        cache.advance_all([e.request for e in entries], seqlens)
         self.steps += 1
         if pad and logits is not None:
             logits = logits[:N - pad]

@@ -135,9 +135,11 @@ class AttentionPlan:
 
     TILE = 64
 
-    def __init__(self, query_lens, seq_lens, device, items=None, tiles=None):
+    def __init__(self, query_lens, seq_lens, device, items=None, tiles=None, total_tokens=None):
         self.decode_pos = []
         item_rows, tile_rows, big_rows, row = [], [], [], 0
+        if total_tokens is not None and total_tokens == len(query_lens):      # one token each: all decode items
+            item_rows, self.decode_pos, query_lens = list(range(total_tokens)), [t - 1 for t in seq_lens], ()
         for b, (n, total) in enumerate(zip(query_lens, seq_lens)):
             if n == 1:
                 item_rows.append(row)
@@ -231,6 +233,7 @@ class Kernels:
             self.lib.llm_set_pdl(0)
         self._scratch_bufs: dict = {}
         self._pair_counters: dict = {}
+        self._linear_plans: dict = {}    # (tokens, n, k, swiglu) -> (kernel, k-splits, shared memory, half-tile form)
         self.scratch_generation = 0
         self._sm_count = None
         self._device_index = None
@@ -528,12 +531,26 @@ class Kernels:
             return out
         # bfloat16: this library's tcgen05 kernel where it is the faster one, else cuBLAS through torch
         tokens, k = x.shape
-        policy = self.gemm_policy(tokens, n, k, swiglu)
+        # which kernel, and how it is cut, depends on the shape alone: decided once per shape
+        pkey = (tokens, n, k, swiglu)
+        plan = self._linear_plans.get(pkey)
+        if plan is None:
+            policy = self.gemm_policy(tokens, n, k, swiglu)
+            if policy == "tcgen05":
+                if swiglu and tokens <= self.swiglu_half_tokens and n % 64 == 0:
+                    # a handful of tokens: 64 gate + 64 up rows per CTA, twice the CTAs, no k-split and no kernel after it
+                    plan = ("tcgen05", 1, self.swiglu_half_smem_kb, True)
+                else:
+                    plan = ("tcgen05",) + tuple(self.gemm_plan(tokens, n, k, swiglu)) + (False,)
+            else:
+                plan = (policy, 1, 0, False)
+            if len(self._linear_plans) > 8192:
+                self._linear_plans.clear()
+            self._linear_plans[pkey] = plan
+        policy, splits, smem_kb, half = plan
         if policy == "tcgen05":
-            if swiglu and tokens <= self.swiglu_half_tokens and n % 64 == 0:
-                # a handful of tokens: 64 gate + 64 up rows per CTA, twice the CTAs, no k-split and no kernel after it
-                return self.gemm_tcgen05(x, weight, out, True, 1, self.swiglu_half_smem_kb, half=True)
-            splits, smem_kb = self.gemm_plan(tokens, n, k, swiglu)
+            if half:
+                return self.gemm_tcgen05(x, weight, out, True, 1, smem_kb, half=True)
             return self.gemm_tcgen05(x, weight, out, swiglu, splits, smem_kb, defer=defer and not swiglu and self.defer_sums)
         if policy == "pair":
             return self.gemm_pair(x, weight, out, swiglu)
