@@ -1,5 +1,5 @@
 // Paged causal attention for prompt portions on the fifth-generation tensor cores
-// (bfloat16, head size 128, page sizes 8 .. 128 that divide 128).
+// (bfloat16, head sizes 64 and 128, page sizes 8 .. 128 that divide 128).
 //
 // One CTA = 128 query positions of one request x two query heads of one key/value group (the last head of
 // a group with an odd number of heads runs alone).  Both heads see the same keys, so every key/value tile
@@ -8,12 +8,12 @@
 // walk through shared memory in tiles of 128 keys; each page of a tile is one TMA box per 64-dim half,
 // placed at its row offset of the 128-byte-swizzled tile, so the paged cache needs no gather pass.
 //
-//   S = Q K^T      tcgen05.mma, M = 128 queries, N = 128 keys, K = 128 dims, both operands K-major in
+//   S = Q K^T      tcgen05.mma, M = 128 queries, N = 128 keys, K = the head's dims, both operands K-major in
 //                  shared memory; S lands in tensor memory (128 float32 columns per head).
 //   softmax        four warps per head, one thread per query row: it reads its row of S with tcgen05.ld (a
 //                  TMEM lane is a row: no shuffles), masks by position, takes the maximum, exponentiates in
 //                  float32 and writes P as bfloat16 back over the first 64 columns of S (tcgen05.st).
-//   O += P V       tcgen05.mma with P read from tensor memory and V MN-major from shared memory (a key's 128
+//   O += P V       tcgen05.mma with P read from tensor memory and V MN-major from shared memory (a key's
 //                  dims are contiguous, so the V tile is used as it was loaded); O stays in tensor memory for
 //                  the whole sequence of key tiles.
 //   rescaling      P is taken relative to a running maximum that is only moved when a row's maximum has
@@ -35,12 +35,11 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int kRows = 128;        // queries per CTA and head (UMMA M)
 constexpr int kKeys = 128;        // keys per tile
-constexpr int kDim = 128;         // head size
-constexpr int kHalfBytes = 128 * 128;          // one 64-column half of a [128 x 128] bf16 tile: 128 rows x 128 bytes
-constexpr int kTileBytes = 2 * kHalfBytes;     // 32 KiB
+constexpr int kHalfBytes = 128 * 128;          // 64 dims of 128 rows (queries or keys) as bf16: 128 rows x 128 bytes
+template <int D> __host__ __device__ constexpr int tile_bytes() { return (D / 64) * kHalfBytes; }   // a [128 x D] tile: 16 or 32 KiB
 constexpr int kThreads = 320;     // warp 0: loads, warp 1: MMA + TMEM, warps 2-5: softmax of head A, warps 6-9: of head B
 constexpr int kGroupThreads = 128;
-constexpr uint32_t kTmemCols = 512;            // S_A | S_B | O_A | O_B, 128 float32 columns each
+constexpr uint32_t kTmemCols = 512;            // S_A | S_B | O_A | O_B, 128 float32 columns each (O uses the head's dims)
 constexpr int kMinSplitTiles = 16;              // key tiles per split, about (the count of splits is rounded)
 constexpr float kRescaleStep = 8.0f;           // in log2 units: P stays below 2^8
 
@@ -128,10 +127,13 @@ struct AttnArgs {
     float sl;                     // softmax scale * log2(e)
 };
 
+template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             const AttnArgs a) {
     extern __shared__ unsigned char smem_raw[];
+    constexpr int kDim = D, kTileBytes = tile_bytes<D>(), kHalves = D / 64;
+    static_assert(D == 64 || D == 128, "head sizes 64 and 128");
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_tile[2] = {base, base + kTileBytes};                          // head A, head B
     unsigned char* k_tile[2] = {base + 2 * kTileBytes, base + 3 * kTileBytes};
@@ -189,12 +191,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     if (warp == 0) {
         // ---- loads: lane 0 keeps the barriers, lane p fetches page p of every tile (its block-table entry
-        //      and the four boxes of that page: K and V, two 64-dim halves each) ----------------------------
+        //      and the boxes of that page: K and V, one per 64 dims) --------------------------------------
         if (lane == 0) {
             mbar_expect_tx(&q_full, n_heads * kTileBytes);
             for (int x = 0; x < n_heads; ++x) {
-                tma_load_2d(q_tile[x], &map_q, &q_full, (head_a + x) * kDim, tok0);
-                tma_load_2d(q_tile[x] + kHalfBytes, &map_q, &q_full, (head_a + x) * kDim + 64, tok0);
+#pragma unroll
+                for (int h = 0; h < kHalves; ++h)
+                    tma_load_2d(q_tile[x] + h * kHalfBytes, &map_q, &q_full, (head_a + x) * kDim + 64 * h, tok0);
             }
         }
         const int* table = a.block_table + (size_t)req * a.table_width;
@@ -218,10 +221,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const int row = (page * 2 * a.kv_heads + hk) * ps;               // K rows of this page; V rows kv_heads * ps further
                 unsigned char* kd = k_tile[s] + lane * ps * 128;
                 unsigned char* vd = v_tile[s] + lane * ps * 128;
-                tma_load_2d(kd, &map_kv, &k_full[s], 0, row);
-                tma_load_2d(kd + kHalfBytes, &map_kv, &k_full[s], 64, row);
-                tma_load_2d(vd, &map_kv, &v_full[s], 0, row + a.kv_heads * ps);
-                tma_load_2d(vd + kHalfBytes, &map_kv, &v_full[s], 64, row + a.kv_heads * ps);
+#pragma unroll
+                for (int h = 0; h < kHalves; ++h) {
+                    tma_load_2d(kd + h * kHalfBytes, &map_kv, &k_full[s], 64 * h, row);
+                    tma_load_2d(vd + h * kHalfBytes, &map_kv, &v_full[s], 64 * h, row + a.kv_heads * ps);
+                }
                 // the next tile's page id (keys past the request's end are masked: any valid page will do)
                 if (j + 1 < n_tiles) page = table[min((k_begin + (j + 1) * kKeys) / ps + lane, a.table_width - 1)];
             }
@@ -420,8 +424,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 constexpr int kMaxKeySplits = 16;
 constexpr int kMergeRows = 1;
 
-__global__ void __launch_bounds__(kDim)
+template <int D>
+__global__ void __launch_bounds__(D)
 attn_tc_merge_kernel(const AttnArgs a) {
+    constexpr int kDim = D;
     pdl_trigger();
     pdl_wait();
     const int tile_id = blockIdx.x / (kRows / kMergeRows), row0 = (blockIdx.x % (kRows / kMergeRows)) * kMergeRows;
@@ -467,11 +473,11 @@ attn_tc_merge_kernel(const AttnArgs a) {
 
 // 1 if the tcgen05 prefill kernel takes this geometry.
 LLM_API int llm_attention_tcgen05_supported(int heads, int kv_heads, int head_dim, int page_size) {
-    return head_dim == 128 && kv_heads > 0 && heads % kv_heads == 0 && page_size >= 8 && page_size <= 128 &&
+    return (head_dim == 64 || head_dim == 128) && kv_heads > 0 && heads % kv_heads == 0 && page_size >= 8 && page_size <= 128 &&
            (128 % page_size) == 0;
 }
 
-// q: [tokens, q_stride] bf16 with head h at columns [h * 128, h * 128 + 128); cache layer [pages, 2, kv_heads, page, 128];
+// q: [tokens, q_stride] bf16 with head h at columns [h * head_dim, (h + 1) * head_dim); cache layer [pages, 2, kv_heads, page, head_dim];
 // tiles: [n_tiles] int4 {first token row, rows (<= 128), position of the first row, request}.
 LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int tokens, const void* cache, long long cache_pages,
                                           const int* block_table, int table_width, const int* tiles, int n_tiles,
@@ -488,7 +494,7 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
     if (int rc = llm_tensor_map_2d(q, (uint64_t)tokens, (uint64_t)q_stride, kRows, 64, &mq)) return rc;
     const uint64_t kv_rows = (uint64_t)cache_pages * 2 * kv_heads * page_size;
     if (kv_rows > 0x7fffffffull) LLM_FAIL(-1, "attention_prefill_tcgen05: the cache layer has too many rows for 32-bit TMA coordinates");
-    if (int rc = llm_tensor_map_2d(cache, kv_rows, kDim, (uint32_t)page_size, 64, &mkv)) return rc;
+    if (int rc = llm_tensor_map_2d(cache, kv_rows, (uint64_t)head_dim, (uint32_t)page_size, 64, &mkv)) return rc;
     AttnArgs a;
     a.block_table = block_table;
     a.table_width = table_width;
@@ -508,10 +514,14 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
     const int group = heads / kv_heads;
     a.per_cta = (group >= 2 && (long long)n_tiles * kv_heads * ((group + 1) / 2) * splits >= sms) ? 2 : 1;
     a.pairs = (group + a.per_cta - 1) / a.per_cta;
-    const size_t smem = 6 * kTileBytes + 1024;
+    const size_t smem = 6 * (size_t)(head_dim == 64 ? tile_bytes<64>() : tile_bytes<128>()) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             6 * tile_bytes<128>() + 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     6 * tile_bytes<64>() + 1024);
         if (e != cudaSuccess) LLM_FAIL(-2, "attention_prefill_tcgen05: %s", cudaGetErrorString(e));
         configured = true;
     }
@@ -520,10 +530,13 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
     a.splits = splits;
     a.part_o = part_o;
     a.part_ml = part_ml;
-    llm_launch(attn_prefill_tcgen05_kernel, dim3(n_tiles, kv_heads * a.pairs, splits), kThreads, smem, stream, mq, mkv, a);
+    const dim3 grid(n_tiles, kv_heads * a.pairs, splits), merge_grid(n_tiles * (kRows / kMergeRows), heads);
+    if (head_dim == 64) llm_launch(attn_prefill_tcgen05_kernel<64>, grid, kThreads, smem, stream, mq, mkv, a);
+    else llm_launch(attn_prefill_tcgen05_kernel<128>, grid, kThreads, smem, stream, mq, mkv, a);
     LLM_CHECK_LAUNCH("attention_prefill_tcgen05");
     if (splits > 1) {
-        llm_launch(attn_tc_merge_kernel, dim3(n_tiles * (kRows / kMergeRows), heads), kDim, 0, stream, a);
+        if (head_dim == 64) llm_launch(attn_tc_merge_kernel<64>, merge_grid, 64, 0, stream, a);
+        else llm_launch(attn_tc_merge_kernel<128>, merge_grid, 128, 0, stream, a);
         LLM_CHECK_LAUNCH("attention_prefill_tcgen05 merge");
     }
     return 0;

@@ -323,19 +323,20 @@ def test_attention_bf16_same_result_in_any_batch(K):
 
 @pytest.mark.parametrize("heads,kv_heads,page,window,splits", [(8, 2, 16, 0, 3), (3, 1, 16, 0, 2), (4, 4, 32, 0, 5),
                                                                (4, 2, 16, 700, 4), (2, 1, 8, 0, 16)])
-def test_attention_tcgen05_key_splits(K, heads, kv_heads, page, window, splits):
+@pytest.mark.parametrize("head_dim", [128, 64])
+def test_attention_tcgen05_key_splits(K, heads, kv_heads, page, window, splits, head_dim):
     """The keys of a query tile shared out over several CTAs whose partial results a merge kernel adds: short
     portions against long contexts, more splits than some tiles have key tiles, a window that leaves early splits
     without a visible key for late rows."""
     lens, qlens = [3000, 1500, 200, 2100], [200, 130, 200, 1]
-    q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, 128, page, lens, qlens, 140)
-    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, 128, window)
+    q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lens, qlens, 140)
+    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, head_dim, window)
     old = K.attention_splits
     try:
         for forced in (splits, None):
             K.attention_splits = forced
-            out = torch.zeros(q.shape[0], heads * 128, device="cuda", dtype=torch.bfloat16)
-            K.attention(q, cache, meta, out, heads, kv_heads, 128, window=window)
+            out = torch.zeros(q.shape[0], heads * head_dim, device="cuda", dtype=torch.bfloat16)
+            K.attention(q, cache, meta, out, heads, kv_heads, head_dim, window=window)
             close(out, want, torch.bfloat16)
     finally:
         K.attention_splits = old
@@ -498,18 +499,20 @@ def test_gemm_pair_tail_split(K, tokens, n, k, swiglu):
     assert K.gemm_pair_status() == 0
 
 
-# ---- the tcgen05 prefill attention (bfloat16, head size 128) -------------------------------
+# ---- the tcgen05 prefill attention (bfloat16, head sizes 64 and 128) ------------------------
+@pytest.mark.parametrize("head_dim", [128, 64])
 @pytest.mark.parametrize("heads,kv_heads,page,window", [(8, 2, 16, 0), (4, 1, 8, 0), (2, 2, 64, 0), (3, 1, 128, 0),
                                                         (4, 2, 16, 100), (4, 2, 32, 128), (16, 1, 16, 0)])
-def test_attention_tcgen05_portions(K, heads, kv_heads, page, window):
+def test_attention_tcgen05_portions(K, heads, kv_heads, page, window, head_dim):
     """Portions of several 128-query tiles, starting at positions that are no multiple of 128, beside
     short ones; page sizes from 8 to 128.  Decoded tokens in the same call go to the decode kernel."""
-    assert K.lib.llm_attention_tcgen05_supported(heads, kv_heads, 128, page)
+    D = head_dim
+    assert K.lib.llm_attention_tcgen05_supported(heads, kv_heads, D, page)
     lens, qlens = [700, 130, 391, 64, 900, 5], [300, 130, 129, 64, 1, 2]
-    q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, 128, page, lens, qlens, 120)
-    out = torch.zeros(q.shape[0], heads * 128, device="cuda", dtype=torch.bfloat16)
-    K.attention(q, cache, meta, out, heads, kv_heads, 128, window=window)
-    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, 128, window)
+    q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, D, page, lens, qlens, 120)
+    out = torch.zeros(q.shape[0], heads * D, device="cuda", dtype=torch.bfloat16)
+    K.attention(q, cache, meta, out, heads, kv_heads, D, window=window)
+    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, D, window)
     close(out, want, torch.bfloat16)
     assert K.attention_status() == 0
     # the mma.sync kernel gives the same to rounding
@@ -517,27 +520,28 @@ def test_attention_tcgen05_portions(K, heads, kv_heads, page, window):
     try:
         meta.attention_plan = None
         out2 = torch.zeros_like(out)
-        K.attention(q, cache, meta, out2, heads, kv_heads, 128, window=window)
+        K.attention(q, cache, meta, out2, heads, kv_heads, D, window=window)
     finally:
         K.attention_tcgen05 = old
     close(out2, want, torch.bfloat16)
 
 
-def test_attention_tcgen05_far_key_and_page_edges(K):
+@pytest.mark.parametrize("head_dim", [128, 64])
+def test_attention_tcgen05_far_key_and_page_edges(K, head_dim):
     """One key among 2000 stands out for every query of a 256-token portion; it sits on a page edge."""
-    heads, kv_heads, page, L, n = 2, 1, 16, 2000, 256
+    heads, kv_heads, page, L, n, D = 2, 1, 16, 2000, 256, head_dim
     for far in (0, 15, 16, 127, 128, 1743):
-        q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, 128, page, [L], [n], 130 + far)
+        q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, D, page, [L], [n], 130 + far)
         cache.mul_(0.05)
         pg, off = int(meta.block_table[0, far // page]), far % page
-        key = rnd((128,), torch.float32, 131)
+        key = rnd((D,), torch.float32, 131)
         key = key / key.norm()
         cache[pg, 0, 0, off] = (key * 40.0).to(torch.bfloat16)
         cache[pg, 1, 0, off] = 3.0
-        q[:, :heads * 128] = (key * 12.0).to(torch.bfloat16).repeat(heads)        # every query points at that key
-        out = torch.zeros(n, heads * 128, device="cuda", dtype=torch.bfloat16)
-        K.attention(q, cache, meta, out, heads, kv_heads, 128)
-        want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, 128)
+        q[:, :heads * D] = (key * 12.0).to(torch.bfloat16).repeat(heads)        # every query points at that key
+        out = torch.zeros(n, heads * D, device="cuda", dtype=torch.bfloat16)
+        K.attention(q, cache, meta, out, heads, kv_heads, D)
+        want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, D)
         close(out, want, torch.bfloat16)
         assert (out.float() - 3.0).abs().max() < 0.1
     assert K.attention_status() == 0
