@@ -19,6 +19,7 @@ import math
 import os
 import threading
 
+import numpy as np
 import torch
 
 from ..csrc import build as _build
@@ -134,6 +135,7 @@ class AttentionPlan:
     position of the first row, request)."""
 
     TILE = 64
+    SPLIT_RULE = os.environ.get("IITJ_DECODE_SPLIT", "auto")    # "equal": always the rule for equal contexts (measurements)
 
     def __init__(self, query_lens, seq_lens, device, items=None, tiles=None, total_tokens=None):
         self.decode_pos = []
@@ -168,11 +170,19 @@ class AttentionPlan:
     def split(self, kv_heads: int, window: int, sm_count: int, head_dim: int = 128, bound: int | None = None):
         """(keys per split, most splits of any item).
 
-        The decode kernel runs `items * kv_heads * splits` CTAs, `slots` of them at a time
-        (2 per SM at head size 128, 4 at 64).  Candidates are scored by waves * (keys per
-        split + a fixed per-CTA cost), which favours split counts that fill whole waves.
-        `bound` replaces the longest context by an upper bound (captured graphs use one so
-        that the choice stays the same while contexts grow)."""
+        The decode kernel runs one CTA per (item, key/value head, split of that item's keys); an item with
+        fewer keys than `keys per split` has one CTA, a long one several.  `resident` CTAs run at a time (2 per
+        SM at head size 128, 4 at 64).  Candidates (the longest context cut into 1 .. 64 parts) are scored in
+        units of keys, a CTA costing its keys plus 192:
+          * contexts of about equal length (the shortest at least three quarters of the longest): rounds of
+            `resident` CTAs times the cost of one, which favours cuts that fill whole rounds; the best wins;
+          * unequal contexts (continuous batching: one 16k-token context beside thirty short ones): the longer
+            of the longest CTA times the rounds that the CTAs of more than half its length need, and the cost
+            of all CTAs together shared out over `resident`; the coarsest cut within 5 % of the best wins.  So
+            a long context among short ones is cut into many CTAs instead of keeping one SM busy while the
+            others idle.
+        `bound` replaces the longest context by an upper bound (captured graphs use one so that the choice
+        stays the same while contexts grow); the other contexts are taken as grown by as much."""
         key = (kv_heads, window, head_dim, bound)
         if key not in self._splits:
             spans = []
@@ -180,19 +190,29 @@ class AttentionPlan:
                 lo = max(0, pos - window + 1) if window > 0 else 0
                 spans.append(pos - (lo // self.TILE) * self.TILE + 1)
             longest = max(spans) if bound is None else max(bound, max(spans))
-            slots = sm_count * (2 if head_dim > 64 else 4)
+            resident = sm_count * (2 if head_dim > 64 else 4)
+            grown = longest - max(spans)
+            equal = 4 * (min(spans) + grown) >= 3 * longest or self.SPLIT_RULE == "equal"
+            arr = None if equal else np.asarray(spans, dtype=np.int64) + grown
+            keys = 0 if equal else int(arr.sum()) * kv_heads
             pairs = self.n_items * kv_heads
-            best = None
+            scored, seen = [], set()
             for n in range(1, 65):
                 kps = -(-(-(-longest // n)) // self.TILE) * self.TILE
                 if n > 1 and kps < 256:
                     break
-                real = -(-longest // kps)
-                waves = -(-pairs * real // slots)
-                cost = waves * (kps + 192)
-                if best is None or cost < best[0]:
-                    best = (cost, kps, real)
-            kps = best[1]
+                if kps in seen:
+                    continue
+                seen.add(kps)
+                if equal:
+                    cost = -(-pairs * -(-longest // kps) // resident) * (kps + 192)
+                else:
+                    ctas = int((-(-arr // kps)).sum()) * kv_heads
+                    long_ctas = int(((arr + kps // 2) // kps).sum()) * kv_heads
+                    cost = max(max(1, -(-long_ctas // resident)) * (min(kps, longest) + 192), (keys + 192 * ctas) / resident)
+                scored.append((cost, kps))
+            least = min(c for c, _ in scored)
+            kps = next(k for c, k in scored if c <= (least if equal else 1.05 * least))
             self._splits[key] = (kps, max((s - 1) // kps + 1 for s in ([longest] if bound is not None else spans)))
         return self._splits[key]
 
