@@ -69,3 +69,4 @@ def write_model_dir(config, out_dir: str, seed: int, dtype=torch.bfloat16, std: 
     with open(os.path.join(out_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(typed.to_dict(), f, indent=1)
     return out_dir
+

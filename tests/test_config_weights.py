@@ -151,3 +151,21 @@ def test_missing_files_are_clear_errors(tmp_path):
     arch, cfg = load_config(str(tmp_path))
     with pytest.raises(FileNotFoundError):
         load_parameters(str(tmp_path), arch, cfg, arch.model_spec(cfg), torch.float32, device="cpu")
+
+
+def test_random_weights_command_line(tmp_path):
+    """`python -m iitj_llm_coopt_b200.weights` writes a folder that the loader's checks accept and that is the
+    same for the same seed."""
+    import subprocess, sys
+    from configs import TINY_B
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(TINY_B))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for name in ("a", "b"):
+        subprocess.run([sys.executable, "-m", "iitj_llm_coopt_b200.weights", "--config", str(cfg_path), "--out",
+                        str(tmp_path / name), "--seed", "5"], check=True, cwd=root, capture_output=True)
+    from safetensors.torch import load_file
+    a, b = load_file(str(tmp_path / "a" / "model.safetensors")), load_file(str(tmp_path / "b" / "model.safetensors"))
+    assert set(a) == set(b) and all(torch.equal(a[k], b[k]) for k in a)
+    assert "lm_head.weight" not in a and a["model.embed_tokens.weight"].shape == (TINY_B["vocab_size"], TINY_B["hidden_size"])
+    assert json.load(open(tmp_path / "a" / "config.json"))["num_key_value_heads"] == TINY_B["num_key_value_heads"]
