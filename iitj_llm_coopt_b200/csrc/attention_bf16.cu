@@ -22,6 +22,8 @@
 // query's result does not depend on the batch it is computed in.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace {
 
 typedef __nv_bfloat16 bf16;
@@ -586,11 +588,27 @@ int page_shift_of(int page_size) {
     return (1 << s) == page_size ? s : -1;
 }
 
+// Opts a kernel in to `bytes` of dynamic shared memory.  The largest size set so far is remembered per device and
+// kernel in a small fixed table (no heap), so that a launch costs no driver call once it is set.
+struct SmemRecord { int dev; const void* fn; size_t bytes; };
+SmemRecord g_smem_records[128];
+int g_smem_count = 0;
+std::mutex g_smem_mutex;
+
 template <typename K> int set_smem(K kernel, size_t bytes, const char* name) {
-    if (bytes + 8 * 1024 > 48 * 1024) {        // (a kernel's static shared memory counts toward the 48 KiB that need no opt-in)
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-        if (e != cudaSuccess) LLM_FAIL(-2, "%s: %s", name, cudaGetErrorString(e));
-    }
+    if (bytes + 8 * 1024 <= 48 * 1024) return 0;   // (a kernel's static shared memory counts toward the 48 KiB that need no opt-in)
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const void* fn = reinterpret_cast<const void*>(kernel);
+    std::lock_guard<std::mutex> lock(g_smem_mutex);
+    SmemRecord* rec = nullptr;
+    for (int i = 0; i < g_smem_count && !rec; ++i)
+        if (g_smem_records[i].dev == dev && g_smem_records[i].fn == fn) rec = &g_smem_records[i];
+    if (rec && bytes <= rec->bytes) return 0;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) LLM_FAIL(-2, "%s: %s", name, cudaGetErrorString(e));
+    if (!rec && g_smem_count < 128) { rec = &g_smem_records[g_smem_count++]; rec->dev = dev; rec->fn = fn; rec->bytes = 0; }
+    if (rec) rec->bytes = bytes;       // (a full table only means that the attribute is set again next time)
     return 0;
 }
 

@@ -21,6 +21,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
+from ..cache.manager import CacheError
 from ..kernels import AttentionPlan, Kernels
 
 LONG_PREFILL = Kernels.LONG_PREFILL
@@ -151,7 +152,9 @@ class ModelRunner:
             r, n = e.request, len(e.tokens)
             if n == 0:
                 raise ValueError(f"request {r!r} brings no tokens")
-            start = stored[r]
+            start = stored.get(r)
+            if start is None:
+                raise CacheError(f"request {r!r} is not admitted to the cache (admit it before its first step)")
             if start + n > room[r]:
                 cache.ensure(r, start + n)         # (the scheduler has reserved already: this is the replay's path)
             starts.append(start)
