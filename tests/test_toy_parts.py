@@ -1,6 +1,6 @@
-"""A toy architecture defined here, in the test: a mixer with state of its own, a feed-forward with
-routing, another position encoding, a layer named twice in the run order, and a call that reads
-another call's cache.  It is registered,
+"""Toy architectures defined here, in the test: a mixer with state of its own, a feed-forward with
+routing, another position encoding, a layer named twice in the run order, a call that reads
+another call's cache, and layers with a window beside layers without.  They are registered,
 built and stepped through the framework's registries alone; no file of the framework
 knows about it.  Stepping in portions must give what whole prompts give."""
 from dataclasses import dataclass
@@ -10,6 +10,7 @@ import torch
 
 from iitj_llm_coopt_b200 import EngineConfig, build_engine, parts
 from iitj_llm_coopt_b200.config.registry import ARCHITECTURES, register_architecture
+from iitj_llm_coopt_b200.engine import StepEntry
 from iitj_llm_coopt_b200.config.specs import (CacheNeed, FeedForwardSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec,
                                               NormSpec, PositionSpec)
 from iitj_llm_coopt_b200.models.base import Architecture
@@ -195,3 +196,93 @@ def test_unknown_part_kinds_are_clear_errors():
     with pytest.raises(KeyError) as e:
         model_parameter_specs(spec)
     assert "running_mean" in str(e.value) and "attention" in str(e.value)
+
+
+# ---- a toy with a window: layers that keep every key beside layers that keep the last 20 ---------------
+@dataclass
+class ToyWindowConfig:
+    head_dim: int = 16
+    window: int = 20
+    width: int = 64
+    vocab: int = 200
+
+    def to_dict(self):
+        return {"architectures": ["ToyWindowLM"], "head_dim": self.head_dim, "window": self.window, "width": self.width,
+                "vocab": self.vocab}
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["head_dim"], d["window"], d["width"], d["vocab"])
+
+    def model_spec(self):
+        norm = NormSpec("rmsnorm", self.width, 1e-5)
+        ff = FeedForwardSpec("swiglu", self.width, 96)
+        pos = PositionSpec("rope", head_dim=self.head_dim, rotary_dim=self.head_dim, theta=10000.0)
+        full = LayerSpec("prenorm", MixerSpec("attention", self.width, heads=4, kv_heads=2, head_dim=self.head_dim, position=pos),
+                         ff, norm, norm)
+        near = LayerSpec("prenorm", MixerSpec("attention", self.width, heads=4, kv_heads=2, head_dim=self.head_dim,
+                                              window=self.window, position=pos), ff, norm, norm)
+        order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2), LayerCall(1, 3))
+        return ModelSpec(width=self.width, vocab=self.vocab, layers=(full, near), order=order, final_norm=norm,
+                         tie_embeddings=True, max_position=4096)
+
+
+class ToyWindowArch(Architecture):
+    name = "ToyWindowLM"
+    config_class = ToyWindowConfig
+
+    def checkpoint_name(self, path, piece):
+        return path if piece is None else f"{path}.{piece}"
+
+
+def _window_engine(device, dtype, head_dim, window, pages=48):
+    kernels = None
+    if device == "cpu":
+        from torch_kernels import TorchKernels
+        kernels = TorchKernels()
+    ec = EngineConfig(dtype=dtype, page_size=8, num_pages=pages, max_num_seqs=3, device=device)
+    return build_engine(None, ec, config=ToyWindowConfig(head_dim, window), architecture=ToyWindowArch(), random_seed=5,
+                        kernels=kernels)
+
+
+@pytest.mark.parametrize("device,dtype,head_dim", [("cpu", "float32", 16),
+                                                   pytest.param("cuda:0", "float32", 16, marks=pytest.mark.gpu),
+                                                   pytest.param("cuda:0", "bfloat16", 16, marks=pytest.mark.gpu),
+                                                   pytest.param("cuda:0", "bfloat16", 64, marks=pytest.mark.gpu),
+                                                   pytest.param("cuda:0", "bfloat16", 128, marks=pytest.mark.gpu)])
+def test_layers_with_a_window_beside_layers_without(device, dtype, head_dim):
+    """Two cache groups with pages of their own: the windowed one gives pages back while a request lives, and every
+    way of cutting gives what whole prompts give; a window changes nothing before position `window` and something
+    after it."""
+    window = 20
+    eng = _window_engine(device, dtype, head_dim, window)
+    cache = eng.cache
+    assert len(cache.paged) == 2 and cache.windowed
+    g_full, g_near = cache.entry_group[0][0], cache.entry_group[1][0]
+    assert g_full != g_near and cache.entry_group[2][0] == g_full and cache.entry_group[3][0] == g_near
+    reqs = cases.requests_for(200, [50, 23, 150, 9], seed=6)
+    whole = run_steps(eng, cases.whole(reqs))
+    tol = 1e-4 if dtype == "float32" else 3e-2
+    for label, steps in (("last32", cases.last_one_by_one(reqs)), ("portions", cases.portions(reqs)),
+                         ("mixed", cases.mixed(reqs, live=3, seed=2)[0])):
+        rows = run_steps(eng, steps)
+        worst = max(rel_err(rows[k], whole[k]) for k in whole)
+        assert worst <= tol, (label, worst)
+        cache.check()
+        assert cache.groups[g_full].pool.num_free == 48 and cache.groups[g_near].pool.num_free == 48
+    # pages of the windowed group come back while the request lives: 150 tokens hold 19 pages where every key is
+    # kept, and never more than the window and one portion need where it is not
+    toks, most_near = reqs["r2"], 0
+    cache.admit("long")
+    for i in range(0, 150, 10):
+        eng.runner.step([StepEntry("long", toks[i:i + 10], [])])
+        most_near = max(most_near, 48 - cache.groups[g_near].pool.num_free)
+        cache.check()
+    assert 48 - cache.groups[g_full].pool.num_free == 19
+    assert most_near <= -(-(window + 10) // 8) + 1
+    cache.release("long")
+    # the window itself: the same weights without a window agree up to position 19 and not after
+    everything = _window_engine(device, dtype, head_dim, 0)
+    other = run_steps(everything, cases.whole({"r2": reqs["r2"]}))
+    assert max(rel_err(other[("r2", p)], whole[("r2", p)]) for p in range(window)) <= tol
+    assert rel_err(other[("r2", 140)], whole[("r2", 140)]) > 3 * tol
