@@ -40,6 +40,13 @@ LLAMA_8B = {
                      "original_max_position_embeddings": 8192},
     "tie_word_embeddings": False, "max_position_embeddings": 131072, "eos_token_id": 128001,
 }
+# The two smaller shapes of the same family (for `--shape`: profiles and sweeps at other sizes; the default line is the 8B shape)
+LLAMA_3B = dict(LLAMA_8B, hidden_size=3072, intermediate_size=8192, num_hidden_layers=28, num_attention_heads=24,
+                head_dim=128, tie_word_embeddings=True,
+                rope_scaling=dict(LLAMA_8B["rope_scaling"], factor=32.0))
+LLAMA_1B = dict(LLAMA_3B, hidden_size=2048, num_hidden_layers=16, num_attention_heads=32, head_dim=64)
+SHAPES = {"8b": ("llama-3.1-8b-shape-random", LLAMA_8B), "3b": ("llama-3.2-3b-shape-random", LLAMA_3B),
+          "1b": ("llama-3.2-1b-shape-random", LLAMA_1B)}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -131,6 +138,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (reported)")
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes: Llama 3.1 8B (the benchmark), 3.2 3B or 3.2 1B")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
@@ -159,7 +167,8 @@ def main() -> int:
     from iitj_llm_coopt_b200.engine.llm import LLM
 
     peaks, peak_source = load_peaks()
-    cfg = dict(LLAMA_8B)
+    model_name, shape_cfg = SHAPES[args.shape]
+    cfg = dict(shape_cfg)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -297,15 +306,15 @@ def main() -> int:
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B}
 
     line = {
-        "metric": "decode tok/s at batch 8 (Llama 3.1 8B shape, 8192-token contexts); prefill and batch 1/64 alongside",
+        "metric": f"decode tok/s at batch {B} ({model_name[:-13]} shape, {C}-token contexts); prefill and batch 1/64 alongside",
         "value": value, "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "llama-3.1-8b-shape-random", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
+        "config": {"model": model_name, "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "global_batch": B, "seq_len": C, "page_size": page, "parallelism": "single-gpu",
-                   "l2": "inputs larger than L2 (a step reads >15 GB of weights)", "weights": "random seed 2"},
+                   "l2": f"inputs larger than L2 (a step reads {weight_bytes / 1e9:.1f} GB of weights)", "weights": "random seed 2"},
         "clocks": clock_rec,
         "e2e": e2e,
         "gpu_launches": launches,

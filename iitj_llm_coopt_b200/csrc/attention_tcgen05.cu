@@ -27,6 +27,7 @@
 // and the CTA falls through to its teardown, where the tensor memory is freed.
 #include "tcgen05_common.cuh"
 
+#include <cstdlib>
 #include <type_traits>
 
 namespace {
@@ -513,6 +514,8 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int group = heads / kv_heads;
     a.per_cta = (group >= 2 && (long long)n_tiles * kv_heads * ((group + 1) / 2) * splits >= sms) ? 2 : 1;
+    static const int forced = [] { const char* e = getenv("IITJ_ATTN_HEADS_PER_CTA"); return e ? atoi(e) : 0; }();   // measurements
+    if (forced == 1 || (forced == 2 && group >= 2)) a.per_cta = forced;
     a.pairs = (group + a.per_cta - 1) / a.per_cta;
     const size_t smem = 6 * (size_t)(head_dim == 64 ? tile_bytes<64>() : tile_bytes<128>()) + 1024;
     static bool configured = false;
