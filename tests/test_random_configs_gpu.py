@@ -2,7 +2,7 @@
 and groups, widths, inner sizes and vocabularies that are no multiple of anything, with and without llama3
 rotary scaling, tied and untied heads, page sizes from 4 to 64.  Each is replayed whole, with the last 32 tokens
 one by one, in portions and mixed over a pool that is just large enough, in float32 and bfloat16, against the
-plain implementation.  The configurations are drawn from fixed seeds, so a failure names its seed."""
+plain implementation; every other checkpoint is stored in float32.  The configurations are drawn from fixed seeds, so a failure names its seed."""
 import random
 
 import pytest
@@ -52,7 +52,9 @@ def test_random_configuration(tmp_path, seed):
     page = rng.choice([16, 16, 16, 8, 32, 64, 4])
     lens = [rng.choice([1, 2, 3, 5, 17, 33, 63, 64, 65, 100, 127, 128, 129, 130, 200, 257, 300])
             for _ in range(rng.choice([3, 4, 5]))]
-    write_model_dir(cfg, str(tmp_path), seed)
+    # every other checkpoint is stored in float32, with values that bfloat16 cannot hold: the float32 engine must use
+    # them as they are, the bfloat16 engine rounds the matrices and keeps the norm gains
+    write_model_dir(cfg, str(tmp_path), seed, dtype=torch.float32 if seed % 2 else torch.bfloat16)
     reqs = cases.requests_for(cfg["vocab_size"], lens, seed + 10)
     c, w = plain.read_model_dir(str(tmp_path), torch.float32)
     ref = {rid: plain.forward(c, w, toks) for rid, toks in reqs.items()}
