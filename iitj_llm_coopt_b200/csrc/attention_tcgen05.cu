@@ -21,7 +21,7 @@
 //                  back before the next P V.  The sum l follows the same reference, so O / l is exact.
 //
 // Replaces flash_attn_varlen_func (engine/model.py:204-207) for portions; same masking and float32
-// statistics as the mma.sync kernel of attention_bf16.cu, which remains for other head and page sizes.
+// statistics as the mma.sync kernel of attention_bf16.cu, which remains for page sizes that do not divide 128.
 //
 // Every mbarrier wait is bounded; a wait that runs out records a code (llm_attention_tcgen05_status)
 // and the CTA falls through to its teardown, where the tensor memory is freed.
