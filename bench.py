@@ -301,7 +301,7 @@ def main() -> int:
         per_step = sorted(stamps)
         t_start, t_last = per_step[B * (WE + 1) - 1], per_step[-1]
         decoded = len(per_step) - B * (WE + 1)
-        h2d = (4 * B + (B + 1) + 4 * B + B * max(16, 1 << ((-(-(C + K) // page)) - 1).bit_length())) * 4
+        h2d = runner.copied_bytes        # the last decode step's index arrays (ids, positions, slots, block tables): one copy
         e2e = {"value": decoded / (t_last - t_start), "unit": "tok/s", "steps": decoded // B, "warmup": WE,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B}
 

@@ -57,6 +57,7 @@ class ModelRunner:
         self._copied = None          # event: the last host-to-device copy of the staging buffer is done
         self._capture_stream = None  # side stream that graph captures are recorded on
         self.steps = 0
+        self.copied_bytes = 0
 
     def forget(self, request) -> None:
         """Told when a request was released.  The runner keeps nothing per request (the cache manager holds the
@@ -278,6 +279,7 @@ class ModelRunner:
             tab[:, cols:] = 0
             put(f"slots{g}", tab[token_request, page_of].astype(np.int64) * ps + offset_in)
         self._meta[:off].copy_(self._pinned[:off], non_blocking=True)
+        self.copied_bytes = 4 * off            # what this step sent to the device (benchmarks report it)
         if self._meta.is_cuda:
             if self._copied is None:
                 self._copied = torch.cuda.Event()
