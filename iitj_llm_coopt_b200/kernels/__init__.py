@@ -174,10 +174,10 @@ class AttentionPlan:
         fewer keys than `keys per split` has one CTA, a long one several.  `resident` CTAs run at a time (2 per
         SM at head size 128, 4 at 64).  Candidates (the longest context cut into 1 .. 64 parts) are scored in
         units of keys, a CTA costing its keys plus 192:
-          * contexts of about equal length (the shortest at least three quarters of the longest): rounds of
-            `resident` CTAs times the cost of one, which favours cuts that fill whole rounds; the best wins;
+          * contexts of about equal length (the shortest at least three quarters of the longest): waves of
+            `resident` CTAs times the cost of one, which favours cuts that fill whole waves; the best wins;
           * unequal contexts (continuous batching: one 16k-token context beside thirty short ones): the longer
-            of the longest CTA times the rounds that the CTAs of more than half its length need, and the cost
+            of the longest CTA times the waves that the CTAs of more than half its length need, and the cost
             of all CTAs together shared out over `resident`; the coarsest cut within 5 % of the best wins.  So
             a long context among short ones is cut into many CTAs instead of keeping one SM busy while the
             others idle.

@@ -41,4 +41,4 @@ def test_a_long_context_among_short_ones_is_cut_finely():
     # contexts of equal length fill the GPU once and are cut no finer
     kps, most = plan_for([8192] * 8).split(8, 0, 148, 128, 8704)
     assert (kps, most) == (2176, 4)
-    assert plan_for([8192] * 32).split(8, 0, 148, 128, 8704) == (8704, 1)     # 256 CTAs: one round as it is
+    assert plan_for([8192] * 32).split(8, 0, 148, 128, 8704) == (8704, 1)     # 256 CTAs: one wave as it is
