@@ -13,8 +13,8 @@ counted over the timed decode steps).  `prefill` is one 2,048-token prompt in on
 relates the decode step's mandatory HBM reads to its time; `points` holds decode at batch
 1 and 64.  Weights are random (seeded, drawn on the device), token ids are random.
 
-The reference arm (`--impl reference`) is unavailable: the reference is a folder of
-scripts without setup.py or pyproject.toml, so the offline install cannot build it.
+`--impl reference` times the unmodified reference engine (a copy of its tree under
+`baseline/_ref`) on the same metric and configuration: see baseline/reference_arm.py.
 """
 from __future__ import annotations
 
@@ -45,8 +45,11 @@ LLAMA_3B = dict(LLAMA_8B, hidden_size=3072, intermediate_size=8192, num_hidden_l
                 head_dim=128, tie_word_embeddings=True,
                 rope_scaling=dict(LLAMA_8B["rope_scaling"], factor=32.0))
 LLAMA_1B = dict(LLAMA_3B, hidden_size=2048, num_hidden_layers=16, num_attention_heads=32, head_dim=64)
+# a toy shape for trying the two arms out in seconds (never the benchmark)
+LLAMA_TOY = dict(LLAMA_8B, hidden_size=512, intermediate_size=1408, num_hidden_layers=2, num_attention_heads=8,
+                 num_key_value_heads=2, head_dim=64, vocab_size=4096)
 SHAPES = {"8b": ("llama-3.1-8b-shape-random", LLAMA_8B), "3b": ("llama-3.2-3b-shape-random", LLAMA_3B),
-          "1b": ("llama-3.2-1b-shape-random", LLAMA_1B)}
+          "1b": ("llama-3.2-1b-shape-random", LLAMA_1B), "toy": ("llama-toy-shape-random", LLAMA_TOY)}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -66,18 +69,19 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi in the background: SM clock and throttle reasons during the timed region."""
+    """nvidia-smi in the background for the whole run: SM clock and throttle reasons.  `busy()` brackets the
+    timed phases; the median clock is taken over the samples that fell inside them, the throttle reasons over all."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
-        self.proc, self.lines = None, []
+        self.proc, self.lines, self.windows = None, [], []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -85,7 +89,19 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def busy(self):
+        sampler = self
+
+        class _Window:
+            def __enter__(self):
+                self.t0 = time.perf_counter()
+
+            def __exit__(self, *exc):
+                sampler.windows.append((self.t0, time.perf_counter()))
+                return False
+        return _Window()
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -95,22 +111,26 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm_all, sm_busy, mx, reasons = [], [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
+        for stamp, line in self.lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
             try:
-                sm.append(float(parts[0]))
+                sm_all.append(float(parts[0]))
                 mx.append(float(parts[1]))
             except ValueError:
                 continue
+            # a sample describes the 100 ms before it arrived
+            if any(t0 <= stamp <= t1 + 0.1 for t0, t1 in self.windows):
+                sm_busy.append(sm_all[-1])
             for name, flag in zip(names, parts[3:7]):
                 if flag == "Active":
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        under = sm_busy or sm_all
+        return {"sm_mhz": statistics.median(under) if under else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm_all), "samples_under_load": len(sm_busy), "reasons": sorted(reasons)}
 
 
 def matmul_weight_bytes(cfg, itemsize=2):
@@ -148,11 +168,6 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step by itself (for profiling)")
     args = ap.parse_args()
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference has no setup.py or pyproject.toml: the offline 'pip install --no-index' of its tree "
-                          "fails with 'not installable'; its engine also needs vLLM's CUDA ops and a downloaded checkpoint"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (only --gpus 1)")
         return 2
@@ -161,28 +176,47 @@ def main() -> int:
     if args.only:
         args.no_points = args.no_e2e = True
 
-    import torch
-
-    from iitj_llm_coopt_b200 import EngineConfig, LlamaConfig, SamplingParams, StepEntry, build_engine
-    from iitj_llm_coopt_b200.engine.llm import LLM
-
     peaks, peak_source = load_peaks()
     model_name, shape_cfg = SHAPES[args.shape]
     cfg = dict(shape_cfg)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
+    B, C, K, W = args.batch, args.context, args.steps, args.warmup
+    weight_bytes = matmul_weight_bytes(cfg)
+    p_flops = prefill_flops(cfg, args.prefill_tokens)
+
+    if args.impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import reference_arm
+        try:
+            line = reference_arm.run(cfg, model_name, full_layers, B, C, K, W, args.prefill_tokens, not args.no_points,
+                                     not args.no_e2e, not args.no_prefill, peaks, peak_source, ClockSampler(), weight_bytes,
+                                     p_flops)
+        except Exception as e:          # the reference's own code failed on this box: say so, as one line
+            line = {"impl": "reference", "unavailable": f"the reference engine raised {type(e).__name__}: {str(e)[:300]}"}
+        print(json.dumps(line))
+        return 0
+
+    import torch
+
+    from iitj_llm_coopt_b200 import LLM, LlamaConfig, SamplingParams, StepEntry
+
     typed = LlamaConfig.from_dict(cfg)
-    # at least six warm-up steps: a step shape is captured into a CUDA graph at its fourth sighting
-    B, C, K, W = args.batch, args.context, args.steps, max(args.warmup, 6)
     page = 16
     biggest = max(B, 1 if args.no_points else 64)
-    pool_tokens = biggest * (C + max(K, 96) + W + 2 * page) + args.prefill_tokens + 4 * page
-    ec = EngineConfig(dtype="bfloat16", page_size=page, num_pages=-(-pool_tokens // page), max_num_seqs=max(biggest, 8),
-                      max_num_batched_tokens=max(args.prefill_tokens, biggest), max_model_len=C + max(K, 96) + W + 64, seed=0,
-                      cuda_graphs=not args.no_graphs)
+    # a step shape is captured into a CUDA graph at its fourth sighting: those sightings come before the W warm-up steps
+    PRIME = 0 if args.no_graphs else 5
+    pool_tokens = biggest * (C + max(K, 96) + W + PRIME + 2 * page) + args.prefill_tokens + 4 * page
     t_build = time.time()
-    engine = build_engine(None, ec, config=typed, random_seed=2)
+    # the engine is built by the public entry point; the device-timed phases drive its step function directly
+    llm = LLM(config=typed, random_seed=2, dtype="bfloat16", page_size=page, num_pages=-(-pool_tokens // page),
+              max_num_seqs=max(biggest, 8),
+              # the end-to-end phase prefills its B prompts in one step, so that all B requests decode together from
+              # the first decode step to the last (with a smaller budget they would start, and end, one after the other)
+              max_num_batched_tokens=max(args.prefill_tokens, biggest, 0 if args.no_e2e else B * C),
+              max_model_len=C + max(K, 96) + W + PRIME + 64, seed=0, cuda_graphs=not args.no_graphs)
+    engine = llm.engine
     runner, cache, sampler, kernels = engine.runner, engine.cache, engine.sampler, engine.sampler.k
     for g in cache.groups:                      # contexts "already in the cache": random keys and values
         if g.storage is not None:
@@ -205,7 +239,7 @@ def main() -> int:
         prev = None
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches = 0
-        for it in range(warmup + steps):
+        for it in range(-PRIME, warmup + steps):
             if it == warmup:
                 torch.cuda.synchronize()
                 launches = kernels.launches
@@ -224,7 +258,6 @@ def main() -> int:
         launches = kernels.launches - launches
         for r in ids:
             cache.release(r)
-            runner.forget(r)
         return times, launches
 
     def prefill_run(T, reps, warmup):
@@ -239,7 +272,6 @@ def main() -> int:
             end.record()
             torch.cuda.synchronize()
             cache.release("p")
-            runner.forget("p")
             if it >= warmup:
                 times.append(start.elapsed_time(end))
         return times
@@ -249,53 +281,48 @@ def main() -> int:
         print(json.dumps({"only": "prefill", "tokens": args.prefill_tokens, "ms": t[len(t) // 2], "min_ms": t[0], "reps": len(t)}))
         return 0
     if args.only == "decode":
-        t, n = decode_run(B, max(1, K), 6)
+        t, n = decode_run(B, max(1, K), W)
         print(json.dumps({"only": "decode", "batch": B, "ms": sum(t) / len(t), "launches_per_step": n / len(t)}))
         return 0
     clocks = ClockSampler()
-    clocks.start()
-    times, launches = decode_run(B, K, W)
-    clock_rec = clocks.stop()
+    clocks.start()              # sampled over every timed phase of the run: decode, prefill, points, end to end
+    with clocks.busy():
+        times, launches = decode_run(B, K, W)
     ms = sum(times) / len(times)
     value = B / (ms / 1e3)
 
-    weight_bytes = matmul_weight_bytes(cfg)
-    kv_bytes = B * (C + W + K / 2) * typed.kv_bytes_per_token(2)
+    kv_bytes = B * (C + PRIME + W + K / 2) * typed.kv_bytes_per_token(2)
     achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
 
-    p_times = prefill_run(args.prefill_tokens, 5, 3) if not args.no_prefill else [float("nan")]
+    with clocks.busy():
+        p_times = prefill_run(args.prefill_tokens, 5, 3) if not args.no_prefill else [float("nan")]
     p_ms = statistics.median(p_times)
-    p_flops = prefill_flops(cfg, args.prefill_tokens)
     prefill = {"value": args.prefill_tokens / (p_ms / 1e3), "tokens": args.prefill_tokens, "ms": p_ms,
                "frac": p_flops / (p_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), "peak": f"of {peak_source}"}
 
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            t, _ = decode_run(b, max(8, K // 2), 6)
+            with clocks.busy():
+                t, _ = decode_run(b, max(8, K // 2), W)
             points[f"decode_b{b}"] = b / (sum(t) / len(t) / 1e3)
 
     e2e = None
     if not args.no_e2e:
-        # through the public entry point: host token ids in, host token ids out
-        llm = LLM.__new__(LLM)
-        llm.engine = engine
+        # through the public entry point: host token ids in (prompts), host token ids out (every step's tokens reach
+        # the callback).  The prompts are prefilled in one step; then come untimed decode steps (the eager sightings
+        # of the step's shape, its capture into a graph, and the clocks' recovery from the prefill at full power,
+        # which the first dozen decode steps still show), then the timed ones.
         prompts = [torch.randint(0, typed.vocab_size, (C,), generator=gen).tolist() for _ in range(B)]
         stamps = []
 
         def on_out(seq, new, fin):
             stamps.append(time.perf_counter())
 
-        budget = engine.policy.max_batched_tokens
-        engine.policy.max_batched_tokens = B * C          # all prompts in one prefill step, then decode steps only
-        # untimed decode steps, then timed ones.  The untimed ones take in the three eager sightings of the step's
-        # shape, its capture into a graph, and the clocks' recovery from the prompts' prefill (65k tokens at full
-        # power), which the first dozen decode steps still show.
         WE, KE = max(W, 24), max(K, 64)
-        seqs = [engine.new_sequence(p, WE + KE + 1, 0.0, True, None, on_out) for p in prompts]
-        engine.run_until_done()
-        torch.cuda.synchronize()
-        engine.policy.max_batched_tokens = budget
+        with clocks.busy():
+            llm.generate(prompts, SamplingParams(max_tokens=WE + KE + 1, ignore_eos=True), on_output=on_out)
+            torch.cuda.synchronize()
         # every decode step hands one token of each request to the callback: the timed region runs from the
         # last callback of warm-up step WE to the last callback of all (KE steps of B tokens)
         per_step = sorted(stamps)
@@ -305,6 +332,8 @@ def main() -> int:
         e2e = {"value": decoded / (t_last - t_start), "unit": "tok/s", "steps": decoded // B, "warmup": WE,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B}
 
+    clock_rec = clocks.stop()
+    kernels.check_health()          # raises if any kernel gave up on a bounded wait during the run
     line = {
         "metric": f"decode tok/s at batch {B} ({model_name[:-13]} shape, {C}-token contexts); prefill and batch 1/64 alongside",
         "value": value, "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms,
@@ -322,6 +351,8 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"], "peak_source": f"of {peak_source}"},
         "points": points,
+        "graph_priming_steps": PRIME,
+        "health": "ok",
         "build_seconds": build_s,
     }
     print(json.dumps(line))

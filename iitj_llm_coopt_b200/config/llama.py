@@ -14,12 +14,9 @@ import json
 import os
 from dataclasses import asdict, dataclass, field
 
+from .errors import ConfigError
 from .specs import (CacheNeed, FeedForwardSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec,
                     NormSpec, PositionSpec)
-
-
-class ConfigError(ValueError):
-    pass
 
 
 _REQUIRED = ("hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",

@@ -9,7 +9,7 @@ from __future__ import annotations
 import json
 import os
 
-from .llama import ConfigError
+from .errors import ConfigError
 
 ARCHITECTURES: dict = {}
 

@@ -315,6 +315,13 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
 // ---------------------------------------------------------------------------------------
 // part_o [items, heads, max_splits, D] float32 (unnormalised, relative to the split's max),
 // part_ml [items, heads, max_splits, 2] float32 (max in the log2 domain, sum).
+//
+// Contract of the callers: keys_per_split * max_splits covers every item's keys (from the 64-aligned start of its
+// window to its position).  The kernels cannot trust a foreign caller with that, so an item that would need more
+// splits is cut down to max_splits (its last keys are then left out: the result is wrong, but nothing is read or
+// written outside the partials of its own (item, head)), and a code is left in g_decode_status.
+__device__ int g_decode_status = 0;            // 0 ok; else (6 << 16) | item of the first item that did not fit
+
 // What the FUSED form reads instead of finished queries.
 struct QkvParts {
     const float* parts;        // [splits][tokens][(heads + 2 kv_heads) * D] float32 partial sums of the qkv product
@@ -344,7 +351,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     const int pos = positions[tok];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int k_begin = lo & ~(kTile - 1);
-    const int n_splits = (pos - k_begin) / keys_per_split + 1;
+    int n_splits = (pos - k_begin) / keys_per_split + 1;
+    if (n_splits > max_splits) {                                  // the caller's contract is broken: see g_decode_status
+        if (split == 0 && hk == 0 && threadIdx.x == 0) atomicCAS(&g_decode_status, 0, (6 << 16) | (item & 0xffff));
+        n_splits = max_splits;
+    }
     if (split >= n_splits) return;
     const int c0 = k_begin + split * keys_per_split;
     const int c1 = min(c0 + keys_per_split, pos + 1);             // keys [c0, c1)
@@ -554,7 +565,7 @@ attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
     const int tok = items[item];
     const int pos = positions[tok];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int n_splits = (pos - (lo & ~(kTile - 1))) / keys_per_split + 1;
+    const int n_splits = min((pos - (lo & ~(kTile - 1))) / keys_per_split + 1, max_splits);   // (cut down as in the decode kernel)
     if (n_splits == 1) return;                                    // the decode kernel wrote the result itself
     float M = -INFINITY, L = 0.f, O = 0.f;
     if (max_splits <= kMergeSplits) {
@@ -721,6 +732,20 @@ int launch_decode(const void* q, int q_stride, const void* cache, const int* blo
                           : launch(attn_decode_kernel<128, false>, attn_merge_kernel<128>, 128);
 }
 }  // namespace
+
+const int* llm_attention_decode_status_word() {
+    void* p = nullptr;
+    return cudaGetSymbolAddress(&p, g_decode_status) == cudaSuccess ? static_cast<const int*>(p) : nullptr;
+}
+
+// Reads and clears the status word of the decode attention: 0, or (6 << 16 | item) of the first item whose keys
+// keys_per_split * max_splits did not cover (its result is wrong: the caller broke the contract stated above).
+LLM_API int llm_attention_decode_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int));
+    return v;
+}
 
 // ---------------------------------------------------------------------------------------
 // The same decode attention with its scratch inside the library (see llm_no_alloc.h).

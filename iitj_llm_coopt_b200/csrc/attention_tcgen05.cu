@@ -545,6 +545,11 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
     return 0;
 }
 
+const int* llm_attention_tcgen05_status_word() {
+    void* p = nullptr;
+    return cudaGetSymbolAddress(&p, g_attn_status) == cudaSuccess ? static_cast<const int*>(p) : nullptr;
+}
+
 LLM_API int llm_attention_tcgen05_status() {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int)) != cudaSuccess) return -1;

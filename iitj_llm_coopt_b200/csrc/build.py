@@ -50,7 +50,8 @@ def sources() -> list:
 
 def _fingerprint() -> str:
     h = hashlib.sha256()
-    for path in sources() + sorted(glob.glob(os.path.join(HERE, "*.cuh"))):
+    headers = sorted(glob.glob(os.path.join(HERE, "*.cuh")) + glob.glob(os.path.join(HERE, "*.h")))
+    for path in sources() + headers:
         h.update(os.path.basename(path).encode())
         with open(path, "rb") as f:
             h.update(f.read())

@@ -30,6 +30,17 @@ char* llm_error_buffer();  // defined in runtime.cu; one buffer per process
         if (e_ != cudaSuccess) LLM_FAIL(-2, "%s: %s", name, cudaGetErrorString(e_)); \
     } while (0)
 
+// ---- health words (host) -----------------------------------------------------------------
+// Kernels with bounded waits, and kernels that check a caller's contract on the device, leave a code in a status
+// word of their file when something went wrong (0 = fine).  These return the words' device addresses on the current
+// device (null if the lookup fails); llm_sample copies the words out beside the sampled ids, so a serving loop
+// sees them at the place where it reads its tokens anyway, without a synchronisation of its own.
+constexpr int kHealthWords = 4;
+const int* llm_gemm_bf16_status_word();          // gemm_bf16.cu
+const int* llm_gemm_bf16_pair_status_word();     // gemm_bf16_pair.cu
+const int* llm_attention_tcgen05_status_word();  // attention_tcgen05.cu
+const int* llm_attention_decode_status_word();   // attention_bf16.cu
+
 // ---- element conversions (device) ------------------------------------------------------
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

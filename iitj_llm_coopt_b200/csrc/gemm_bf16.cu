@@ -401,6 +401,11 @@ LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, 
     return 0;
 }
 
+const int* llm_gemm_bf16_status_word() {
+    void* p = nullptr;
+    return cudaGetSymbolAddress(&p, g_status) == cudaSuccess ? static_cast<const int*>(p) : nullptr;
+}
+
 // Reads and clears the status word: 0, or (code << 16 | block) of the first CTA whose wait ran out
 // (code 1: producer waiting for a free stage, 2: MMA issuer waiting for data, 3: epilogue waiting for the accumulator).
 LLM_API int llm_gemm_bf16_status() {

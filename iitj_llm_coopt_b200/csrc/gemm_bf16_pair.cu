@@ -561,6 +561,11 @@ LLM_API int llm_gemm_bf16_pair(const void* x, const void* w, void* out, int out_
     return swiglu ? launch_pair<true>(mx, mw, mo, a, clusters, stream) : launch_pair<false>(mx, mw, mo, a, clusters, stream);
 }
 
+const int* llm_gemm_bf16_pair_status_word() {
+    void* p = nullptr;
+    return cudaGetSymbolAddress(&p, g_pair_status) == cudaSuccess ? static_cast<const int*>(p) : nullptr;
+}
+
 // Reads and clears the status word: 0, or (code << 16 | block) of the first CTA whose wait ran out (code 1: producer
 // waiting for a free stage, 2: MMA issuer waiting for data, 3: epilogue waiting for an accumulator, 4: MMA issuer
 // waiting for a drained accumulator, 5: a tile's owner waiting for the other clusters' partial sums).

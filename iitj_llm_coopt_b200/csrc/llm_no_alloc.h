@@ -25,6 +25,13 @@
 //     writes every partial it later reads -- but two calls whose kernels may run at the
 //     same time on one GPU (different streams, different threads) race on it.  Keep such
 //     calls on one stream, or order them with events.
+//   * keys_per_split (a multiple of 64) times max_splits must cover the longest item: its
+//     position + 1 keys, or with a window the keys from the 64-aligned start of the window.
+//     The kernels cannot see what the caller meant, so an item that would need more splits
+//     is cut down to max_splits: its last keys are left out, its result is wrong, nothing
+//     outside its own partials is touched, and llm_attention_decode_status() returns a
+//     non-zero code (6 << 16 | item) until it is read.  The same holds for
+//     llm_attention_decode_bf16.
 //   * It calls neither cudaMalloc nor cudaFree nor any allocating library routine.
 #pragma once
 
@@ -43,6 +50,10 @@ int llm_attention_decode_bf16_static(const void* q, int q_stride, const void* ca
                                      const int* positions, void* out, int out_stride, int heads, int kv_heads,
                                      int head_dim, int page_size, int window, float scale, int keys_per_split,
                                      int max_splits, cudaStream_t stream);
+
+// Reads and clears the status word of the decode attention kernels (0 = every call since the last read kept the
+// contract above).  It copies one int from the device and so waits for the work in flight.
+int llm_attention_decode_status(void);
 
 #ifdef __cplusplus
 }

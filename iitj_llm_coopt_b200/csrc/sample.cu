@@ -10,7 +10,17 @@
 // request's tokens do not depend on what else is in the batch.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace {
+
+// The library's health words (see common.cuh), copied out beside the sampled ids by the last kernel of a call.
+struct HealthWords { const int* word[kHealthWords]; };
+
+__device__ __forceinline__ void copy_health(const HealthWords& hw, int* health_out) {
+    if (health_out && blockIdx.x == 0 && threadIdx.x < kHealthWords)
+        health_out[threadIdx.x] = hw.word[threadIdx.x] ? *hw.word[threadIdx.x] : 0;
+}
 
 __device__ __forceinline__ uint64_t mix64(uint64_t z) {  // splitmix64 finaliser
     z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
@@ -26,9 +36,11 @@ __device__ __forceinline__ float gumbel(uint64_t key, uint32_t i) {
 
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ temperature,
-              const unsigned long long* __restrict__ keys, int* __restrict__ out, int vocab) {
+              const unsigned long long* __restrict__ keys, int* __restrict__ out, int vocab, const HealthWords hw,
+              int* __restrict__ health_out) {
     pdl_trigger();
     pdl_wait();
+    copy_health(hw, health_out);
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const int r = blockIdx.x;
@@ -107,9 +119,11 @@ sample_chunk_kernel(const float* __restrict__ logits, int ld, const float* __res
 
 // Stage 2: the best over a row's chunks (one warp per row).
 __global__ void __launch_bounds__(32)
-sample_pick_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int* __restrict__ out, int chunks) {
+sample_pick_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int* __restrict__ out, int chunks,
+                   const HealthWords hw, int* __restrict__ health_out) {
     pdl_trigger();
     pdl_wait();
+    copy_health(hw, health_out);
     const int r = blockIdx.x;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -125,6 +139,31 @@ sample_pick_kernel(const float* __restrict__ part_v, const int* __restrict__ par
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
     if (threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+}
+
+// Device addresses of the health words on the current device, looked up once per device.
+constexpr int kMaxDevices = 64;
+HealthWords g_health[kMaxDevices];
+bool g_health_known[kMaxDevices] = {};
+std::mutex g_health_mutex;
+
+int health_words(HealthWords* out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) LLM_FAIL(-2, "sample: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) LLM_FAIL(-1, "sample: device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_health_mutex);
+    if (!g_health_known[dev]) {
+        g_health[dev].word[0] = llm_gemm_bf16_status_word();
+        g_health[dev].word[1] = llm_gemm_bf16_pair_status_word();
+        g_health[dev].word[2] = llm_attention_tcgen05_status_word();
+        g_health[dev].word[3] = llm_attention_decode_status_word();
+        for (int i = 0; i < kHealthWords; ++i)
+            if (!g_health[dev].word[i]) LLM_FAIL(-2, "sample: the address of health word %d could not be looked up", i);
+        g_health_known[dev] = true;
+    }
+    *out = g_health[dev];
+    return 0;
 }
 
 }  // namespace
@@ -152,9 +191,15 @@ LLM_API int llm_sample_scratch_floats(int rows, int vocab) {
 }
 
 // scratch: llm_sample_scratch_floats(rows, vocab) floats, or null to scan each row with a single block.
+// health_out: null, or kHealthWords (4) ints that receive the library's status words as they stand when this call's
+// last kernel runs (tcgen05 product, CTA-pair product, tcgen05 attention, decode attention; 0 = fine).  The words
+// are not cleared: the llm_*_status functions do that.
 LLM_API int llm_sample(const float* logits, int ld, const float* temperature, const unsigned long long* keys,
-                       int* out, int rows, int vocab, float* scratch, cudaStream_t stream) {
+                       int* out, int rows, int vocab, float* scratch, int* health_out, cudaStream_t stream) {
     if (rows == 0) return 0;
+    HealthWords hw = {};
+    if (health_out)
+        if (int rc = health_words(&hw)) return rc;
     const int chunks = (vocab + kChunk - 1) / kChunk;
     if (scratch && chunks > 1) {
         if (rows > 65535) LLM_FAIL(-1, "sample: too many rows");
@@ -162,11 +207,11 @@ LLM_API int llm_sample(const float* logits, int ld, const float* temperature, co
         int* part_i = reinterpret_cast<int*>(scratch + (size_t)rows * chunks);
         llm_launch(sample_chunk_kernel, dim3(chunks, rows), 256, 0, stream, logits, ld, temperature, keys, part_v, part_i, vocab, chunks);
         LLM_CHECK_LAUNCH("sample");
-        llm_launch(sample_pick_kernel, rows, 32, 0, stream, (const float*)part_v, (const int*)part_i, out, chunks);
+        llm_launch(sample_pick_kernel, rows, 32, 0, stream, (const float*)part_v, (const int*)part_i, out, chunks, hw, health_out);
         LLM_CHECK_LAUNCH("sample_pick");
         return 0;
     }
-    llm_launch(sample_kernel, rows, 1024, 0, stream, logits, ld, temperature, keys, out, vocab);
+    llm_launch(sample_kernel, rows, 1024, 0, stream, logits, ld, temperature, keys, out, vocab, hw, health_out);
     LLM_CHECK_LAUNCH("sample");
     return 0;
 }

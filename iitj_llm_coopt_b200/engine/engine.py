@@ -61,15 +61,9 @@ class Engine:
         self._next_id += 1
         return self.add_request(seq)
 
-    def runner_forget(self, seq_id) -> None:
-        forget = getattr(self.runner, "forget", None)
-        if forget:
-            forget(seq_id)
-
     def release(self, seq) -> None:
         if self.cache.has(seq.seq_id):
             self.cache.release(seq.seq_id)
-        self.runner_forget(seq.seq_id)
 
     def _finish(self, seq, reason) -> None:
         seq.finished, seq.finish_reason = True, reason

@@ -120,9 +120,11 @@ class LLM:
                           device=device, cuda_graphs=cuda_graphs, lookahead=lookahead)
         self.engine = build_engine(model, ec, config=config, random_seed=random_seed, kernels=kernels)
 
-    def generate(self, prompt_token_ids, sampling_params=None) -> list:
+    def generate(self, prompt_token_ids, sampling_params=None, on_output=None) -> list:
         """prompt_token_ids: a list of prompts (each a list of token ids).  sampling_params:
-        one SamplingParams for all, or one per prompt.  Returns RequestOutputs in order."""
+        one SamplingParams for all, or one per prompt.  `on_output(sequence, new_token_ids, finished)` is
+        called as tokens arrive, as the reference's Sequence.on_output (engine/engine.py:40, 483-484).
+        Returns RequestOutputs in order."""
         if prompt_token_ids and isinstance(prompt_token_ids[0], int):
             prompt_token_ids = [prompt_token_ids]
         n = len(prompt_token_ids)
@@ -133,7 +135,7 @@ class LLM:
         if len(sampling_params) != n:
             raise ValueError("one SamplingParams per prompt, or one for all")
         t0 = time.perf_counter()
-        seqs = [self.engine.new_sequence(p, sp.max_tokens, sp.temperature, sp.ignore_eos, sp.seed)
+        seqs = [self.engine.new_sequence(p, sp.max_tokens, sp.temperature, sp.ignore_eos, sp.seed, on_output)
                 for p, sp in zip(prompt_token_ids, sampling_params)]
         self.engine.run_until_done()
         return [RequestOutput(request_id=s.seq_id, prompt_token_ids=s.tokens[:s.prompt_len],

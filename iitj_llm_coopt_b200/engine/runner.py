@@ -59,10 +59,6 @@ class ModelRunner:
         self.steps = 0
         self.copied_bytes = 0
 
-    def forget(self, request) -> None:
-        """Told when a request was released.  The runner keeps nothing per request (the cache manager holds the
-        block tables in the form the device wants), so there is nothing to drop."""
-
     # ---- staging ---------------------------------------------------------------------
     def _stage(self, total: int):
         if self._copied is not None:

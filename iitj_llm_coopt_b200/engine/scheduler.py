@@ -83,8 +83,6 @@ class Scheduler:
         """Drop the victim's cache; it is recomputed from position 0 when re-admitted."""
         self.running.remove(seq)
         self.cache.release(seq.seq_id)
-        if self.engine is not None:
-            self.engine.runner_forget(seq.seq_id)
         seq.num_computed = 0
         seq.num_preemptions += 1
         self.counters["num_preemptions_total"] = self.counters.get("num_preemptions_total", 0) + 1

@@ -73,8 +73,18 @@ _SIGNATURES = {
     "llm_gemm_bf16_pair_status": [],
     "llm_gather_tokens": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
     "llm_sample_scratch_floats": [_c_int, _c_int],
-    "llm_sample": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
+    "llm_sample": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "llm_attention_decode_status": [],
 }
+
+# The library's health words in the order llm_sample copies them out (csrc/common.cuh): which kernel, and what its codes mean.
+HEALTH_WORDS = (
+    ("tcgen05 matrix product", "a bounded wait ran out (1 producer, 2 MMA issuer, 3 epilogue)"),
+    ("CTA-pair matrix product", "a bounded wait ran out (1 producer, 2 MMA issuer, 3 epilogue, 4 drained accumulator, "
+                                "5 other clusters' partial sums)"),
+    ("tcgen05 prefill attention", "a bounded wait ran out"),
+    ("decode attention", "keys_per_split * max_splits did not cover an item's keys (6)"),
+)
 
 
 def _ptr(t):
@@ -693,6 +703,30 @@ class Kernels:
         """0, or a code if the tcgen05 attention kernel gave up waiting on a barrier since the last call."""
         return self.lib.llm_attention_tcgen05_status()
 
+    def decode_status(self) -> int:
+        """0, or a code if a decode attention call since the last read was given too few splits for an item's keys."""
+        return self.lib.llm_attention_decode_status()
+
+    HEALTH_WORDS = len(HEALTH_WORDS)
+
+    def check_health(self, codes=None) -> None:
+        """Raises KernelError if a kernel of this library reported that it gave up (a bounded wait that ran out) or
+        that a contract was broken since the last check; what such a kernel wrote cannot be used.  `codes`: the
+        words as `sample(..., health=...)` copied them out; None reads them from the device now (which waits for
+        the work in flight).  On a failure the device words are cleared and the CTA-pair product's tile counters,
+        which a CTA that gave up may have left non-zero, are zeroed again, so the library can be used afterwards."""
+        if codes is None:
+            codes = [self.gemm_status(), self.gemm_pair_status(), self.attention_status(), self.decode_status()]
+        codes = [int(c) for c in codes]
+        if not any(codes):
+            return
+        self.gemm_status(), self.gemm_pair_status(), self.attention_status(), self.decode_status()   # read = clear
+        for counters in self._pair_counters.values():
+            counters.zero_()
+        bad = [f"{name}: code {c >> 16} in block/item {c & 0xffff} ({meaning})"
+               for c, (name, meaning) in zip(codes, HEALTH_WORDS) if c]
+        raise KernelError("a kernel gave up, its output is not valid: " + "; ".join(bad))
+
     def gather_tokens(self, dst, src, rows):
         """dst[i] = src[rows[i]] where rows[i] >= 0 (int32 device tensors): the previous step's sampled ids
         become this step's input tokens without a trip to the host."""
@@ -703,8 +737,9 @@ class Kernels:
         self._call("llm_gather_tokens", _ptr(dst), _ptr(src), _ptr(rows), dst.shape[0], self._stream())
 
     # ---- sampling --------------------------------------------------------------------
-    def sample(self, logits, temperature, keys, out):
-        """out[r] = argmax of row r (temperature[r] <= 0) or a draw from softmax(row / T)."""
+    def sample(self, logits, temperature, keys, out, health=None):
+        """out[r] = argmax of row r (temperature[r] <= 0) or a draw from softmax(row / T).  `health`: an int32 tensor
+        of HEALTH_WORDS entries that receives the library's status words (see `check_health`)."""
         _check(logits, "sample.logits", torch.float32, 2)
         _check(out, "sample.out", torch.int32, 1)
         rows = logits.shape[0]
@@ -713,10 +748,13 @@ class Kernels:
             _check(temperature, "sample.temperature", torch.float32, 1)
             _check(keys, "sample.keys", torch.int64, 1)
             _need(temperature.shape[0] == rows and keys.shape[0] == rows, "sample: one temperature and key per row")
+        if health is not None:
+            _check(health, "sample.health", torch.int32, 1)
+            _need(health.shape[0] >= self.HEALTH_WORDS, "sample.health: too short")
         need = self.lib.llm_sample_scratch_floats(rows, logits.shape[1])
         scratch = self._scratch("sample.part", need, logits.device) if need else None
         self._call("llm_sample", _ptr(logits), logits.shape[1], _ptr(temperature), _ptr(keys), _ptr(out), rows,
-                   logits.shape[1], _ptr(scratch), self._stream())
+                   logits.shape[1], _ptr(scratch), _ptr(health), self._stream())
         return out
 
 

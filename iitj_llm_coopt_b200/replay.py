@@ -68,7 +68,6 @@ def run(args, lines, out=sys.stdout, kernels=None) -> int:
         for rid in rec.get("end", []):
             if cache.has(rid):
                 cache.release(rid)
-                runner.forget(rid)
         print(f"done {step}", file=out, flush=True)
     return 0
 

@@ -4,7 +4,9 @@ Greedy rows take the argmax (engine/spec_decode.py:14-15; the lowest index wins 
 torch.argmax does).  Rows with temperature T > 0 are drawn from softmax(logits / T)
 (engine/spec_decode.py:16-17) by the Gumbel-max identity; the random stream of a row is
 keyed by (engine seed, request seed, index of the token in its request), so a request's
-tokens do not depend on batching.  One device-to-host copy per call brings the ids back.
+tokens do not depend on batching.  One device-to-host copy per call brings the ids back,
+and with them the kernel library's health words (a kernel whose bounded wait ran out leaves a
+code there): `fetch` raises instead of handing out tokens computed from such a kernel's output.
 """
 from __future__ import annotations
 
@@ -32,16 +34,21 @@ def _signed(u: int) -> int:
     return u - (1 << 64) if u >= (1 << 63) else u
 
 
+HEALTH = 4      # int32 entries in front of the ids: the library's health words
+
+
 class _Slot:
-    """Device output, pinned host copies and an event: one sampling call in flight."""
+    """Device output, pinned host copies and an event: one sampling call in flight.  The device output and its
+    host copy hold the health words first, then the ids (one copy brings both)."""
 
     def __init__(self, cap, device):
         pin = torch.cuda.is_available()
         self.cap = cap
-        self.out = torch.empty(cap, dtype=torch.int32, device=device)
+        self.both = torch.zeros(HEALTH + cap, dtype=torch.int32, device=device)
+        self.health, self.out = self.both[:HEALTH], self.both[HEALTH:]
         self.temps = torch.empty(cap, dtype=torch.float32, device=device)
         self.keys = torch.empty(cap, dtype=torch.int64, device=device)
-        self.host = torch.empty(cap, dtype=torch.int32)
+        self.host = torch.zeros(HEALTH + cap, dtype=torch.int32)
         self.temps_host = torch.empty(cap, dtype=torch.float32)
         self.keys_host = torch.empty(cap, dtype=torch.int64)
         if pin:
@@ -69,7 +76,7 @@ class Sampler:
     def _buffers(self, n):
         """(device ids, host ids) of a fresh slot (for callers that launch the kernel themselves)."""
         slot = self._slot(n)
-        return slot.out[:n], slot.host[:n]
+        return slot.out[:n], slot.host[HEALTH:HEALTH + n]
 
     def launch(self, logits, rows: list):
         """rows[i] = (temperature, request seed, token index) for logits row i; returns a handle for `fetch`.
@@ -80,14 +87,14 @@ class Sampler:
         slot = self._slot(n)
         out = slot.out[:n]
         if all(t <= 0 for t, _, _ in rows):
-            self.k.sample(logits, None, None, out)
+            self.k.sample(logits, None, None, out, health=slot.health)
         else:
             slot.temps_host[:n] = torch.tensor([float(t) for t, _, _ in rows], dtype=torch.float32)
             slot.keys_host[:n] = torch.tensor([_signed(row_key(self.seed, s, i)) for _, s, i in rows], dtype=torch.int64)
             slot.temps[:n].copy_(slot.temps_host[:n], non_blocking=True)
             slot.keys[:n].copy_(slot.keys_host[:n], non_blocking=True)
-            self.k.sample(logits, slot.temps[:n], slot.keys[:n], out)
-        slot.host[:n].copy_(out, non_blocking=True)
+            self.k.sample(logits, slot.temps[:n], slot.keys[:n], out, health=slot.health)
+        slot.host[:HEALTH + n].copy_(slot.both[:HEALTH + n], non_blocking=True)
         if slot.event is not None:
             slot.event.record()
         return _Handle(slot, n)
@@ -95,7 +102,10 @@ class Sampler:
     def fetch(self, handle) -> list:
         if handle.slot.event is not None:
             handle.slot.event.synchronize()
-        return handle.slot.host[:handle.n].tolist()
+        words = handle.slot.host[:HEALTH + handle.n].tolist()
+        if any(words[:HEALTH]):
+            self.k.check_health(words[:HEALTH])      # raises KernelError: these ids come from a kernel that gave up
+        return words[HEALTH:]
 
     def sample(self, logits, rows: list) -> list:
         """Ids of the rows; one device-to-host read."""

@@ -57,14 +57,16 @@ def random_parameters(arch, spec, seed: int, engine_dtype: torch.dtype, std: flo
     return params
 
 
-def write_model_dir(config, out_dir: str, seed: int, dtype=torch.bfloat16, std: float = 0.02) -> str:
+def write_model_dir(config, out_dir: str, seed: int, dtype=torch.bfloat16, std: float = 0.02, device="cpu") -> str:
     """Writes `out_dir/config.json` and `out_dir/model.safetensors`; `config` is a typed
-    configuration or a plain dict of config.json keys (with "architectures")."""
+    configuration or a plain dict of config.json keys (with "architectures").  `device`: where the
+    values are drawn (a GPU draws a large model in seconds; its generator gives other values than the CPU's)."""
     raw = config if isinstance(config, dict) else config.to_dict()
     arch = architecture_for(raw)
     typed = arch.config_class.from_dict(raw)
     os.makedirs(out_dir, exist_ok=True)
-    tensors = random_checkpoint(arch, arch.model_spec(typed), seed, dtype=dtype, std=std)
+    tensors = random_checkpoint(arch, arch.model_spec(typed), seed, dtype=dtype, std=std, device=device)
+    tensors = {name: t.cpu() for name, t in tensors.items()}
     save_file(tensors, os.path.join(out_dir, "model.safetensors"), metadata={"format": "pt"})
     with open(os.path.join(out_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(typed.to_dict(), f, indent=1)

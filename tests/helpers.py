@@ -43,5 +43,4 @@ def run_steps(engine, steps):
                     r += 1
         for rid in ends:
             cache.release(rid)
-            runner.forget(rid)
     return rows

@@ -6,6 +6,7 @@ reads config.json and the safetensors file itself and uses only elementary torch
 tests/golden/ holds outputs of the reference's own model code for two tiny models, and
 tests/test_plain_vs_reference.py checks this file against them.
 """
+import glob
 import json
 import math
 import os
@@ -14,15 +15,18 @@ import torch
 from safetensors import safe_open
 
 
-def read_model_dir(model_dir, dtype=torch.float32):
-    """(config dict, {tensor name: tensor as `dtype`}) -- engine/model.py:137-142."""
+def read_model_dir(model_dir, dtype=torch.float32, device="cpu"):
+    """(config dict, {tensor name: tensor as `dtype`}) -- engine/model.py:137-142.  Every *.safetensors file of the
+    folder is read (engine/model.py:139).  `device`: where the tensors are put; `forward` computes where they lie (a
+    GPU only for models too large for the CPU; the formulas are the same elementary torch ops)."""
     with open(os.path.join(model_dir, "config.json")) as f:
         cfg = json.load(f)
     cfg.setdefault("head_dim", cfg["hidden_size"] // cfg["num_attention_heads"])  # engine/model.py:47
     weights = {}
-    with safe_open(os.path.join(model_dir, "model.safetensors"), framework="pt", device="cpu") as sf:
-        for name in sf.keys():
-            weights[name] = sf.get_tensor(name).to(dtype)
+    for path in sorted(glob.glob(os.path.join(model_dir, "*.safetensors"))):
+        with safe_open(path, framework="pt", device="cpu") as sf:
+            for name in sf.keys():
+                weights[name] = sf.get_tensor(name).to(device=device, dtype=dtype)
     return cfg, weights
 
 
@@ -79,8 +83,8 @@ def causal_attention(q, k, v, scale, window=0):
     kk = k.repeat_interleave(group, dim=1).float()
     vv = v.repeat_interleave(group, dim=1).float()
     scores = torch.einsum("qhd,khd->hqk", q.float(), kk) * scale
-    qpos = torch.arange(T).view(1, T, 1)
-    kpos = torch.arange(T).view(1, 1, T)
+    qpos = torch.arange(T, device=q.device).view(1, T, 1)
+    kpos = torch.arange(T, device=q.device).view(1, 1, T)
     hidden = kpos > qpos
     if window > 0:
         hidden = hidden | (kpos < qpos - window + 1)
@@ -102,8 +106,9 @@ def forward(cfg, w, tokens, collect=None):
     H, Hkv, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     eps = cfg["rms_norm_eps"]
     cos, sin = rope_tables(cfg, T)
-    x = w["model.embed_tokens.weight"][torch.tensor(tokens, dtype=torch.long)]        # engine/model.py:191
-    cos, sin = cos.to(x.dtype), sin.to(x.dtype)                                      # engine/model.py:123-124
+    device = w["model.embed_tokens.weight"].device
+    x = w["model.embed_tokens.weight"][torch.tensor(tokens, dtype=torch.long, device=device)]   # engine/model.py:191
+    cos, sin = cos.to(device=device, dtype=x.dtype), sin.to(device=device, dtype=x.dtype)       # engine/model.py:123-124
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
         h = rms_norm(x, w[p + "input_layernorm.weight"], eps)                         # :193

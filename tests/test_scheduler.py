@@ -35,14 +35,13 @@ class FakeRunner:
     def __init__(self, cache):
         self.cache, self.history, self.log = cache, {}, []
 
-    def forget(self, request):
-        self.history.pop(request, None)
-
     def step(self, entries):
         rows = []
         self.log.append([(e.request, len(e.tokens), list(e.want)) for e in entries])
         for e in entries:
             start = self.cache.num_tokens(e.request)
+            if start == 0:
+                self.history[e.request] = []        # a new request, or one recomputed after a preemption
             hist = self.history.setdefault(e.request, [])
             assert len(hist) == start, "tokens must continue where the cache ends"
             self.cache.ensure(e.request, start + len(e.tokens))

@@ -6,7 +6,8 @@ device memory where they call: its split partials live in an array built into th
 library.  The test calls the symbol with ctypes exactly as such a caller would (raw
 pointers, nothing allocated in between), twice in a row on different inputs so that the
 second call runs over what the first left in the shared array, and compares each result
-with the ordinary entry point, which is given scratch by its caller.
+with the ordinary entry point, which is given scratch by its caller, and with the plain
+restatement of paged attention in tests/torch_kernels.py.
 
 This file sorts last on purpose: a run that stops at the first failure has then already
 run every other test.
@@ -17,6 +18,8 @@ from types import SimpleNamespace
 
 import pytest
 import torch
+
+import torch_kernels as R
 
 pytestmark = pytest.mark.gpu
 
@@ -66,6 +69,10 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice():
         torch.cuda.synchronize()
         err = (out.float() - want.float()).abs().max().item()
         assert err <= TOL * want.float().abs().max().item(), err
+        plain = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, head_dim)
+        err = (out.float() - plain).abs().max().item()
+        assert err <= TOL * plain.abs().max().item(), err
+    assert K.decode_status() == 0
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
@@ -83,3 +90,42 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     assert rc < 0
     msg = K.lib.llm_last_error().decode()
     assert "scratch" in msg and "2097152" in msg
+
+
+def test_too_few_splits_are_reported_and_stay_inside_their_partials():
+    """A caller that passes max_splits one too small for its longest item breaks the entry point's contract.  The
+    kernels cut that item down to max_splits: nothing outside the item's own partials is read or written (the other
+    items' results stay right, and so does the memory after the output), the item's last keys are left out (its
+    result is the attention over the keys that were covered), and the status word says so."""
+    from iitj_llm_coopt_b200 import kernels
+    K = kernels.load()
+    fn = K.lib.llm_attention_decode_bf16_static
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    fn.argtypes = [vp, ci, vp, vp, ci, vp, ci, vp, vp, vp, ci, ci, ci, ci, ci, ci, ctypes.c_float, ci, ci, vp]
+    fn.restype = ci
+    heads, kv_heads, head_dim, page, kps = 8, 2, 128, 16, 256
+    lens = [500, 1000, 300]                              # the second needs four splits of 256 keys; it gets three
+    q, cache, meta = _case(3, lens, heads, kv_heads, head_dim, page)
+    items = torch.arange(len(lens), dtype=torch.int32, device="cuda")
+    guard = 4096
+    buf = torch.full((len(lens) * heads * head_dim + guard,), 7.0, device="cuda", dtype=torch.bfloat16)
+    out = buf[:len(lens) * heads * head_dim].view(len(lens), heads * head_dim)
+    K.decode_status()                                    # start from a clear word
+    rc = fn(q.data_ptr(), q.shape[1], cache.data_ptr(), meta.block_table.data_ptr(), meta.block_table.shape[1],
+            items.data_ptr(), len(lens), meta.token_request.data_ptr(), meta.positions.data_ptr(), out.data_ptr(),
+            out.shape[1], heads, kv_heads, head_dim, page, 0, 1.0 / math.sqrt(head_dim), kps, 3,
+            torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, K.lib.llm_last_error().decode()
+    torch.cuda.synchronize()
+    code = K.decode_status()
+    assert code >> 16 == 6 and code & 0xffff == 1, hex(code)
+    assert K.decode_status() == 0                        # reading cleared it
+    assert bool((buf[len(lens) * heads * head_dim:] == 7.0).all())
+    plain = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, head_dim)
+    for b in (0, 2):
+        assert (out[b].float() - plain[b]).abs().max().item() <= TOL * plain.abs().max().item()
+    # the cut item: attention over its first 3 * 256 keys, by the plain restatement with the position moved back
+    short = meta.positions.clone()
+    short[1] = 3 * kps - 1
+    covered = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, short, heads, kv_heads, head_dim)
+    assert (out[1].float() - covered[1]).abs().max().item() <= TOL * covered.abs().max().item()

@@ -167,7 +167,17 @@ class TorchKernels:
         out.copy_(ref_linear(x, weight, swiglu))     # never split: `defer` has nothing to leave for later
         return out
 
-    def sample(self, logits, temperature, keys, out):
+    health_codes = (0, 0, 0, 0)     # what `sample` reports as the library's health words (tests set a failure here)
+
+    def sample(self, logits, temperature, keys, out, health=None):
         ids, _ = ref_sample(logits, temperature, keys)
         out.copy_(ids)
+        if health is not None:
+            health[:4] = torch.tensor(self.health_codes, dtype=torch.int32)
         return out
+
+    def check_health(self, codes=None):
+        codes = list(self.health_codes if codes is None else codes)
+        if any(codes):
+            self.health_codes = (0, 0, 0, 0)
+            raise RuntimeError(f"a kernel gave up: {codes}")
