@@ -30,26 +30,9 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# Llama 3.1 8B: the sizes of the benchmark configuration (random weights, no checkpoint)
-LLAMA_8B = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
-    "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
-    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
-    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                     "original_max_position_embeddings": 8192},
-    "tie_word_embeddings": False, "max_position_embeddings": 131072, "eos_token_id": 128001,
-}
-# The two smaller shapes of the same family (for `--shape`: profiles and sweeps at other sizes; the default line is the 8B shape)
-LLAMA_3B = dict(LLAMA_8B, hidden_size=3072, intermediate_size=8192, num_hidden_layers=28, num_attention_heads=24,
-                head_dim=128, tie_word_embeddings=True,
-                rope_scaling=dict(LLAMA_8B["rope_scaling"], factor=32.0))
-LLAMA_1B = dict(LLAMA_3B, hidden_size=2048, num_hidden_layers=16, num_attention_heads=32, head_dim=64)
-# a toy shape for trying the two arms out in seconds (never the benchmark)
-LLAMA_TOY = dict(LLAMA_8B, hidden_size=512, intermediate_size=1408, num_hidden_layers=2, num_attention_heads=8,
-                 num_key_value_heads=2, head_dim=64, vocab_size=4096)
-SHAPES = {"8b": ("llama-3.1-8b-shape-random", LLAMA_8B), "3b": ("llama-3.2-3b-shape-random", LLAMA_3B),
-          "1b": ("llama-3.2-1b-shape-random", LLAMA_1B), "toy": ("llama-toy-shape-random", LLAMA_TOY)}
+from iitj_llm_coopt_b200.presets import SHAPES      # config.json dicts of the benchmark shapes (data only; imports no kernels)
+
+BENCH_SHAPES = ("8b", "3b", "1b", "toy")            # the default line is the 8B shape; the others are for sweeps and trials
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -158,7 +141,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (reported)")
-    ap.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes: Llama 3.1 8B (the benchmark), 3.2 3B or 3.2 1B")
+    ap.add_argument("--shape", choices=BENCH_SHAPES, default="8b", help="layer sizes: Llama 3.1 8B (the benchmark), 3.2 3B or 3.2 1B")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")

@@ -147,7 +147,8 @@ def test_decode_attention_at_the_headline_shape(fused, bound):
     gq = torch.Generator(device="cuda").manual_seed(301)
     qkv = torch.randn((tokens, width), generator=gq, device="cuda") * 0.3
     # the planted keys: request b looks for a key at `far[b]`
-    far = {0: 0, 1: kps - 1, 2: kps, 3: kps + 1, 4: 2 * kps - 1, 5: 16399 - 1, 6: lens[6] - 2, 7: 4097, 9: 3 * kps}
+    far = {0: 0, 1: kps - 1, 2: kps, 3: kps + 1, 4: 2 * kps - 1, 5: 2 * kps, 13: 3 * kps - 1, 6: lens[6] - 2, 7: 4097, 9: 63}
+    far = {b: min(p, lens[b] - 2) for b, p in far.items()}        # (a split edge beyond a request's keys: its last key but one)
     direction = torch.randn(D, generator=gq, device="cuda")
     direction = direction / direction.norm()
     for b, pos in far.items():
@@ -162,7 +163,7 @@ def test_decode_attention_at_the_headline_shape(fused, bound):
     if fused:
         # the qkv product as two partial sums, no rotation (cos 1, sin 0): the kernel adds, stores the token's key and
         # value, and attends
-        parts = torch.stack([qkv * 0.25, qkv * 0.75]).contiguous()
+        parts = torch.stack([qkv * 0.5, qkv * 0.5]).contiguous()       # (halves add up exactly)
         cos = torch.ones(tokens, D // 2, device="cuda")
         sin = torch.zeros(tokens, D // 2, device="cuda")
         want_cache = cache.clone()
