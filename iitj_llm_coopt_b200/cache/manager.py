@@ -7,18 +7,23 @@ table[p // page] * page + p % page, `ensure` that raises before it allocates any
 `free` at the end of a request).  What is added here:
 
 * Groups.  Layers (cache entries) whose `CacheNeed` is equal share one group.  Each paged
-  group has its own pool of pages, its own table per request and its own rule for giving
-  pages back: a group that keeps every token returns pages when the request ends; a
-  group with a window also returns, after each step, the pages that every later query's
-  window has passed (their table entry becomes -1 and is never read again).
+  group has its own pool of pages, of its own size, its own table per request and its own
+  rule for giving pages back: a group that keeps every token returns pages when the request
+  ends; a group with a window also returns, after each step, the pages that every later
+  query's window has passed (their table entry becomes -1 and is never read again).  A
+  windowed group never holds more than a window and a step's new tokens per request, so its
+  pool is sized for that (`pool_pages`), not for whole contexts.
   One page id addresses the same page in every cache entry of its group, as in the
   reference (engine/model.py:148-155: one K and V tensor per layer, same block ids).
 * State slots.  Every admitted request holds one slot id in [0, max_requests); groups of
   kind "state" keep a [entries, max_requests, *state_shape] buffer indexed by it.  The
   slot exists even when no layer keeps state (Llama: zero bytes).
 
-Device storage of a paged group: [entries, pages + 1, 2, kv_heads, page_size, head_dim] (the last page is
-the padding page, never handed out)
+* State that starts at zero.  `admit` clears the request's slot in every state group, so a part
+  with state never has to know whether a portion is a request's first.
+
+Device storage of a paged group: [entries, pages of the group + 1, 2, kv_heads, page_size, head_dim] (the last
+page is the group's padding page, never handed out)
 (K plane then V plane of a page; one head's rows of a page are contiguous).
 """
 from __future__ import annotations
@@ -109,11 +114,13 @@ class StateGroup:
 
 class CacheManager:
     def __init__(self, needs: list, page_size: int, num_pages: int, max_requests: int,
-                 dtype: torch.dtype = torch.bfloat16, device=None):
-        """needs[i] is the CacheNeed of cache entry i.  `device=None` keeps bookkeeping only
-        (no storage is allocated), which is all the scheduler and the CPU tests use."""
+                 dtype: torch.dtype = torch.bfloat16, device=None, max_step_tokens: int | None = None):
+        """needs[i] is the CacheNeed of cache entry i.  `num_pages` is the pool of a group that keeps every token;
+        a group with a window gets `pool_pages(...)` pages if `max_step_tokens` (the most tokens one step brings)
+        is given, else `num_pages` too.  `device=None` keeps bookkeeping only (no storage is allocated), which is
+        all the scheduler and the CPU tests use."""
         self.page_size, self.num_pages, self.max_requests = page_size, num_pages, max_requests
-        self.dtype, self.device = dtype, device
+        self.dtype, self.device, self.max_step_tokens = dtype, device, max_step_tokens
         self.groups: list = []
         self.entry_group: list = []       # entry -> (group index, index of the entry inside the group)
         by_need: dict = {}
@@ -124,7 +131,8 @@ class CacheManager:
             if need not in by_need:
                 by_need[need] = len(self.groups)
                 if need.kind == "paged_kv":
-                    self.groups.append(PagedGroup(need, [], PagePool(num_pages), page_size))
+                    pages = self.pool_pages(need, page_size, num_pages, max_requests, max_step_tokens)
+                    self.groups.append(PagedGroup(need, [], PagePool(pages), page_size))
                 elif need.kind == "state":
                     self.groups.append(StateGroup(need, []))
                 else:
@@ -137,7 +145,7 @@ class CacheManager:
         for i in self.paged:
             g = self.groups[i]
             g.matrix = np.zeros((max_requests + 1, 16), dtype=np.int32)
-            g.matrix[max_requests, 0] = num_pages            # the padding row: one page, the padding page
+            g.matrix[max_requests, 0] = g.pool.num_pages     # the padding row: one page, the group's padding page
             g.lengths = np.zeros(max_requests + 1, dtype=np.int32)
             g.lengths[max_requests] = 1
         # per-request records
@@ -154,19 +162,26 @@ class CacheManager:
         for g in self.groups:
             if isinstance(g, PagedGroup):
                 n = g.need
-                # one page more than the pool hands out: the padding page (see pad_page)
-                g.storage = torch.zeros((len(g.entries), self.num_pages + 1, 2, n.kv_heads, self.page_size, n.head_dim),
+                # one page more than the pool hands out: the group's padding page.  Rows that only pad a batch to a
+                # size with a captured graph read and write there (the reference keeps such a scratch page too,
+                # engine/engine.py:207-211)
+                g.storage = torch.zeros((len(g.entries), g.pool.num_pages + 1, 2, n.kv_heads, self.page_size, n.head_dim),
                                         dtype=self.dtype, device=self.device)
             else:
                 dt = getattr(torch, g.need.state_dtype)
                 g.storage = torch.zeros((len(g.entries), self.max_requests + 1) + tuple(g.need.state_shape),
                                         dtype=dt, device=self.device)
 
-    @property
-    def pad_page(self) -> int:
-        """A page id that no request ever gets: rows that only pad a batch to a size with a captured graph
-        read and write there (the reference keeps such a scratch page too, engine/engine.py:207-211)."""
-        return self.num_pages
+    @staticmethod
+    def pool_pages(need, page_size: int, num_pages: int, max_requests: int, max_step_tokens: int | None) -> int:
+        """Pages of the pool of a paged group.  A group that keeps every token gets `num_pages`.  A group with a
+        window holds, per request, the pages its window touches (window / page, and one more at either end) and,
+        until the step is over, the pages of the step's new tokens, of which all requests together bring at most
+        `max_step_tokens`: that, if it is less."""
+        if need.window <= 0 or max_step_tokens is None:
+            return num_pages
+        per_request = -(-need.window // page_size) + 2
+        return min(num_pages, max_requests * per_request + -(-max_step_tokens // page_size) + max_requests)
 
     @property
     def pad_slot(self) -> int:
@@ -174,9 +189,28 @@ class CacheManager:
         return self.max_requests
 
     @staticmethod
-    def bytes_per_page(needs: list, page_size: int, itemsize: int) -> int:
-        """Bytes one page id costs over all paged cache entries (to size the pool from memory)."""
-        return sum(2 * n.kv_heads * n.head_dim * page_size * itemsize for n in needs if n.kind == "paged_kv")
+    def bytes_for(needs: list, page_size: int, num_pages: int, itemsize: int, max_requests: int,
+                  max_step_tokens: int | None) -> int:
+        """Bytes of the paged storage with `num_pages` pages: every cache entry pays for the pages of its group's pool."""
+        return sum(2 * n.kv_heads * n.head_dim * page_size * itemsize
+                   * (CacheManager.pool_pages(n, page_size, num_pages, max_requests, max_step_tokens) + 1)
+                   for n in needs if n.kind == "paged_kv")
+
+    @staticmethod
+    def pages_for_bytes(needs: list, page_size: int, budget_bytes: float, itemsize: int, max_requests: int,
+                        max_step_tokens: int | None) -> int:
+        """The largest `num_pages` whose paged storage fits `budget_bytes` (0 if not even one page does)."""
+        def cost(pages):
+            return CacheManager.bytes_for(needs, page_size, pages, itemsize, max_requests, max_step_tokens)
+        if cost(1) > budget_bytes:
+            return 0
+        lo, hi = 1, 2
+        while cost(hi) <= budget_bytes and hi < (1 << 40):
+            lo, hi = hi, hi * 2
+        while hi - lo > 1:                         # cost is monotone in the page count
+            mid = (lo + hi) // 2
+            lo, hi = (mid, hi) if cost(mid) <= budget_bytes else (lo, mid)
+        return lo
 
     def view(self, entry: int):
         """(group index, storage of that cache entry): [pages, 2, kv_heads, page, head_dim] or
@@ -199,12 +233,15 @@ class CacheManager:
         if not self.free_slots:
             raise CacheError(f"all {self.max_requests} request slots are in use")
         self.stored[request] = 0
-        self.slot_of[request] = self.free_slots.popleft()
-        for gi in self.paged:
-            self.groups[gi].tables[request] = []
-            self.groups[gi].lengths[self.slot_of[request]] = 0
+        slot = self.slot_of[request] = self.free_slots.popleft()
+        for g in self.groups:
+            if isinstance(g, PagedGroup):
+                g.tables[request] = []
+                g.lengths[slot] = 0
+            elif g.storage is not None:
+                g.storage[:, slot].zero_()         # state starts at zero, whoever held the slot before
         self._set_room(request)
-        return self.slot_of[request]
+        return slot
 
     def has(self, request) -> bool:
         return request in self.stored
@@ -235,16 +272,38 @@ class CacheManager:
     # ---- capacity ------------------------------------------------------------------------
     @property
     def num_free(self) -> int:
-        """Free pages of the tightest paged group."""
+        """Free pages of the paged group with the fewest."""
         return min((self.groups[gi].pool.num_free for gi in self.paged), default=self.num_pages)
 
     @property
     def usage(self) -> float:
-        return 1.0 - self.num_free / self.num_pages
+        """The fullest paged group's share of pages in use."""
+        return max((1.0 - self.groups[gi].pool.num_free / self.groups[gi].pool.num_pages for gi in self.paged), default=0.0)
 
     @property
     def capacity_tokens(self) -> int:
-        return self.num_pages * self.page_size
+        """Tokens a lone request can hold: what the pools of the groups that keep every token take."""
+        full = [self.groups[gi].pool.num_pages for gi in self.paged if self.groups[gi].need.window <= 0]
+        return min(full, default=self.num_pages) * self.page_size
+
+    def can_admit(self, tokens: int, watermark: float = 0.0) -> bool:
+        """True if a new request's first `tokens` tokens fit every paged group while `watermark` of the group's
+        pool stays free (the reference's admission rule, engine/engine.py:124-140, per group)."""
+        for gi in self.paged:
+            g = self.groups[gi]
+            if g.pages_for(tokens) > g.pool.num_free - int(watermark * g.pool.num_pages):
+                return False
+        return True
+
+    def can_grow_all(self, totals: list) -> bool:
+        """True if every (request, total tokens) of `totals` can be served at once: per group, the new pages all of
+        them need together are free."""
+        for gi in self.paged:
+            g = self.groups[gi]
+            need = sum(g.extra_pages(r, t) for r, t in totals if t > self.room.get(r, 0))
+            if need > g.pool.num_free:
+                return False
+        return True
 
     def extra_pages_needed(self, request, total_tokens: int) -> int:
         """Largest number of new pages any group needs so the request can hold total_tokens."""
@@ -376,7 +435,7 @@ class CacheManager:
             if set(g.tables) != set(self.stored):
                 raise CacheError(f"group {gi}: tables exist for other requests than the admitted ones")
             rows = np.zeros_like(g.matrix)
-            rows[self.max_requests, 0] = self.num_pages
+            rows[self.max_requests, 0] = g.pool.num_pages
             sizes = np.zeros_like(g.lengths)
             sizes[self.max_requests] = 1
             for request, table in g.tables.items():

@@ -146,8 +146,7 @@ class LlamaConfig:
         ff = FeedForwardSpec(kind="swiglu", width=self.hidden_size, inner=self.intermediate_size,
                              activation="silu")
         norm = NormSpec(kind="rmsnorm", width=self.hidden_size, eps=self.rms_norm_eps)
-        layer = LayerSpec(arrangement="prenorm", mixer=mixer, feed_forward=ff,
-                          mixer_norm=norm, feed_forward_norm=norm)
+        layer = LayerSpec.of("prenorm", mixer_norm=norm, mixer=mixer, feed_forward_norm=norm, feed_forward=ff)
         n = self.num_hidden_layers
         return ModelSpec(width=self.hidden_size, vocab=self.vocab_size,
                          layers=tuple(layer for _ in range(n)),

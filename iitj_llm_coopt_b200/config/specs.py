@@ -1,8 +1,9 @@
 """Architecture-neutral descriptions of what a model is made of.
 
-A model is a list of layers and an order in which they run.  Each layer names its
-parts (norm, mixer, feed-forward, position encoding) with every size and constant
-they need.  Nothing here knows about a particular architecture: an architecture's
+A model is an embedding, a list of layers, an order in which they run, a final norm and an
+output head.  Each layer names its arrangement and, by name, the parts that arrangement is wired
+from (norms, a mixer, a feed-forward, ...; a mixer names its position encoding) with every size
+and constant they need.  Nothing here knows about a particular architecture: an architecture's
 typed configuration (for instance `LlamaConfig`) turns its config.json keys into
 these records, and the parts are built from the records alone.
 """
@@ -84,12 +85,44 @@ class FeedForwardSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: `arrangement` names how the parts are wired (parts.ARRANGEMENTS)."""
+    """One block: `arrangement` names how the parts are wired (parts.ARRANGEMENTS); `parts` holds one spec record
+    for each part name the arrangement declares (its PARTS), as (name, spec) pairs.  `LayerSpec.of("prenorm",
+    mixer_norm=..., mixer=..., feed_forward_norm=..., feed_forward=...)` builds one from keywords."""
     arrangement: str
-    mixer: MixerSpec
-    feed_forward: FeedForwardSpec
-    mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    parts: tuple = ()            # of (part name, spec record)
+
+    @classmethod
+    def of(cls, arrangement: str, **parts) -> "LayerSpec":
+        return cls(arrangement, tuple(parts.items()))
+
+    def part(self, name: str):
+        for n, spec in self.parts:
+            if n == name:
+                return spec
+        raise KeyError(f"layer ({self.arrangement}) has no part {name!r}; it has: {', '.join(n for n, _ in self.parts)}")
+
+    def names(self) -> tuple:
+        return tuple(n for n, _ in self.parts)
+
+
+@dataclass(frozen=True)
+class EmbeddingSpec:
+    """How token ids become the first residual stream."""
+    kind: str                    # key in parts.EMBEDDINGS
+    vocab: int
+    width: int
+    scale: float = 1.0
+    options: tuple = ()
+
+
+@dataclass(frozen=True)
+class HeadSpec:
+    """How the normed rows that want logits become logits."""
+    kind: str                    # key in parts.HEADS
+    vocab: int
+    width: int
+    scale: float = 1.0
+    options: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -118,6 +151,14 @@ class ModelSpec:
     eos_token_ids: tuple = ()
     embedding_scale: float = 1.0
     logit_scale: float = 1.0
+    embedding: EmbeddingSpec | None = None     # None: a plain table of [vocab, width] scaled by embedding_scale
+    head: HeadSpec | None = None               # None: a plain [vocab, width] projection scaled by logit_scale
+
+    def embedding_spec(self) -> EmbeddingSpec:
+        return self.embedding or EmbeddingSpec("table", self.vocab, self.width, self.embedding_scale)
+
+    def head_spec(self) -> HeadSpec:
+        return self.head or HeadSpec("linear", self.vocab, self.width, self.logit_scale)
 
     def cache_entries(self) -> int:
         """Number of distinct cache entries the run order writes."""

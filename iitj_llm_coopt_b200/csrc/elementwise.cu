@@ -540,4 +540,50 @@ LLM_API int llm_silu_mul(const void* gu, void* act, int dtype, int tokens, int i
     });
 }
 
+// ---------------------------------------------------------------------------------------
+// small float32 helpers: x *= scale (a head with a logit scale), and out = sum over the first
+// dimension of parts [splits, n] (k-split partial sums whose reader is no kernel of this library)
+// ---------------------------------------------------------------------------------------
+namespace {
+
+__global__ void scale_kernel(float* __restrict__ x, float scale, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] *= scale;
+}
+
+// parts are added in split order, as every other reader of deferred sums adds them
+template <typename TO>
+__global__ void sum_parts_kernel(const float* __restrict__ parts, TO* __restrict__ out, int splits, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float a = parts[i];
+        for (int s = 1; s < splits; ++s) a += parts[(size_t)s * n + i];
+        out[i] = from_f32<TO>(a);
+    }
+}
+
+}  // namespace
+
+LLM_API int llm_scale_f32(float* x, float scale, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    llm_launch(scale_kernel, blocks, 256, 0, stream, x, scale, (size_t)n);
+    LLM_CHECK_LAUNCH("scale_f32");
+    return 0;
+}
+
+// out [n] (dtype `out_dtype`) = parts[0] + parts[1] + ... + parts[splits - 1], each [n] float32
+LLM_API int llm_sum_parts(const float* parts, void* out, int out_dtype, int splits, long long n, cudaStream_t stream) {
+    if (n <= 0 || splits <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    return llm_dispatch_dtype(out_dtype, [&](auto tag) {
+        using T = decltype(tag);
+        llm_launch(sum_parts_kernel<T>, blocks, 256, 0, stream, parts, (T*)out, splits, (size_t)n);
+        LLM_CHECK_LAUNCH("sum_parts");
+        return 0;
+    });
+}
+
 LLM_TRACE_EXPORT(elementwise)

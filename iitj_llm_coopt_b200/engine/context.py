@@ -89,6 +89,7 @@ class StepContext:
     starts: list = field(default_factory=list)
     slots_host: list = field(default_factory=list)
     shared: dict = field(default_factory=dict)   # per-step results that several layers share (e.g. rotary tables)
+    prepared: dict = field(default_factory=dict)  # prepare_key -> the StepPlan a part made for this step (parts/base.py)
 
     def buffer(self, name: str, shape, dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)

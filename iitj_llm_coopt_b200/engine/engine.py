@@ -188,9 +188,8 @@ class Engine:
             return None
 
         decodes = [s for s in sched.running if s.remaining == 1]
-        need = sum(cache.extra_pages_needed(s.seq_id, len(s.tokens)) for s in decodes)
-        if need > cache.num_free:                  # somebody would have to give way: decide that with prev known
-            return undo()
+        if not cache.can_grow_all([(s.seq_id, len(s.tokens)) for s in decodes]):
+            return undo()                          # somebody would have to give way: decide that with prev known
         waiting_before = len(sched.waiting)
         sched.held_slots = len(running_before) - len(sched.running)     # the ending ones keep slot and pages until collected
         try:

@@ -41,8 +41,11 @@ def workspace_bytes_estimate(spec, tokens: int, rows: int, itemsize: int) -> int
     shapes need: the workspace grows its buffers to powers of two)."""
     widest = 0
     for layer in spec.layers:
-        m, f = layer.mixer, layer.feed_forward
-        widest = max(widest, (m.heads + 2 * m.kv_heads) * m.head_dim + m.heads * m.head_dim + 3 * f.inner + 3 * spec.width)
+        cols = 3 * spec.width
+        for _name, ps in layer.parts:        # whatever sizes the layer's parts name: projections, inner widths
+            heads, kv_heads, head_dim = (getattr(ps, a, 0) or 0 for a in ("heads", "kv_heads", "head_dim"))
+            cols += (2 * heads + 2 * kv_heads) * head_dim + 3 * (getattr(ps, "inner", 0) or 0)
+        widest = max(widest, cols)
     return 2 * (tokens * (widest * itemsize + 4 * spec.width) + rows * spec.vocab * 4) + (64 << 20)
 
 
@@ -75,21 +78,26 @@ def build_engine(model: str | None = None, engine_config: EngineConfig | None = 
         del params
         needs = cache_needs(spec)
         itemsize = 2 if dtype == torch.bfloat16 else 4
-        per_page = CacheManager.bytes_per_page(needs, ec.page_size, itemsize)
+        step_tokens = ec.max_num_batched_tokens
+
+        def pages_that_fit(budget_bytes):
+            return CacheManager.pages_for_bytes(needs, ec.page_size, budget_bytes, itemsize, ec.max_num_seqs, step_tokens)
         if ec.num_pages is not None:
             num_pages = ec.num_pages
         elif ec.kv_gb is not None:
-            num_pages = int(ec.kv_gb * 2**30 // max(per_page, 1))
+            num_pages = pages_that_fit(ec.kv_gb * 2**30)
         else:
+            # what is left under the utilisation cap after the weights, the step's scratch tensors and a margin
+            # (engine/engine.py:174-192 measures the activations instead of estimating them)
             free, total = torch.cuda.mem_get_info(device)
             work = workspace_bytes_estimate(spec, ec.max_num_batched_tokens, ec.max_num_seqs, itemsize)
-            budget = total * ec.gpu_memory_utilization - (total - free) - work - (256 << 20)
-            num_pages = int(budget // max(per_page, 1))
+            num_pages = pages_that_fit(total * ec.gpu_memory_utilization - (total - free) - work - (256 << 20))
             # no need for more pages than max_num_seqs full-length requests could ever fill
             num_pages = min(num_pages, ec.max_num_seqs * (-(-ec.max_model_len // ec.page_size)))
         if num_pages <= 0:
             raise RuntimeError("no memory left for the key/value cache")
-        cache = CacheManager(needs, ec.page_size, num_pages, max_requests=ec.max_num_seqs, dtype=dtype, device=device)
+        cache = CacheManager(needs, ec.page_size, num_pages, max_requests=ec.max_num_seqs, dtype=dtype, device=device,
+                             max_step_tokens=step_tokens)
         runner = ModelRunner(net, cache, device, cuda_graphs=ec.cuda_graphs)
         sampler = Sampler(kernels, ec.seed, device)
     pol = policy or StaticPolicy(max_num_seqs=ec.max_num_seqs, max_batched_tokens=ec.max_num_batched_tokens,

@@ -12,6 +12,11 @@ table, the cache slot of every new token and the rows that need logits.  Differe
 all index arrays travel in one pinned buffer and one host-to-device copy; logits are
 computed only where wanted (possibly nowhere); page tables are mirrored as arrays so a
 decode step does not rebuild them from Python lists.
+
+Parts may need index arrays of their own (an attention kernel's tile lists): the step function
+asks every part that implements `prepare_step` (parts/base.py) once per step, places the arrays
+it returns in the same buffer, hands them back as device views, and folds the part's `graph_key`
+into the key under which the step's CUDA graph is kept.  It knows no part by name.
 """
 from __future__ import annotations
 
@@ -22,10 +27,11 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheError
-from ..kernels import AttentionPlan, Kernels
-
-LONG_PREFILL = Kernels.LONG_PREFILL
+from ..parts.base import Part, StepShape
 from .context import GroupMeta, StepContext, Workspace
+
+
+_no_plan = Part.prepare_step       # the base class's "nothing to plan"
 
 
 @dataclass
@@ -58,6 +64,17 @@ class ModelRunner:
         self._capture_stream = None  # side stream that graph captures are recorded on
         self.steps = 0
         self.copied_bytes = 0
+        self._preparer_list = None
+
+    def _preparers(self) -> list:
+        """(prepare_key, part) of every part of the model that plans per-step arrays, one per key."""
+        if self._preparer_list is None:
+            found = {}
+            for part in getattr(self.model, "all_parts", lambda: [])():
+                if getattr(type(part), "prepare_step", _no_plan) is not _no_plan:
+                    found.setdefault(getattr(part, "prepare_key", None) or id(part), part)
+            self._preparer_list = list(found.items())
+        return self._preparer_list
 
     # ---- staging ---------------------------------------------------------------------
     def _stage(self, total: int):
@@ -193,11 +210,14 @@ class ModelRunner:
         graphable = self.use_graphs
         if graphable:
             widths = {g: max(16, 1 << (w - 1).bit_length()) for g, w in widths.items()}
-        plan = AttentionPlan(qlens, seqlens, self.device, items=False, tiles=False, total_tokens=T)
-        if graphable and plan.n_items:
-            # the split choice of decode attention is frozen into a graph: fix it by an upper bound of
-            # the contexts, in steps of 512 tokens, and capture anew when the batch outgrows the bound
-            plan.context_bound = (max(plan.decode_pos) + 512) // 512 * 512
+        # the parts' own index arrays and what a graph freezes of them
+        shape = StepShape(query_lens=qlens, seq_lens=seqlens, num_tokens=T, decode_shaped=decode_shaped,
+                          graphable=graphable, device=self.device)
+        prepared = {}
+        for key, part in self._preparers():
+            plan = part.prepare_step(shape)
+            if plan is not None:
+                prepared[key] = plan
 
         # layout of the one int32 buffer
         layout, off = {}, 0
@@ -215,9 +235,9 @@ class ModelRunner:
         fed = prev_ids is not None and any(e.source_rows is not None for e in entries)
         if fed:
             place("token_src", T)
-        place("attn_items", plan.n_items)
-        place("attn_tiles", 4 * plan.n_tiles)
-        place("attn_big_tiles", 4 * len(plan.big_rows))
+        for key, plan in prepared.items():
+            for name, values in plan.arrays.items():
+                place(f"{key}.{name}", len(values))
         old_meta = self._meta
         host = self._stage(off)
         if self._meta is not old_meta:
@@ -259,11 +279,9 @@ class ModelRunner:
             put("logit_rows", [first[b] + w for b, e in enumerate(entries) for w in e.want])
         put("state_slots", slot_rows)
         put("first_portion", st == 0)
-        if plan.n_items:
-            put("attn_items", plan.item_rows)
-        if plan.n_tiles:
-            put("attn_tiles", np.asarray(plan.tile_rows, dtype=np.int64).reshape(-1))
-            put("attn_big_tiles", np.asarray(plan.big_rows, dtype=np.int64).reshape(-1))
+        for key, plan in prepared.items():
+            for name, values in plan.arrays.items():
+                put(f"{key}.{name}", values)
         ps = cache.page_size
         page_of, offset_in = positions // ps, positions % ps
         for g in groups:
@@ -287,9 +305,8 @@ class ModelRunner:
 
         if fed:
             self.model.k.gather_tokens(dev("token_ids"), prev_ids, dev("token_src"))
-        plan.items = dev("attn_items") if plan.n_items else None
-        plan.tiles = dev("attn_tiles").view(-1, 4) if plan.n_tiles else None
-        plan.big_tiles = dev("attn_big_tiles").view(-1, 4) if plan.n_tiles else None
+        for key, plan in prepared.items():
+            plan.bind({name: dev(f"{key}.{name}") for name in plan.arrays})
         token_request, positions = dev("token_request"), dev("positions")
         cu_dev, seq_dev = dev("cu_seqlens"), dev("seq_lens")
         metas = {}
@@ -297,19 +314,16 @@ class ModelRunner:
             o, _ = layout[f"table{g}"]
             metas[g] = GroupMeta(block_table=self._meta[o:o + B * widths[g]].view(B, widths[g]),
                                  slots=dev(f"slots{g}"), token_request=token_request, positions=positions,
-                                 query_lens=qlens, seq_lens_host=seqlens, cu_seqlens=cu_dev, seq_lens=seq_dev,
-                                 attention_plan=plan)
+                                 query_lens=qlens, seq_lens_host=seqlens, cu_seqlens=cu_dev, seq_lens=seq_dev)
         ctx = StepContext(num_tokens=T, num_requests=B, num_logits=N, token_ids=dev("token_ids"),
                           positions=positions, token_request=token_request, cu_seqlens=cu_dev, seq_lens=seq_dev,
                           logit_rows=dev("logit_rows"), state_slots=dev("state_slots"),
                           first_portion=dev("first_portion"), groups=metas, cache=cache,
                           workspace=self.workspace, requests=[e.request for e in entries] + [None] * pad,
-                          query_lens=qlens, starts=starts, slots_host=slots_b)
+                          query_lens=qlens, starts=starts, slots_host=slots_b, prepared=prepared)
         if graphable:
-            # (a long context switches the prefill attention to key splits: such steps get graphs of their own)
-            long_prefill = not decode_shaped and any(n > 1 and end >= LONG_PREFILL for n, end in zip(qlens, seqlens))
-            shape = ("decode", B) if decode_shaped else (tuple(qlens), tuple(len(e.want) for e in entries))
-            key = (shape, tuple(sorted(widths.items())), plan.context_bound, fed, long_prefill)
+            form = ("decode", B) if decode_shaped else (tuple(qlens), tuple(len(e.want) for e in entries))
+            key = (form, tuple(sorted(widths.items())), fed, tuple((k, p.graph_key) for k, p in prepared.items()))
             logits = self._forward_graphed(key, ctx, eager_runs=self.graph_after if decode_shaped else max(4, self.graph_after))
         else:
             logits = self.model.forward(ctx)

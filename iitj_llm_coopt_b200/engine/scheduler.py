@@ -3,7 +3,8 @@
 Three phases per step, as the reference's Scheduler.schedule (engine/engine.py:91-155):
   1. decodes first: every running sequence with exactly one token left to feed; if their
      new pages do not fit, the policy's victim (the newest running sequence) is preempted
-     until they do or only one sequence runs;
+     until they do or only one sequence runs; if there are more of them than the token budget,
+     they take turns from step to step;
   2. running prefills, oldest first, each cut to what is left of the step's token budget;
      a portion whose pages do not fit is skipped this step;
   3. admissions from the waiting queue while the budget, `max_num_seqs` and the page
@@ -78,6 +79,7 @@ class Scheduler:
         self.waiting: deque = deque()
         self.running: list = []
         self.held_slots = 0          # request slots held by sequences that are not in `running` (about to finish)
+        self._decode_turn = 0        # where phase 1 starts in the list of decodes when the budget cannot take them all
 
     def _preempt(self, seq) -> None:
         """Drop the victim's cache; it is recomputed from position 0 when re-admitted."""
@@ -103,10 +105,16 @@ class Scheduler:
         # 1. decodes: reserve one more token each, preempting the newest if pages are short
         while True:
             decodes = [s for s in self.running if s.remaining == 1]
-            need = sum(cache.extra_pages_needed(s.seq_id, len(s.tokens)) for s in decodes)
-            if need <= cache.num_free or len(self.running) <= 1:
+            if cache.can_grow_all([(s.seq_id, len(s.tokens)) for s in decodes]) or len(self.running) <= 1:
                 break
             self._preempt(pol.preempt_victim(self.running))
+        if len(decodes) > budget:
+            # more sequences decode than a step may hold tokens: start where the last step stopped, so that every
+            # sequence advances within ceil(len / budget) steps (the reference always starts at the front,
+            # engine/engine.py:109-112, and would starve the tail)
+            at = self._decode_turn % len(decodes)
+            decodes = decodes[at:] + decodes[:at]
+            self._decode_turn = at + budget
         for s in decodes:
             if budget <= 0:
                 break
@@ -130,12 +138,11 @@ class Scheduler:
 
         # 3. admissions
         while self.waiting and budget > 0 and len(self.running) + self.held_slots < pol.max_num_seqs:
-            reserve = int(pol.watermark * cache.num_pages) if self.running else 0
             i = pol.pick_next(self.waiting, self.engine)
             s = self.waiting[i]
             end = s.num_computed + min(s.remaining, budget)
-            pages = -(-end // cache.page_size)
-            if pages > cache.num_free - reserve or not pol.admit(s, self.engine):
+            # (the watermark is waived while nothing runs, so that a prompt that fits the pool is admitted eventually)
+            if not cache.can_admit(end, pol.watermark if self.running else 0.0) or not pol.admit(s, self.engine):
                 break
             del self.waiting[i]
             self.running.append(s)

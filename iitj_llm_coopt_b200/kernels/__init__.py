@@ -45,6 +45,8 @@ _SIGNATURES = {
     "llm_rope_store": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, ctypes.c_longlong, _c_void_p],
     "llm_silu_mul": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "llm_scale_f32": [_c_void_p, _c_float, ctypes.c_longlong, _c_void_p],
+    "llm_sum_parts": [_c_void_p, _c_void_p, _c_int, _c_int, ctypes.c_longlong, _c_void_p],
     "llm_attention_generic": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "llm_attention_bf16_supported": [_c_int, _c_int, _c_int],
@@ -142,7 +144,19 @@ class AttentionPlan:
     """How one step's tokens are handed to the tensor-core attention kernels: requests that
     bring one token go to the split-key decode kernel (`items`: their token rows), the rest
     are cut into tiles of 64 queries for the prefill kernel (`tiles`: first token row, rows,
-    position of the first row, request)."""
+    position of the first row, request).
+
+    It is also the step plan of the attention mixer (parts/base.py, StepPlan): `arrays` are the lists the
+    step function copies to the device with its own index arrays, `bind` receives them back as device
+    tensors, `graph_key` is what a captured graph freezes of the plan."""
+
+    graph_key = ()
+    arrays: dict = {}
+
+    def bind(self, views: dict) -> None:
+        self.items = views.get("items")
+        self.tiles = views["tiles"].view(-1, 4) if "tiles" in views else None
+        self.big_tiles = views["big_tiles"].view(-1, 4) if "big_tiles" in views else None
 
     TILE = 64
     SPLIT_RULE = os.environ.get("IITJ_DECODE_SPLIT", "auto")    # "equal": always the rule for equal contexts (measurements)
@@ -304,6 +318,28 @@ class Kernels:
         rc = self.lib.llm_check_device()
         if rc != 0:
             raise KernelError(self.lib.llm_last_error().decode())
+
+    def plan_attention(self, shape) -> AttentionPlan:
+        """The attention mixer's plan of a step (`shape`: parts.base.StepShape).  For a step that may run from a
+        captured graph the split choice of decode attention is fixed by an upper bound of the contexts, in steps of
+        512 tokens (the graph is captured anew when the batch outgrows the bound), and a step whose prompt portions
+        reach contexts from LONG_PREFILL on is kept apart (its prefill attention launches key splits and a merge)."""
+        plan = AttentionPlan(shape.query_lens, shape.seq_lens, shape.device, items=False, tiles=False,
+                             total_tokens=shape.num_tokens)
+        long_prefill = False
+        if shape.graphable:
+            if plan.n_items:
+                plan.context_bound = (max(plan.decode_pos) + 512) // 512 * 512
+            long_prefill = not shape.decode_shaped and any(n > 1 and end >= self.LONG_PREFILL
+                                                           for n, end in zip(shape.query_lens, shape.seq_lens))
+        plan.graph_key = (plan.context_bound, long_prefill)
+        plan.arrays = {}
+        if plan.n_items:
+            plan.arrays["items"] = plan.item_rows
+        if plan.n_tiles:
+            plan.arrays["tiles"] = np.asarray(plan.tile_rows, dtype=np.int64).reshape(-1)
+            plan.arrays["big_tiles"] = np.asarray(plan.big_rows, dtype=np.int64).reshape(-1)
+        return plan
 
     # ---- row-wise kernels ------------------------------------------------------------
     def embed(self, ids, table, out, scale: float = 1.0):
@@ -619,11 +655,18 @@ class Kernels:
         return out
 
     def sum_parts(self, parts, out):
-        """out = the sum over the first dimension of `parts` [splits, tokens, n] float32."""
+        """out = the sum over the first dimension of `parts` [splits, tokens, n] float32, added in split order."""
         _check(parts, "sum_parts.parts", torch.float32, 3)
+        _check(out, "sum_parts.out", tuple(DTYPE_CODE), 2)
         _need(tuple(parts.shape[1:]) == tuple(out.shape), "sum_parts: shapes do not fit")
-        torch.sum(parts, dim=0, out=out) if out.dtype == torch.float32 else out.copy_(torch.sum(parts, dim=0))
+        self._call("llm_sum_parts", _ptr(parts), _ptr(out), DTYPE_CODE[out.dtype], parts.shape[0], out.numel(), self._stream())
         return out
+
+    def scale_(self, x, scale: float):
+        """x *= scale, float32, in place."""
+        _check(x, "scale_.x", torch.float32)
+        self._call("llm_scale_f32", _ptr(x), float(scale), x.numel(), self._stream())
+        return x
 
     def gemm_pair(self, x, weight, out, swiglu: bool = False, tail_split: bool = True):
         """out = x . weight^T on this library's persistent CTA-pair tcgen05 kernel (many tokens).  With

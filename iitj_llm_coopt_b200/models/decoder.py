@@ -1,8 +1,10 @@
 """The generic decoder: embedding, the layers in their run order, final norm, output head.
 
-It is assembled from a `ModelSpec` alone.  Each layer's parts are looked up in the part
-registries by the `kind` of their spec record, so different layers of one model can have
-different mixers and feed-forwards; the run order (`spec.order`) is walked as data.
+It is assembled from a `ModelSpec` alone.  Each layer's arrangement declares the names and
+families of its parts; the parts are looked up in the registries by the `kind` of their spec
+record, so different layers of one model can have different arrangements, mixers and
+feed-forwards; embedding and head come from registries too; the run order (`spec.order`) is
+walked as data.
 Forward formulas in the reference's order: engine/model.py:181-213.
 """
 from __future__ import annotations
@@ -13,42 +15,58 @@ from .. import parts as P
 from ..parts.base import delta_for
 
 
-def _layer_part_classes(layer):
-    return {
-        "mixer_norm": (P.NORMS, layer.mixer_norm),
-        "mixer": (P.MIXERS, layer.mixer),
-        "feed_forward_norm": (P.NORMS, layer.feed_forward_norm),
-        "feed_forward": (P.FEED_FORWARDS, layer.feed_forward),
-    }
-
-
-def _lookup(registry, spec, what):
+def _lookup(family: str, spec, what: str):
+    registry = P.FAMILIES[family]
     if spec.kind not in registry:
         raise KeyError(f"{what} kind {spec.kind!r} is not registered; known: {', '.join(sorted(registry))}")
     return registry[spec.kind]
 
 
+def _arrangement(layer):
+    if layer.arrangement not in P.ARRANGEMENTS:
+        raise KeyError(f"arrangement {layer.arrangement!r} is not registered; known: {', '.join(sorted(P.ARRANGEMENTS))}")
+    return P.ARRANGEMENTS[layer.arrangement]
+
+
+def layer_parts(layer) -> list:
+    """[(part name, family, spec record, class)] of a layer, in the order its arrangement declares them."""
+    arr = _arrangement(layer)
+    names = set(layer.names())
+    if names != set(arr.PARTS):
+        raise KeyError(f"arrangement {layer.arrangement!r} is wired from {sorted(arr.PARTS)}, the layer gives {sorted(names)}")
+    if sum(1 for f in arr.PARTS.values() if f == "mixer") > 1:
+        raise ValueError(f"arrangement {layer.arrangement!r} declares more than one mixer (one cache entry per call)")
+    return [(name, family, layer.part(name), _lookup(family, layer.part(name), name)) for name, family in arr.PARTS.items()]
+
+
 def model_parameter_specs(spec) -> dict:
     """{parameter path: ParamSpec} of the whole model, without building anything."""
-    out = {"embedding.weight": P.Embedding.parameters(spec)["weight"]}
+    emb = spec.embedding_spec()
+    out = {f"embedding.{n}": ps for n, ps in _lookup("embedding", emb, "embedding").parameters(emb).items()}
     for i, layer in enumerate(spec.layers):
-        for part_name, (registry, part_spec) in _layer_part_classes(layer).items():
-            cls = _lookup(registry, part_spec, part_name)
+        for part_name, _family, part_spec, cls in layer_parts(layer):
             for pname, pspec in cls.parameters(part_spec).items():
                 out[f"layers.{i}.{part_name}.{pname}"] = pspec
-    for pname, pspec in _lookup(P.NORMS, spec.final_norm, "norm").parameters(spec.final_norm).items():
+    for pname, pspec in _lookup("norm", spec.final_norm, "norm").parameters(spec.final_norm).items():
         out[f"final_norm.{pname}"] = pspec
-    if not spec.tie_embeddings:
-        out["lm_head.weight"] = P.OutputHead.parameters(spec)["weight"]
+    head = spec.head_spec()
+    head_cls = _lookup("head", head, "head")
+    for pname, pspec in head_cls.parameters(head).items():
+        if spec.tie_embeddings and pname == getattr(head_cls, "tied_parameter", None):
+            continue                      # the embedding's table stands in
+        out[f"lm_head.{pname}"] = pspec
     return out
 
 
 def cache_needs(spec) -> list:
     """One CacheNeed per cache entry (indexed by LayerCall.cache of the writing call)."""
+    from ..config.specs import CacheNeed
     entries = {}
     for call in spec.order:
-        layer = spec.layers[call.layer]
-        need = _lookup(P.MIXERS, layer.mixer, "mixer").cache_need(layer.mixer)
+        need = CacheNeed()
+        for _name, family, part_spec, cls in layer_parts(spec.layers[call.layer]):
+            if family == "mixer":
+                need = cls.cache_need(part_spec)
         if call.write:
             if call.cache in entries and entries[call.cache] != need:
                 raise ValueError(f"cache entry {call.cache} is written by layers with different needs")
@@ -57,40 +75,53 @@ def cache_needs(spec) -> list:
         if call.cache not in entries:
             raise ValueError(f"run order reads cache entry {call.cache} that no call writes")
     n = max(entries) + 1 if entries else 0
-    from ..config.specs import CacheNeed
     return [entries.get(i, CacheNeed()) for i in range(n)]
+
+
+def build_part(family: str, part_spec, cls, kernels, dtype, device, name: str = ""):
+    """One part from its spec record.  A mixer is handed its position encoding, built from the spec's `position`.
+    `name` (the part's name in its arrangement) becomes `part.part_name`: parts that keep an output buffer in the
+    step's workspace name it after that, so that two parts of one class in one layer do not share a buffer."""
+    if family == "mixer":
+        pos = None
+        if getattr(part_spec, "position", None) is not None:
+            pos_cls = _lookup("position", part_spec.position, "position encoding")
+            pos = pos_cls(part_spec.position, kernels, dtype, device)
+        part = cls(part_spec, kernels, dtype, position=pos)
+    else:
+        part = cls(part_spec, kernels, dtype)
+    part.part_name = name
+    return part
 
 
 class DecoderModel:
     def __init__(self, spec, kernels, dtype, device="cuda"):
         self.spec, self.k, self.dtype, self.device = spec, kernels, dtype, device
-        self.embedding = P.Embedding(spec.vocab, spec.width, kernels, spec.embedding_scale)
+        emb = spec.embedding_spec()
+        self.embedding = build_part("embedding", emb, _lookup("embedding", emb, "embedding"), kernels, dtype, device)
         self.layers = []
         for layer in spec.layers:
-            built = {}
-            for part_name, (registry, part_spec) in _layer_part_classes(layer).items():
-                cls = _lookup(registry, part_spec, part_name)
-                if part_name == "mixer":
-                    pos = None
-                    if part_spec.position is not None:
-                        pos_cls = _lookup(P.POSITION_ENCODINGS, part_spec.position, "position encoding")
-                        pos = pos_cls(part_spec.position, kernels, dtype, device)
-                    built[part_name] = cls(part_spec, kernels, dtype, position=pos)
-                else:
-                    built[part_name] = cls(part_spec, kernels, dtype)
-            if layer.arrangement not in P.ARRANGEMENTS:
-                raise KeyError(f"arrangement {layer.arrangement!r} is not registered")
-            self.layers.append(P.ARRANGEMENTS[layer.arrangement](**built))
-        self.final_norm = _lookup(P.NORMS, spec.final_norm, "norm")(spec.final_norm, kernels, dtype)
-        self.head = P.OutputHead(spec.vocab, spec.width, kernels, spec.logit_scale)
+            built = {name: build_part(family, part_spec, cls, kernels, dtype, device, name)
+                     for name, family, part_spec, cls in layer_parts(layer)}
+            self.layers.append(_arrangement(layer)(**built))
+        self.final_norm = build_part("norm", spec.final_norm, _lookup("norm", spec.final_norm, "norm"), kernels, dtype, device,
+                                     "final_norm")
+        head = spec.head_spec()
+        self.head = build_part("head", head, _lookup("head", head, "head"), kernels, dtype, device)
+
+    def all_parts(self) -> list:
+        """Every part of the model, the parts that parts own included (each object once)."""
+        seen, out = set(), []
+        for part in [self.embedding] + [p for b in self.layers for p in b.all_parts()] + [self.final_norm, self.head]:
+            if id(part) not in seen:
+                seen.add(id(part))
+                out.append(part)
+        return out
 
     @property
     def graph_safe(self) -> bool:
         """True if every part only launches shape-determined work, so decode steps can be captured."""
-        mixers_ok = all(getattr(b.mixer.position, "graph_safe", True) for b in self.layers
-                        if getattr(b.mixer, "position", None) is not None)
-        return mixers_ok and all(getattr(b, "graph_safe", False) for b in self.layers) and \
-            self.embedding.graph_safe and self.final_norm.graph_safe and self.head.graph_safe
+        return all(getattr(p, "graph_safe", False) for p in self.all_parts())
 
     # ---- parameters ----------------------------------------------------------------------
     def load_parameters(self, params: dict) -> None:
@@ -105,16 +136,18 @@ class DecoderModel:
             per_part.setdefault(owner, {})[name] = t
         self.embedding.load(per_part["embedding"])
         self.final_norm.load(per_part["final_norm"])
-        self.head.load(per_part["lm_head"] if not self.spec.tie_embeddings
-                       else {"weight": per_part["embedding"]["weight"]})
+        head_params = dict(per_part.get("lm_head", {}))
+        tied = getattr(self.head, "tied_parameter", None)
+        if self.spec.tie_embeddings and tied is not None:
+            head_params[tied] = per_part["embedding"][tied]       # the head reads the embedding's table (engine/model.py:106)
+        self.head.load(head_params)
         for i, block in enumerate(self.layers):
             for part_name, part in block.parts().items():
                 part.load(per_part.get(f"layers.{i}.{part_name}", {}))
 
     def parameter_bytes(self) -> int:
         seen, total = set(), 0
-        for part in [self.embedding, self.final_norm, self.head] + \
-                [p for b in self.layers for p in b.parts().values()]:
+        for part in self.all_parts():
             for v in vars(part).values():
                 if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
                     seen.add(v.data_ptr())

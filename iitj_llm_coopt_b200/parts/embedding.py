@@ -14,8 +14,8 @@ from .base import ParamSpec, Part
 class Embedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab, width, kernels, scale=1.0):
-        self.vocab, self.width, self.k, self.scale = vocab, width, kernels, scale
+    def __init__(self, spec, kernels, dtype=None):
+        self.spec, self.vocab, self.width, self.k, self.scale = spec, spec.vocab, spec.width, kernels, spec.scale
         self.weight = None
 
     @classmethod
@@ -30,8 +30,10 @@ class Embedding(Part):
 class OutputHead(Part):
     graph_safe = True
 
-    def __init__(self, vocab, width, kernels, scale=1.0):
-        self.vocab, self.width, self.k, self.scale = vocab, width, kernels, scale
+    tied_parameter = "weight"     # the parameter that is the embedding's table when the model ties them
+
+    def __init__(self, spec, kernels, dtype=None):
+        self.spec, self.vocab, self.width, self.k, self.scale = spec, spec.vocab, spec.width, kernels, spec.scale
         self.weight = None
 
     @classmethod
@@ -42,5 +44,5 @@ class OutputHead(Part):
         logits = ctx.buffer("logits", (x.shape[0], self.vocab), torch.float32)
         self.k.linear(x, self.weight, logits)
         if self.scale != 1.0:
-            logits.mul_(self.scale)
+            self.k.scale_(logits, self.scale)
         return logits

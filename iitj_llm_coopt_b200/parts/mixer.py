@@ -19,6 +19,7 @@ from .base import ParamSpec, Part
 
 class PagedAttention(Part):
     graph_safe = True
+    prepare_key = "paged_attention"      # every attention layer of a model shares one plan of the step's tiles and items
 
     def __init__(self, spec, kernels, dtype, position):
         self.spec, self.k, self.dtype = spec, kernels, dtype
@@ -42,10 +43,23 @@ class PagedAttention(Part):
     def cache_need(cls, spec) -> CacheNeed:
         return CacheNeed(kind="paged_kv", kv_heads=spec.kv_heads, head_dim=spec.head_dim, window=spec.window)
 
+    def subparts(self) -> tuple:
+        return (self.position,) if self.position is not None else ()
+
+    def prepare_step(self, shape):
+        """The kernel set's plan of this step's attention work (which tokens are single decoded tokens, how prompt
+        portions are cut into query tiles, what a captured graph freezes of it); None for a kernel set that plans
+        nothing on the host."""
+        plan = getattr(self.k, "plan_attention", None)
+        return plan(shape) if plan is not None else None
+
     def forward(self, ctx, x, call):
         t = x.shape[0]
         group, view = ctx.cache.view(call.cache)
         meta = ctx.group(group)
+        plan = ctx.prepared.get(self.prepare_key)
+        if plan is not None:
+            meta.attention_plan = plan
         qkv = ctx.buffer("attn.qkv", (t, self.qkv_width), self.dtype)
         # a position encoding that says so takes the product's k-split partial sums and adds them as it reads
         qkv = self.k.linear(x, self.qkv, qkv, defer=getattr(self.position, "takes_partial_sums", False))

@@ -24,5 +24,5 @@ class RMSNorm(Part):
 
     def forward(self, ctx, residual, delta=None, rows=None):
         n = rows.shape[0] if rows is not None else residual.shape[0]
-        out = ctx.buffer("norm.out" if rows is None else "norm.rows", (n, self.width), self.dtype)
+        out = ctx.buffer(f"norm.{self.part_name}.out" if rows is None else f"norm.{self.part_name}.rows", (n, self.width), self.dtype)
         return self.k.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows=rows)

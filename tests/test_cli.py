@@ -140,7 +140,7 @@ def test_pool_sized_from_bytes_or_from_free_memory(model_dirs, how):
     cfg_d, seed, page = CONFIGS["A"]
     per_page = 2 * cfg_d["num_hidden_layers"] * cfg_d["num_key_value_heads"] * cfg_d["head_dim"] * page * 4   # float32
     if how == "kv_gb":
-        kv_gb = 300 * per_page / 2**30
+        kv_gb = (300 + 1) * per_page / 2**30              # (the storage holds one padding page beyond the pool)
         llm = LLM(model_dirs["A"], dtype="float32", page_size=page, kv_gb=kv_gb, max_num_seqs=4)
         assert llm.engine.cache.num_pages == 300
     else:

@@ -61,10 +61,13 @@ def test_model_spec_is_data():
     spec = arch.model_spec(LlamaConfig.from_dict(TINY_B))
     assert len(spec.layers) == 3 and [c.layer for c in spec.order] == [0, 1, 2]
     assert all(c.cache == i and c.write for i, c in enumerate(spec.order))
-    m = spec.layers[0].mixer
+    assert spec.layers[0].arrangement == "prenorm"
+    assert spec.layers[0].names() == ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
+    m = spec.layers[0].part("mixer")
     assert (m.kind, m.heads, m.kv_heads, m.head_dim, m.window) == ("attention", 3, 1, 32, 0)
     assert m.position.kind == "rope" and dict(m.position.scaling)["factor"] == 8.0
-    assert spec.layers[0].feed_forward.inner == 256 and spec.final_norm.eps == 1e-6
+    assert spec.layers[0].part("feed_forward").inner == 256 and spec.final_norm.eps == 1e-6
+    assert (spec.embedding_spec().kind, spec.head_spec().kind, spec.head_spec().vocab) == ("table", "linear", 320)
     needs = cache_needs(spec)
     assert len(needs) == 3 and all(n.kind == "paged_kv" and n.kv_heads == 1 and n.head_dim == 32 for n in needs)
     names = model_parameter_specs(spec)

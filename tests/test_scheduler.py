@@ -327,3 +327,21 @@ def test_lookahead_drops_the_token_computed_past_an_eos():
     assert eng.counters["generation_tokens_total"] == cut + 25
     cache.check()
     assert cache.num_free == 64
+
+
+def test_more_decodes_than_the_token_budget_take_turns():
+    """Seven sequences decode under a budget of three tokens a step: every one advances within three steps, and all
+    finish with the tokens they would have had alone."""
+    eng, runner, cache = make(pages=64, page=4, max_seqs=8, budget=3)
+    prompts = [prompt(i, 2) for i in range(7)]
+    seqs = [eng.new_sequence(p, 9, 0.0, True) for p in prompts]
+    while any(s.num_generated == 0 for s in seqs):          # prefill: three tokens a step
+        eng.step()
+    for _ in range(4):
+        before = [len(s.tokens) for s in seqs]
+        for _ in range(3):
+            eng.step()
+        assert all(len(s.tokens) > b or s.finished for s, b in zip(seqs, before))
+    eng.run_until_done()
+    assert [s.tokens[2:] for s in seqs] == [expected(p, 9) for p in prompts]
+    assert cache.num_free == 64

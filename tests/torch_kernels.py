@@ -169,6 +169,9 @@ class TorchKernels:
 
     health_codes = (0, 0, 0, 0)     # what `sample` reports as the library's health words (tests set a failure here)
 
+    def scale_(self, x, scale):
+        return x.mul_(scale)
+
     def sample(self, logits, temperature, keys, out, health=None):
         ids, _ = ref_sample(logits, temperature, keys)
         out.copy_(ids)
