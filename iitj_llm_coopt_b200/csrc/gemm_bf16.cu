@@ -401,6 +401,29 @@ LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, 
     return 0;
 }
 
+// ---- a wait that runs out, on purpose (tests) ---------------------------------------------------------------
+// One thread sets up an mbarrier that nobody will ever arrive on and waits for it with the kernels' own bounded
+// wait, cut to `polls` polls; when the wait gives up it records code 7 in the status word, exactly as a product's
+// CTA records its code, and the kernel returns.  No copy and no MMA is in flight and no tensor memory is held, so
+// there is nothing to clean up: the kernel shows what the host sees of a wait that ran out.
+namespace {
+__global__ void wait_probe_kernel(uint32_t polls) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mbar_wait(&bar, 0, polls)) give_up(7);
+    }
+}
+}  // namespace
+
+LLM_API int llm_gemm_bf16_wait_probe(int polls, cudaStream_t stream) {
+    if (polls < 1 || polls > (1 << 16)) LLM_FAIL(-1, "gemm_bf16_wait_probe: 1 to 65536 polls");
+    wait_probe_kernel<<<1, 32, 0, stream>>>((uint32_t)polls);
+    LLM_CHECK_LAUNCH("gemm_bf16_wait_probe");
+    return 0;
+}
+
 const int* llm_gemm_bf16_status_word() {
     void* p = nullptr;
     return cudaGetSymbolAddress(&p, g_status) == cudaSuccess ? static_cast<const int*>(p) : nullptr;

@@ -69,6 +69,7 @@ _SIGNATURES = {
     "llm_gemm_bf16": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                       _c_int, _c_int, _c_int, _c_void_p],
     "llm_gemm_bf16_status": [],
+    "llm_gemm_bf16_wait_probe": [_c_int, _c_void_p],
     "llm_gemm_bf16_pair": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                            _c_void_p, _c_void_p],
     "llm_gemm_bf16_pair_scratch": [_c_int],
@@ -296,6 +297,15 @@ class Kernels:
             self._scratch_bufs[(name, device)] = buf
             self.scratch_generation += 1
         return buf
+
+    def _scratch_bf16(self, name, elements, device):
+        """Grow-only bfloat16 scratch (grown to powers of two, so that token counts that creep up reallocate rarely)."""
+        buf = self._scratch_bufs.get((name, device))
+        if buf is None or buf.numel() < elements:
+            buf = torch.empty(1 << max(elements - 1, 1 << 16).bit_length(), dtype=torch.bfloat16, device=device)
+            self._scratch_bufs[(name, device)] = buf
+            self.scratch_generation += 1
+        return buf[:elements]
 
     # ---- plumbing --------------------------------------------------------------------
     def _call(self, name, *args):
@@ -621,7 +631,9 @@ class Kernels:
         if policy == "pair":
             return self.gemm_pair(x, weight, out, swiglu)
         if swiglu:
-            gu = torch.mm(x, weight.t())
+            # the [tokens, 2 * inner] intermediate lives in this library's grow-only scratch: a step allocates nothing
+            gu = self._scratch_bf16("gemm.gate_up", tokens * weight.shape[0], x.device).view(tokens, weight.shape[0])
+            torch.mm(x, weight.t(), out=gu)
             return self.silu_mul(gu, out)
         if out.dtype == torch.float32:
             torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
@@ -737,6 +749,12 @@ class Kernels:
     def gemm_status(self) -> int:
         """0, or a code if a tcgen05 GEMM gave up waiting on one of its barriers since the last call."""
         return self.lib.llm_gemm_bf16_status()
+
+    def wait_probe(self, polls: int = 2000) -> None:
+        """Launches a kernel whose only act is a bounded wait that runs out after `polls` polls (an mbarrier nobody
+        arrives on; nothing else is in flight); it leaves code 7 in the tcgen05 product's status word.  For tests of
+        what the host makes of a kernel that gave up."""
+        self._call("llm_gemm_bf16_wait_probe", int(polls), self._stream())
 
     def gemm_pair_status(self) -> int:
         """0, or a code if the CTA-pair GEMM gave up waiting on one of its barriers since the last call."""

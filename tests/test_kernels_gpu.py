@@ -593,3 +593,27 @@ def test_attention_decode_fused_is_refused_for_mixed_steps(K):
     qkv = PartialSums(K, parts, torch.zeros(6, 8 * 128, device="cuda", dtype=torch.bfloat16))
     assert not K.can_fuse_decode(qkv, meta, cache, 4, 2, 128)
     assert not K.can_fuse_decode(qkv.out, meta, cache, 4, 2, 128)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_library_goes_on(K):
+    """A bounded wait that gives up: the status word says which code, the sampler refuses to hand out tokens that
+    were computed while a kernel had given up, and the next ordinary product is right again."""
+    from iitj_llm_coopt_b200.kernels import KernelError
+    from iitj_llm_coopt_b200.sampling import Sampler
+    K.check_health()
+    K.wait_probe(2000)
+    torch.cuda.synchronize()
+    code = K.gemm_status()
+    assert code >> 16 == 7 and K.gemm_status() == 0           # read once, then clear
+    # the same through the path serving takes: the word travels with the sampled ids
+    K.wait_probe(500)
+    sampler = Sampler(K, 0, "cuda")
+    logits = rnd((3, 1000), torch.float32, 400)
+    with pytest.raises(KernelError, match="gave up"):
+        sampler.sample(logits, [(0.0, 0, 0)] * 3)
+    assert sampler.sample(logits, [(0.0, 0, 0)] * 3) == logits.argmax(-1).tolist()    # cleared by the report
+    x, w = rnd((8, 512), torch.bfloat16, 401), rnd((256, 512), torch.bfloat16, 402, 0.05)
+    out = torch.empty(8, 256, device="cuda", dtype=torch.bfloat16)
+    K.gemm_tcgen05(x, w, out)
+    close(out, R.ref_linear(x, w), torch.bfloat16)
+    K.check_health()

@@ -405,10 +405,12 @@ def test_a_layer_of_five_parts_is_described_and_built(device, dtype):
         for steps in (cases.portions(reqs), cases.mixed(reqs, live=3, seed=2)[0]):
             rows = run_steps(eng, steps)
             assert max(rel_err(rows[k], whole[k]) for k in whole) <= tol
-        # the fifth part does something: with its gains doubled the logits move
-        block.mixer_post_norm.weight.mul_(2.0)
+        # the fifth part does something: with its gains turned round and tripled the logits move
+        block.mixer_post_norm.weight.mul_(-3.0)
         moved = run_steps(eng, cases.whole({"r1": reqs["r1"]}))
-        assert rel_err(moved[("r1", 20)], whole[("r1", 20)]) > 10 * tol
+        effect = rel_err(moved[("r1", 20)], whole[("r1", 20)])
+        print("effect of the fifth part:", effect)
+        assert effect > 0.1
     finally:
         parts.ARRANGEMENTS.pop("postnorm", None)
 
