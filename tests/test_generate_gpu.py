@@ -284,3 +284,39 @@ def test_lookahead_changes_no_token(lively_dirs, name, dtype):
         assert any(reason == "stop" for _, reason in runs[keys[0]])
     finally:
         shutil.rmtree(d)
+
+
+def test_captured_decode_steps_follow_a_context_that_outgrows_their_bounds(tmp_path):
+    """Decoding from 450 to 1100 tokens of context with captured graphs on tiny D (head size 128): the split choice of
+    the decode attention is frozen in a graph by an upper bound of the context (steps of 512 tokens), so the graph has
+    to be captured anew when the context passes 512 and 1024, with several key splits and their merge inside the
+    graph from then on.  The queries of this model are scaled up so that attention is peaked: keys left out by a
+    stale split would move the logits.  Every decoded position is compared with the plain implementation and with
+    the same engine without graphs."""
+    from safetensors.torch import load_file, save_file
+    from helpers import make_engine, rel_err, run_steps
+    cfg_d, seed, page = CONFIGS["D"]
+    d = str(tmp_path / "peaked")
+    write_model_dir(cfg_d, d, seed)
+    tensors = load_file(os.path.join(d, "model.safetensors"))
+    for name in tensors:
+        if name.endswith("q_proj.weight"):
+            tensors[name] = (tensors[name].float() * 12.0).to(tensors[name].dtype)
+    save_file(tensors, os.path.join(d, "model.safetensors"), metadata={"format": "pt"})
+    total, head = 1100, 450
+    reqs = cases.requests_for(cfg_d["vocab_size"], [total], seed + 70)
+    cfg, w = plain.read_model_dir(d, torch.float32)
+    ref = plain.forward(cfg, w, reqs["r0"])
+    steps = cases.last_one_by_one(reqs, tail=total - head)
+    rows = {}
+    for graphs in (True, False):
+        eng = make_engine(d, "bfloat16", page, -(-total // page) + 2, max_num_seqs=2, cuda_graphs=graphs)
+        rows[graphs] = run_steps(eng, steps)
+        if graphs:
+            runner = eng.runner
+            assert runner.graph_captures >= 3 and runner.graph_replays > 500      # bounds 512, 1024 and 1536
+        del eng
+    got = torch.stack([rows[True][("r0", i)] for i in range(total)])
+    eager = torch.stack([rows[False][("r0", i)] for i in range(total)])
+    assert rel_err(got, ref) <= 2e-2
+    assert rel_err(got[head:], eager[head:]) <= 5e-3          # same kernels, the splits chosen from a bound: rounding only
