@@ -73,43 +73,99 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
         ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// Packed float32 pairs (sm_100: one instruction multiplies-and-adds, or adds, two values) and the three-input maximum:
+// they halve the instruction count of the softmax's arithmetic, which shares its issue slots with the exponentials.
+__device__ __forceinline__ unsigned long long pair_of(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ unsigned long long pair_of_bits(uint32_t lo, uint32_t hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void split_pair(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_pair(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ unsigned long long add_pair(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 // Maximum of 32 scores (keys k0 .. k0+31) with four independent chains.
 template <bool MASK>
 __device__ __forceinline__ float chunk_max(const uint32_t (&r)[32], int k0, int row_pos, int row_lo, float mx) {
     float m0 = mx, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+    if constexpr (!MASK) {
 #pragma unroll
-    for (int c = 0; c < 32; c += 4) {
-        float a0 = __uint_as_float(r[c]), a1 = __uint_as_float(r[c + 1]), a2 = __uint_as_float(r[c + 2]), a3 = __uint_as_float(r[c + 3]);
-        if (MASK) {
+        for (int c = 0; c < 32; c += 8) {
+            m0 = max3(m0, __uint_as_float(r[c]), __uint_as_float(r[c + 1]));
+            m1 = max3(m1, __uint_as_float(r[c + 2]), __uint_as_float(r[c + 3]));
+            m2 = max3(m2, __uint_as_float(r[c + 4]), __uint_as_float(r[c + 5]));
+            m3 = max3(m3, __uint_as_float(r[c + 6]), __uint_as_float(r[c + 7]));
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+            float a0 = __uint_as_float(r[c]), a1 = __uint_as_float(r[c + 1]), a2 = __uint_as_float(r[c + 2]), a3 = __uint_as_float(r[c + 3]);
             const int key = k0 + c;
             if (key > row_pos || key < row_lo) a0 = -INFINITY;
             if (key + 1 > row_pos || key + 1 < row_lo) a1 = -INFINITY;
             if (key + 2 > row_pos || key + 2 < row_lo) a2 = -INFINITY;
             if (key + 3 > row_pos || key + 3 < row_lo) a3 = -INFINITY;
+            m0 = fmaxf(m0, a0); m1 = fmaxf(m1, a1); m2 = fmaxf(m2, a2); m3 = fmaxf(m3, a3);
         }
-        m0 = fmaxf(m0, a0); m1 = fmaxf(m1, a1); m2 = fmaxf(m2, a2); m3 = fmaxf(m3, a3);
     }
     return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
-// P = 2^(S * sl - mu) of 32 scores, packed as 16 columns of two bfloat16; adds to four partial sums.
+// P = 2^(S * sl - mu) of 32 scores, packed as 16 columns of two bfloat16; adds to four partial sums (sum[i] takes the
+// keys i, i + 4, ... of the chunk in both forms, so a row's sum does not depend on whether its tile was masked).
 template <bool MASK>
 __device__ __forceinline__ void chunk_exp(const uint32_t (&r)[32], uint32_t (&packed)[16], float sl, float mu, int k0, int row_pos,
                                           int row_lo, float (&sum)[4]) {
+    if constexpr (!MASK) {
+        const unsigned long long sl2 = pair_of(sl, sl), nmu2 = pair_of(-mu, -mu);
+        unsigned long long s01 = pair_of(sum[0], sum[1]), s23 = pair_of(sum[2], sum[3]);
 #pragma unroll
-    for (int c = 0; c < 32; c += 4) {
-        float p0 = ex2(fmaf(__uint_as_float(r[c]), sl, -mu)), p1 = ex2(fmaf(__uint_as_float(r[c + 1]), sl, -mu));
-        float p2 = ex2(fmaf(__uint_as_float(r[c + 2]), sl, -mu)), p3 = ex2(fmaf(__uint_as_float(r[c + 3]), sl, -mu));
-        if (MASK) {
+        for (int c = 0; c < 32; c += 4) {
+            float x0, x1, x2, x3;
+            split_pair(fma_pair(pair_of_bits(r[c], r[c + 1]), sl2, nmu2), x0, x1);
+            split_pair(fma_pair(pair_of_bits(r[c + 2], r[c + 3]), sl2, nmu2), x2, x3);
+            const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(x2), p3 = ex2(x3);
+            s01 = add_pair(s01, pair_of(p0, p1));
+            s23 = add_pair(s23, pair_of(p2, p3));
+            packed[c >> 1] = pack2(p0, p1);
+            packed[(c >> 1) + 1] = pack2(p2, p3);
+        }
+        split_pair(s01, sum[0], sum[1]);
+        split_pair(s23, sum[2], sum[3]);
+    } else {
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+            float p0 = ex2(fmaf(__uint_as_float(r[c]), sl, -mu)), p1 = ex2(fmaf(__uint_as_float(r[c + 1]), sl, -mu));
+            float p2 = ex2(fmaf(__uint_as_float(r[c + 2]), sl, -mu)), p3 = ex2(fmaf(__uint_as_float(r[c + 3]), sl, -mu));
             const int key = k0 + c;
             if (key > row_pos || key < row_lo) p0 = 0.f;
             if (key + 1 > row_pos || key + 1 < row_lo) p1 = 0.f;
             if (key + 2 > row_pos || key + 2 < row_lo) p2 = 0.f;
             if (key + 3 > row_pos || key + 3 < row_lo) p3 = 0.f;
+            sum[0] += p0; sum[1] += p1; sum[2] += p2; sum[3] += p3;
+            packed[c >> 1] = pack2(p0, p1);
+            packed[(c >> 1) + 1] = pack2(p2, p3);
         }
-        sum[0] += p0; sum[1] += p1; sum[2] += p2; sum[3] += p3;
-        packed[c >> 1] = pack2(p0, p1);
-        packed[(c >> 1) + 1] = pack2(p2, p3);
     }
 }
 
