@@ -541,6 +541,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
 // All loads of a thread are asked for at once (the partial results of every possible split, and the position
 // that tells how many of them count): the kernel is one round trip to memory long instead of four.
 constexpr int kMergeSplits = 16;
+constexpr int kMaxMergeSplits = 1024;          // most key splits of one item (the merge keeps their maxima and sums in shared memory)
 
 template <int D>
 __global__ void __launch_bounds__(D)
@@ -582,10 +583,32 @@ attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
             }
         }
     } else {
-        for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-        for (int s = 0; s < n_splits; ++s) {
-            const float f = exp2f(part_ml[(base + s) * 2] - M);
-            L += part_ml[(base + s) * 2 + 1] * f;
+        // Many splits (a single request with a long context): the splits' maxima and sums go through shared memory
+        // once (one split per thread), every thread then weighs its dim of the partial outputs, eight loads at a time.
+        __shared__ float sm_w[kMaxMergeSplits], sm_l[kMaxMergeSplits];
+        float M_all = -INFINITY;
+        for (int s0 = 0; s0 < n_splits; s0 += D) {              // (n_splits <= kMaxMergeSplits, checked by the launcher)
+            const int sidx = s0 + d;
+            if (sidx < n_splits) { sm_w[sidx] = part_ml[(base + sidx) * 2]; sm_l[sidx] = part_ml[(base + sidx) * 2 + 1]; }
+        }
+        __syncthreads();
+        for (int s = 0; s < n_splits; ++s) M_all = fmaxf(M_all, sm_w[s]);
+        M = M_all;
+        int s = 0;
+        for (; s + 8 <= n_splits; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = part_o[(base + s + i) * D + d];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float f = exp2f(sm_w[s + i] - M);
+                L += sm_l[s + i] * f;
+                O += v[i] * f;
+            }
+        }
+        for (; s < n_splits; ++s) {
+            const float f = exp2f(sm_w[s] - M);
+            L += sm_l[s] * f;
             O += part_o[(base + s) * D + d] * f;
         }
     }
@@ -703,7 +726,8 @@ int launch_decode(const void* q, int q_stride, const void* cache, const int* blo
     if (!llm_attention_bf16_supported(heads, kv_heads, head_dim))
         LLM_FAIL(-1, "attention_decode_bf16: heads %d / kv_heads %d / head_dim %d not supported", heads, kv_heads, head_dim);
     if (keys_per_split <= 0 || keys_per_split % kTile) LLM_FAIL(-1, "attention_decode_bf16: keys_per_split must be a multiple of 64");
-    if (max_splits < 1 || kv_heads > 65535 || n_items > 65535) LLM_FAIL(-1, "attention_decode_bf16: grid out of range");
+    if (max_splits < 1 || max_splits > kMaxMergeSplits || kv_heads > 65535 || n_items > 65535)
+        LLM_FAIL(-1, "attention_decode_bf16: grid out of range (1 to %d splits, at most 65535 items and key/value heads)", kMaxMergeSplits);
     if (max_splits > 1 && (!part_o || !part_ml)) LLM_FAIL(-1, "attention_decode_bf16: scratch is missing");
     const float sl = scale * 1.4426950408889634f;
     const int page_shift = page_shift_of(page_size);

@@ -161,6 +161,7 @@ class AttentionPlan:
 
     TILE = 64
     SPLIT_RULE = os.environ.get("IITJ_DECODE_SPLIT", "auto")    # "equal": always the rule for equal contexts (measurements)
+    FORCE_KPS = int(os.environ.get("IITJ_DECODE_KPS", "0"))     # keys per split, whatever the rule says (measurements)
 
     def __init__(self, query_lens, seq_lens, device, items=None, tiles=None, total_tokens=None):
         self.decode_pos = []
@@ -238,6 +239,8 @@ class AttentionPlan:
                 scored.append((cost, kps))
             least = min(c for c, _ in scored)
             kps = next(k for c, k in scored if c <= (least if equal else 1.05 * least))
+            if self.FORCE_KPS:
+                kps = self.FORCE_KPS
             self._splits[key] = (kps, max((s - 1) // kps + 1 for s in ([longest] if bound is not None else spans)))
         return self._splits[key]
 
