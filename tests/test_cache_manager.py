@@ -148,3 +148,70 @@ def test_random_orders_never_lose_or_share_a_page(seed, geometry, windowed):
         cm.release(r)
     cm.check()
     assert cm.num_free == pages and len(cm.free_slots) == 4
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(0, 2**32 - 1), st.sampled_from([(4, 40, 12), (8, 30, 24), (16, 12, 16)]))
+def test_pools_of_their_own_size_and_the_questions_the_scheduler_asks(seed, geometry):
+    """A group with a window gets a pool sized for windows and one step's tokens; `can_admit` and `can_grow_all` must
+    say exactly what `ensure` then does, group by group, under random orders of requests whose steps stay within
+    the declared bound."""
+    page, pages, step_tokens = geometry
+    needs = [FULL, WIN, FULL]
+    cm = CacheManager(needs, page_size=page, num_pages=pages, max_requests=3, max_step_tokens=step_tokens)
+    g_full, g_win = cm.entry_group[0][0], cm.entry_group[1][0]
+    sizes = {g: cm.groups[g].pool.num_pages for g in cm.paged}
+    assert sizes[g_full] == pages
+    assert sizes[g_win] == min(pages, 3 * (-(-WIN.window // page) + 2) + -(-step_tokens // page) + 3)
+    assert CacheManager.bytes_for(needs, page, pages, 2, 3, step_tokens) == \
+        2 * (2 * FULL.kv_heads * FULL.head_dim * page * 2) * (pages + 1) + (2 * WIN.kv_heads * WIN.head_dim * page * 2) * (sizes[g_win] + 1)
+    rng = random.Random(seed)
+    live, next_id = {}, 0
+    for _ in range(150):
+        op = rng.random()
+        if op < 0.3 and len(live) < 3:
+            first = rng.randint(1, step_tokens)
+            fits = all(cm.groups[g].pages_for(first) <= cm.groups[g].pool.num_free for g in cm.paged)
+            assert cm.can_admit(first) == fits
+            if fits:
+                cm.admit(next_id)
+                cm.ensure(next_id, first)
+                cm.advance(next_id, first)
+                live[next_id] = first
+                next_id += 1
+        elif op < 0.85 and live:
+            # one step: some of the live requests grow, together by no more than the step's bound
+            grow, left = [], step_tokens
+            for r in rng.sample(list(live), rng.randint(1, len(live))):
+                n = rng.randint(1, max(1, min(left, page + 3)))
+                if n > left:
+                    break
+                grow.append((r, live[r] + n))
+                left -= n
+            need = {g: sum(cm.groups[g].extra_pages(r, t) for r, t in grow) for g in cm.paged}
+            fits = all(need[g] <= cm.groups[g].pool.num_free for g in cm.paged)
+            assert cm.can_grow_all(grow) == fits
+            if fits:
+                for r, t in grow:
+                    cm.ensure(r, t)
+                for r, t in grow:
+                    cm.advance(r, t)
+                    live[r] = t
+            else:
+                victim = rng.choice(list(live))
+                cm.release(victim)
+                del live[victim]
+        elif live:
+            r = rng.choice(list(live))
+            cm.release(r)
+            del live[r]
+        cm.check()
+        for g in cm.paged:
+            held = sum(1 for r in live for p in cm.table(g, r) if p >= 0)
+            assert held + cm.groups[g].pool.num_free == sizes[g]
+        # the windowed group never holds more than its windows and the last step's tokens
+        assert sizes[g_win] - cm.groups[g_win].pool.num_free <= 3 * (-(-WIN.window // page) + 2) + -(-step_tokens // page) + 3
+    for r in list(live):
+        cm.release(r)
+    cm.check()
+    assert all(cm.groups[g].pool.num_free == sizes[g] for g in cm.paged)
