@@ -14,10 +14,11 @@
 //   SWIGLU    W holds gate rows then up rows; the CTA keeps two accumulators (gate, up) for
 //             the same 128 features and writes silu(gate) * up (engine/model.py:210-211,
 //             251-252), so the [T, 2I] intermediate is never written.
-//   HALF      the SwiGLU product of at most 16 tokens: the 128 MMA rows are 64 gate rows and the 64 up rows
-//             of the same features (two TMA boxes per stage), one accumulator; the epilogue warps that hold
-//             the up rows hand them to the warps with the gate rows through shared memory.  Twice as many
-//             CTAs as the form above, so the k range needs no split and no kernel adds partial sums.
+//   HALF      the SwiGLU product of at most 128 tokens (one token tile): the 128 MMA rows are 64 gate rows and
+//             the 64 up rows of the same features (two TMA boxes per stage), one accumulator; the epilogue
+//             warps that hold the up rows hand them to the warps with the gate rows through shared memory,
+//             16 tokens at a time.  Twice as many CTAs as the form above, two of them per SM, so the k range
+//             needs no split and no kernel adds partial sums.
 //   split-K   when a product has too few tiles to fill the GPU, the k range is split over
 //             CTAs; partial sums go to float32 scratch and splitk_reduce_kernel adds them in
 //             split order (and applies SwiGLU, or rounds to bfloat16), unless the caller leaves the
@@ -59,7 +60,7 @@ struct GemmArgs {
 template <int N_TOK, bool SWIGLU, bool HALF = false>
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs a) {
-    static_assert(!HALF || (SWIGLU && N_TOK == 16), "the half-tile form is the SwiGLU product of at most 16 tokens");
+    static_assert(!HALF || (SWIGLU && N_TOK <= 128), "the half-tile form is the SwiGLU product of one token tile of at most 128");
     constexpr int kABytes = kFeatTile * kBlockK * 2;               // 16 KiB per weight tile
     constexpr int kBBytes = N_TOK * kBlockK * 2;
     constexpr int kWTiles = (SWIGLU && !HALF) ? 2 : 1;             // weight tiles (and accumulators) per stage
@@ -147,30 +148,36 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int feat = feat0 + quarter * 32 + lane;
         pdl_wait();                               // nothing is stored before the previous kernel has finished
         if constexpr (HALF) {
-            // lanes 0-63 of the accumulator are gate rows, lanes 64-127 the up rows of the same 64 features
-            __shared__ float up_rows[N_TOK * (kFeatTile / 2)];
+            // lanes 0-63 of the accumulator are gate rows, lanes 64-127 the up rows of the same 64 features: per 16
+            // tokens the upper two warps hand their values over through one of two buffers, the lower two finish
+            __shared__ float up_rows[2][16 * (kFeatTile / 2)];
             const bool ok = n_kb > 0 && mbar_wait(&accum_bar, 0) && !failed;
             if (!ok && n_kb > 0 && !failed) give_up(3);
-            uint32_t g[16];
             const int f = (quarter & 1) * 32 + lane;              // feature of this lane inside the tile
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16), g);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (quarter >= 2) {
+            if (ok) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int c0 = 0; c0 < N_TOK; c0 += 16) {
+                uint32_t g[16];
+                float* hand = up_rows[(c0 >> 4) & 1];
+                const bool live = ok && tok0 + c0 < a.tokens;
+                if (live) {
+                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, g);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (quarter >= 2) {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) up_rows[c * (kFeatTile / 2) + f] = __uint_as_float(g[c]);
+                        for (int c = 0; c < 16; ++c) hand[c * (kFeatTile / 2) + f] = __uint_as_float(g[c]);
+                    }
                 }
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps, whatever happened above
-            if (ok && quarter < 2 && feat0 + f < a.n_feat) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps, whatever happened above
+                if (live && quarter < 2 && feat0 + f < a.n_feat) {
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const int tok = tok0 + c;
-                    if (tok >= a.tokens) break;
-                    const float gv = __uint_as_float(g[c]);
-                    const float v = gv / (1.0f + expf(-gv)) * up_rows[c * (kFeatTile / 2) + f];
-                    ((bf16*)a.out)[(size_t)tok * a.ldc + feat0 + f] = __float2bfloat16_rn(v);
+                    for (int c = 0; c < 16; ++c) {
+                        const int tok = tok0 + c0 + c;
+                        if (tok >= a.tokens) break;
+                        const float gv = __uint_as_float(g[c]);
+                        const float v = gv / (1.0f + expf(-gv)) * hand[c * (kFeatTile / 2) + f];
+                        ((bf16*)a.out)[(size_t)tok * a.ldc + feat0 + f] = __float2bfloat16_rn(v);
+                    }
                 }
             }
         } else
@@ -339,7 +346,7 @@ LLM_API int llm_gemm_bf16_token_tile(int tokens) {
 // unless `defer` is set: then the partial sums [splits][tokens][n] stay in scratch for the kernel that reads
 // the result (llm_add_rmsnorm, llm_rope_store) and `out` is not written.
 // smem_kb: shared memory of one CTA's ring in KiB (0 = 200: one CTA per SM; about 100 lets two CTAs share an SM).
-// half: the SwiGLU product of at most 16 tokens with 64 gate and 64 up rows per CTA (n % 64 == 0, no split).
+// half: the SwiGLU product of at most 128 tokens with 64 gate and 64 up rows per CTA (n % 64 == 0, no split).
 LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, int tokens, int n, int K, int ldc,
                           int swiglu, int splits, float* scratch, int smem_kb, int defer, int half, cudaStream_t stream) {
     if (tokens == 0 || n == 0) return 0;
@@ -352,8 +359,8 @@ LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, 
     if (splits > 1 && (n % 4)) LLM_FAIL(-1, "gemm_bf16: split-K needs n %% 4 == 0");
     const int w_rows = swiglu ? 2 * n : n;
     const int tile = llm_gemm_bf16_token_tile(tokens);
-    if (half && (!swiglu || tile != 16 || n % (kFeatTile / 2) || splits != 1))
-        LLM_FAIL(-1, "gemm_bf16: the half-tile form is the unsplit SwiGLU product of at most 16 tokens with n %% 64 == 0");
+    if (half && (!swiglu || tile > 128 || n % (kFeatTile / 2) || splits != 1))
+        LLM_FAIL(-1, "gemm_bf16: the half-tile form is the unsplit SwiGLU product of at most 128 tokens with n %% 64 == 0");
     CUtensorMap mw, mx;
     if (int rc = llm_tensor_map_2d(w, w_rows, K, half ? kFeatTile / 2 : kFeatTile, kBlockK, &mw)) return rc;
     if (int rc = llm_tensor_map_2d(x, tokens, K, tile, kBlockK, &mx)) return rc;
@@ -371,8 +378,12 @@ LLM_API int llm_gemm_bf16(const void* x, const void* w, void* out, int out_f32, 
     if (grid.y > 65535 || grid.z > 65535) LLM_FAIL(-1, "gemm_bf16: grid out of range");
     int rc;
     if (half) {
-        rc = launch_tile<16, true, true>(mw, mx, a, grid, stream);
-        return rc;
+        switch (tile) {
+            case 16: return launch_tile<16, true, true>(mw, mx, a, grid, stream);
+            case 32: return launch_tile<32, true, true>(mw, mx, a, grid, stream);
+            case 64: return launch_tile<64, true, true>(mw, mx, a, grid, stream);
+            default: return launch_tile<128, true, true>(mw, mx, a, grid, stream);
+        }
     }
 #define LLM_GEMM_CASE(T)                                                                       \
     case T: rc = swiglu ? launch_tile<T, true>(mw, mx, a, grid, stream) : launch_tile<T, false>(mw, mx, a, grid, stream); break;

@@ -272,7 +272,7 @@ class Kernels:
         self.gemm_plain_tokens = int(os.environ.get("IITJ_GEMM_PLAIN_TOKENS", "128"))   # plain products: tcgen05 up to here
         self.gemm_pair_mode = os.environ.get("IITJ_GEMM_PAIR", "swiglu")   # off | swiglu | all
         self.defer_sums = os.environ.get("IITJ_DEFER_SUMS", "1") == "1"     # k-split sums added by the reading kernel
-        self.swiglu_half_tokens = int(os.environ.get("IITJ_SWIGLU_HALF_TOKENS", "8"))   # half-tile SwiGLU product up to here
+        self.swiglu_half_tokens = int(os.environ.get("IITJ_SWIGLU_HALF_TOKENS", "64"))  # half-tile SwiGLU product up to here
         self.swiglu_half_smem_kb = int(os.environ.get("IITJ_SWIGLU_HALF_KB", "100"))
         self.fuse_decode = os.environ.get("IITJ_FUSE_DECODE", "1") != "0"   # rope + cache write inside decode attention
         self.attention_splits = os.environ.get("IITJ_ATTN_SPLITS")         # forces the key splits of prefill attention
@@ -617,7 +617,11 @@ class Kernels:
             policy = self.gemm_policy(tokens, n, k, swiglu)
             if policy == "tcgen05":
                 if swiglu and tokens <= self.swiglu_half_tokens and n % 64 == 0:
-                    # a handful of tokens: 64 gate + 64 up rows per CTA, twice the CTAs, no k-split and no kernel after it
+                    # decode batches: 64 gate + 64 up rows per CTA, twice the CTAs (two per SM), no k-split and no kernel
+                    # after it.  Against the whole tile (128 + 128 rows, one CTA per SM, 112 CTAs at the 8B shape) a decode
+                    # step at 4096-token contexts: batch 16 / 32 at the 8B shape 4.61 -> 4.57 / 5.98 -> 5.93 ms, batch 32 / 64
+                    # at the 3B shape 4.43 -> 4.31 / 7.54 -> 7.42 ms, at the 1B shape 1.97 -> 1.88 / 3.11 -> 3.03 ms; level at
+                    # batch 64 of the 8B shape and at batch 128, where the whole tile stays
                     plan = ("tcgen05", 1, self.swiglu_half_smem_kb, True)
                 else:
                     plan = ("tcgen05",) + tuple(self.gemm_plan(tokens, n, k, swiglu)) + (False,)
@@ -648,7 +652,7 @@ class Kernels:
                      half: bool = False):
         """out = x . weight^T on this library's tcgen05 kernel (bfloat16 in, bfloat16 or float32 out).  With `defer`
         and more than one split the partial sums are returned as a PartialSums instead of being added here.
-        `half`: the SwiGLU product of at most 16 tokens with 64 gate and 64 up rows per CTA (unsplit, n % 64 == 0)."""
+        `half`: the SwiGLU product of at most 128 tokens with 64 gate and 64 up rows per CTA (unsplit, n % 64 == 0)."""
         _check(x, "gemm.x", torch.bfloat16, 2)
         _check(weight, "gemm.weight", torch.bfloat16, 2)
         _check(out, "gemm.out", (torch.bfloat16, torch.float32), 2)
@@ -732,8 +736,8 @@ class Kernels:
 
         Products with many feature tiles (the LM head) run unsplit with three CTAs per SM.  Products with
         few tiles are split along k until about two CTAs per SM are in flight (at most eight splits, at
-        least four k-blocks each).  The SwiGLU product beyond a handful of tokens runs unsplit with the
-        whole shared memory as its ring."""
+        least four k-blocks each).  The SwiGLU product beyond the half-tile form's token count (see linear) runs
+        unsplit with the whole shared memory as its ring."""
         tile = self.lib.llm_gemm_bf16_token_tile(tokens)
         tiles = -(-n // 128) * -(-tokens // tile)
         k_blocks = -(-k // 64)

@@ -437,9 +437,12 @@ def test_gemm_tcgen05_swiglu(K, tokens, n, k, splits):
     assert K.gemm_status() == 0
 
 
-@pytest.mark.parametrize("tokens,n,k", [(1, 64, 64), (8, 192, 1024), (16, 448, 4104), (5, 1024, 200), (3, 14336, 4096)])
+@pytest.mark.parametrize("tokens,n,k", [(1, 64, 64), (8, 192, 1024), (16, 448, 4104), (5, 1024, 200), (3, 14336, 4096),
+                                        (17, 192, 264), (31, 448, 1024), (33, 64, 4104), (50, 1024, 200), (64, 14336, 4096),
+                                        (65, 320, 136), (100, 192, 520), (128, 448, 1032)])
 def test_gemm_tcgen05_swiglu_half_tiles(K, tokens, n, k):
-    """The SwiGLU product of a few tokens with 64 gate rows and 64 up rows in one 128-row MMA tile."""
+    """The SwiGLU product of up to 128 tokens with 64 gate rows and 64 up rows in one 128-row MMA tile (token tiles of
+    16, 32, 64 and 128; the up rows change hands 16 tokens at a time)."""
     x, w = rnd((tokens, k), torch.bfloat16, 304), rnd((2 * n, k), torch.bfloat16, 305, 0.2)
     for kb in (0, 100, 66):
         out = torch.full((tokens, n), float("nan"), device="cuda", dtype=torch.bfloat16)
@@ -449,7 +452,7 @@ def test_gemm_tcgen05_swiglu_half_tiles(K, tokens, n, k):
         close(out, R.ref_linear(x, w, swiglu=True), torch.bfloat16, 0.5)
     assert K.gemm_status() == 0
     with pytest.raises(Exception):
-        K.gemm_tcgen05(rnd((17, k), torch.bfloat16, 1), w, torch.zeros(17, n, device="cuda", dtype=torch.bfloat16), swiglu=True, half=True)
+        K.gemm_tcgen05(rnd((129, k), torch.bfloat16, 1), w, torch.zeros(129, n, device="cuda", dtype=torch.bfloat16), swiglu=True, half=True)
 
 
 def test_gemm_tcgen05_row_does_not_depend_on_batch(K):
