@@ -20,7 +20,7 @@
 // Softmax statistics, the running output and all sums are float32; P is rounded to bfloat16
 // only as the operand of P.V.  Tiles start at multiples of 64 of the key position, so a
 // query's result does not depend on the batch it is computed in.
-#include "common.cuh"
+#include "tcgen05_common.cuh"      // mbarriers with bounded waits, TMA tile loads, the cache of tensor maps
 
 #include <mutex>
 
@@ -32,7 +32,6 @@ constexpr int kTile = 64;       // keys per shared-memory tile
 constexpr int kThreads = 128;   // 4 warps
 constexpr int kStages = 3;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
 }
@@ -61,6 +60,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Element offset of 16-byte chunk `c` of row `r` in a [rows][D] bf16 tile whose chunks are
 // XOR-swizzled by the row, so that the 8 rows an ldmatrix reads fall into different banks.
 template <int D> __device__ __forceinline__ int tile_off(int r, int c) { return r * D + ((c ^ (r & 7)) << 3); }
+// The same for a tile that TMA boxes with the 128-byte swizzle filled (attn_decode_tma_kernel): per 64 dims a block of
+// [64 rows][128 bytes], the eight chunks of a row XOR-swizzled by the row.
+__device__ __forceinline__ int tma_tile_off(int r, int c) { return (c >> 3) * (64 * 64) + r * 64 + (((c & 7) ^ (r & 7)) << 3); }
+template <int D, bool TMA> __device__ __forceinline__ int kv_tile_off(int r, int c) { return TMA ? tma_tile_off(r, c) : tile_off<D>(r, c); }
 
 // Page ids of the rows of tile [key0, key0 + 64) that this thread copies (rows past `key_last`
 // repeat that key: their scores are masked by the caller, and no page beyond the request's
@@ -100,7 +103,7 @@ __device__ __forceinline__ void load_kv_tiles(bf16* ktile, bf16* vtile, const bf
 }
 
 // S[16 x 16 keys] for one warp: rows = the A fragments `qa`, keys = tile rows [r0, r0 + 16).
-template <int D>
+template <int D, bool TMA = false>
 __device__ __forceinline__ void qk_16keys(float (&s0)[4], float (&s1)[4], const uint32_t (&qa)[D / 16][4],
                                           const bf16* ktile, int r0, int lane) {
 #pragma unroll
@@ -108,21 +111,21 @@ __device__ __forceinline__ void qk_16keys(float (&s0)[4], float (&s1)[4], const 
         uint32_t b[4];
         const int row = r0 + ((lane >> 4) << 3) + (lane & 7);
         const int chunk = 2 * kt + ((lane >> 3) & 1);
-        ldmatrix_x4(b, smem_u32(ktile + tile_off<D>(row, chunk)));
+        ldmatrix_x4(b, smem_u32(ktile + kv_tile_off<D, TMA>(row, chunk)));
         mma_bf16(s0, qa[kt], b[0], b[1]);
         mma_bf16(s1, qa[kt], b[2], b[3]);
     }
 }
 
 // O[16 x D] += P[16 x 16 keys] . V[16 keys x D], V rows = tile rows [r0, r0 + 16).
-template <int D>
+template <int D, bool TMA = false>
 __device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (&pa)[4], const bf16* vtile, int r0, int lane) {
 #pragma unroll
     for (int n2 = 0; n2 < D / 16; ++n2) {
         uint32_t b[4];
         const int row = r0 + (((lane >> 3) & 1) << 3) + (lane & 7);
         const int chunk = 2 * n2 + (lane >> 4);
-        ldmatrix_x4_trans(b, smem_u32(vtile + tile_off<D>(row, chunk)));
+        ldmatrix_x4_trans(b, smem_u32(vtile + kv_tile_off<D, TMA>(row, chunk)));
         mma_bf16(o[2 * n2], pa, b[0], b[1]);
         mma_bf16(o[2 * n2 + 1], pa, b[2], b[3]);
     }
@@ -333,6 +336,148 @@ struct QkvParts {
     bf16* cache;               // the same cache layer, for the store
 };
 
+// FUSED prologue of a decode CTA, run by its `nthreads` computing threads (`tid` among them): adds the qkv product's
+// partial sums of the group's queries, rotates them and leaves them in q_new [16][D]; the CTA whose keys end with the
+// token (`owner`) also adds and rotates the key, adds the value, leaves both in kv_new [2][D] and stores them in
+// the cache.  Items of four neighbouring dims: per rotated head D/8 of them (dims i.. and i + D/2..), per value head
+// D/4.  The arithmetic is that of rope_store_sum_kernel, and the results are rounded to bfloat16 as it rounds them, so
+// both routes hand the same queries, keys and values to the products that follow.
+template <int D>
+__device__ __forceinline__ void decode_fused_prologue(const QkvParts& f, int tok, int hk, int G, int heads, int kv_heads,
+                                                      int page_size, int page_shift, size_t plane, bool owner, bf16* q_new,
+                                                      bf16* kv_new, int tid, int nthreads) {
+    constexpr int half = D / 2, hp = D / 8, per_head = D / 4;
+    const float* row = f.parts + (size_t)tok * ((size_t)(heads + 2 * kv_heads) * D);
+    const int n_q = G * hp;
+    const int n_work = n_q + (owner ? hp + per_head : 0);
+    size_t kdst = 0;
+    if (owner) {
+        const int slot = f.slots[tok];
+        const int page = page_shift >= 0 ? slot >> page_shift : slot / page_size;
+        const int off = page_shift >= 0 ? slot & (page_size - 1) : slot % page_size;
+        kdst = (size_t)page * 2 * plane + (size_t)hk * page_size * D + (size_t)off * D;
+    }
+    for (int w = tid; w < n_work; w += nthreads) {
+        if (w < n_q + hp) {
+            const bool is_q = w < n_q;
+            const int h = is_q ? hk * G + w / hp : heads + hk;
+            const int i = (w % hp) * 4;
+            const float4 a = sum_parts4(row + (size_t)h * D + i, f.splits, f.split_stride);
+            const float4 b = sum_parts4(row + (size_t)h * D + i + half, f.splits, f.split_stride);
+            const float4 c = *reinterpret_cast<const float4*>(f.cos_table + (size_t)tok * half + i);
+            const float4 sg = *reinterpret_cast<const float4*>(f.sin_table + (size_t)tok * half + i);
+            uint2 lo2, hi2;
+            lo2.x = pack_bf16(a.x * c.x - b.x * sg.x, a.y * c.y - b.y * sg.y);
+            lo2.y = pack_bf16(a.z * c.z - b.z * sg.z, a.w * c.w - b.w * sg.w);
+            hi2.x = pack_bf16(b.x * c.x + a.x * sg.x, b.y * c.y + a.y * sg.y);
+            hi2.y = pack_bf16(b.z * c.z + a.z * sg.z, b.w * c.w + a.w * sg.w);
+            bf16* dst = is_q ? q_new + (w / hp) * D : kv_new;
+            *reinterpret_cast<uint2*>(dst + i) = lo2;
+            *reinterpret_cast<uint2*>(dst + i + half) = hi2;
+            if (!is_q) {
+                *reinterpret_cast<uint2*>(f.cache + kdst + i) = lo2;
+                *reinterpret_cast<uint2*>(f.cache + kdst + i + half) = hi2;
+            }
+        } else {
+            const int i = (w - n_q - hp) * 4;
+            const float4 v = sum_parts4(row + (size_t)(heads + kv_heads + hk) * D + i, f.splits, f.split_stride);
+            uint2 v2;
+            v2.x = pack_bf16(v.x, v.y);
+            v2.y = pack_bf16(v.z, v.w);
+            *reinterpret_cast<uint2*>(kv_new + D + i) = v2;
+            *reinterpret_cast<uint2*>(f.cache + kdst + plane + i) = v2;
+        }
+    }
+}
+
+// The A fragments of the group's query heads: rows 0 .. G-1 of the MMA tile (row g at qrow0 + g * D for g < 8 given by
+// the caller as its own row pointer); the other rows are zero.
+template <int D>
+__device__ __forceinline__ void decode_query_fragments(uint32_t (&qa)[D / 16][4], const bf16* qrow0, int g, int t4, int G) {
+    const bf16* qrow1 = qrow0 + 8 * D;
+#pragma unroll
+    for (int kt = 0; kt < D / 16; ++kt) {
+        qa[kt][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + kt * 16 + 2 * t4) : 0u;
+        qa[kt][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + kt * 16 + 2 * t4) : 0u;
+        qa[kt][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + kt * 16 + 8 + 2 * t4) : 0u;
+        qa[kt][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + kt * 16 + 8 + 2 * t4) : 0u;
+    }
+}
+
+// One warp's scores, softmax update and P V of its 16 keys [k0, k0 + 16) of a tile (tile rows r0 ..); keys outside
+// [lo, c1) are masked.
+template <int D, bool TMA>
+__device__ __forceinline__ void decode_warp_tile(const uint32_t (&qa)[D / 16][4], const bf16* ktile, const bf16* vtile, int r0,
+                                                 int k0, int lo, int c1, float sl, float (&m)[2], float (&l)[2],
+                                                 float (&o)[D / 8][4], int lane) {
+    const int t4 = lane & 3;
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    qk_16keys<D, TMA>(s0, s1, qa, ktile, r0, lane);
+    if (k0 + 16 > c1 || k0 < lo) {
+        const int kb = k0 + 2 * t4;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            if (kb + e >= c1 || kb + e < lo) s0[e] = s0[2 + e] = -INFINITY;
+            if (kb + 8 + e >= c1 || kb + 8 + e < lo) s1[e] = s1[2 + e] = -INFINITY;
+        }
+    }
+    uint32_t pa[4];
+    softmax_16keys<D>(s0, s1, m, l, o, pa, sl);
+    pv_16keys<D, TMA>(o, pa, vtile, r0, lane);
+}
+
+// The end of a decode CTA: its four computing warps (each saw other keys) are merged through `scratch`
+// ([4][16][D] + 2 x [4][16] floats of shared memory that nobody reads any more), rows < G only, and the result goes to
+// `out` (one split) or to the partials.  `sync` is the barrier of the computing threads.
+template <int D, typename Sync>
+__device__ __forceinline__ void decode_finish(float (&o)[D / 8][4], float (&m)[2], float (&l)[2], float* scratch, int warp,
+                                              int lane, int tid, int nthreads, int G, int hk, int heads, int tok, int item,
+                                              int split, int n_splits, int max_splits, float* part_o, float* part_ml,
+                                              bf16* out, int out_stride, Sync sync) {
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    float* sm_o = scratch;                                        // [4][16][D]
+    float* sm_m = sm_o + 4 * 16 * D;                              // [4][16]
+    float* sm_l = sm_m + 4 * 16;                                  // [4][16]
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+        const int col = n * 8 + 2 * t4;
+        if (g < G) { sm_o[(warp * 16 + g) * D + col] = o[n][0]; sm_o[(warp * 16 + g) * D + col + 1] = o[n][1]; }
+        if (g + 8 < G) { sm_o[(warp * 16 + g + 8) * D + col] = o[n][2]; sm_o[(warp * 16 + g + 8) * D + col + 1] = o[n][3]; }
+    }
+    if (t4 == 0) {
+        sm_m[warp * 16 + g] = m[0]; sm_l[warp * 16 + g] = l[0];
+        sm_m[warp * 16 + g + 8] = m[1]; sm_l[warp * 16 + g + 8] = l[1];
+    }
+    sync();
+    for (int i = tid; i < G * D; i += nthreads) {
+        const int r = i / D, d = i % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + r]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sm_m[w * 16 + r];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            L += sm_l[w * 16 + r] * f;
+            O += sm_o[(w * 16 + r) * D + d] * f;
+        }
+        const int head = hk * G + r;
+        if (n_splits == 1) {
+            out[(size_t)tok * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(O / L);
+        } else {
+            const size_t base = ((size_t)item * heads + head) * max_splits + split;
+            part_o[base * D + d] = O;
+            if (d == 0) { part_ml[base * 2] = M; part_ml[base * 2 + 1] = L; }
+        }
+    }
+}
+
 template <int D, bool FUSED>
 __global__ void __launch_bounds__(kThreads)
 attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache,
@@ -387,66 +532,12 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     if (kStages - 1 < n_tiles) tile_pages<D>(pg, table, c0 + (kStages - 1) * kTile, pos, page_size, page_shift);
     const bool owner = FUSED && c1 == pos + 1;                    // this CTA's keys end with the token itself
     if constexpr (FUSED) {
-        // Items of four neighbouring dims: per rotated head D/8 of them (dims i.. and i + D/2..), per value head D/4.
-        // The arithmetic is that of rope_store_sum_kernel, and the results are rounded to bfloat16 as it rounds
-        // them, so both routes hand the same queries, keys and values to the products below.
-        constexpr int half = D / 2, hp = D / 8, per_head = D / 4;
-        const float* row = f.parts + (size_t)tok * ((size_t)(heads + 2 * kv_heads) * D);
-        const int n_q = G * hp;
-        const int n_work = n_q + (owner ? hp + per_head : 0);
-        size_t kdst = 0;
-        if (owner) {
-            const int slot = f.slots[tok];
-            const int page = page_shift >= 0 ? slot >> page_shift : slot / page_size;
-            const int off = page_shift >= 0 ? slot & (page_size - 1) : slot % page_size;
-            kdst = (size_t)page * 2 * plane + (size_t)hk * page_size * D + (size_t)off * D;
-        }
-        for (int w = threadIdx.x; w < n_work; w += kThreads) {
-            if (w < n_q + hp) {
-                const bool is_q = w < n_q;
-                const int h = is_q ? hk * G + w / hp : heads + hk;
-                const int i = (w % hp) * 4;
-                const float4 a = sum_parts4(row + (size_t)h * D + i, f.splits, f.split_stride);
-                const float4 b = sum_parts4(row + (size_t)h * D + i + half, f.splits, f.split_stride);
-                const float4 c = *reinterpret_cast<const float4*>(f.cos_table + (size_t)tok * half + i);
-                const float4 sg = *reinterpret_cast<const float4*>(f.sin_table + (size_t)tok * half + i);
-                uint2 lo2, hi2;
-                lo2.x = pack_bf16(a.x * c.x - b.x * sg.x, a.y * c.y - b.y * sg.y);
-                lo2.y = pack_bf16(a.z * c.z - b.z * sg.z, a.w * c.w - b.w * sg.w);
-                hi2.x = pack_bf16(b.x * c.x + a.x * sg.x, b.y * c.y + a.y * sg.y);
-                hi2.y = pack_bf16(b.z * c.z + a.z * sg.z, b.w * c.w + a.w * sg.w);
-                bf16* dst = is_q ? q_new + (w / hp) * D : kv_new;
-                *reinterpret_cast<uint2*>(dst + i) = lo2;
-                *reinterpret_cast<uint2*>(dst + i + half) = hi2;
-                if (!is_q) {
-                    *reinterpret_cast<uint2*>(f.cache + kdst + i) = lo2;
-                    *reinterpret_cast<uint2*>(f.cache + kdst + i + half) = hi2;
-                }
-            } else {
-                const int i = (w - n_q - hp) * 4;
-                const float4 v = sum_parts4(row + (size_t)(heads + kv_heads + hk) * D + i, f.splits, f.split_stride);
-                uint2 v2;
-                v2.x = pack_bf16(v.x, v.y);
-                v2.y = pack_bf16(v.z, v.w);
-                *reinterpret_cast<uint2*>(kv_new + D + i) = v2;
-                *reinterpret_cast<uint2*>(f.cache + kdst + plane + i) = v2;
-            }
-        }
+        decode_fused_prologue<D>(f, tok, hk, G, heads, kv_heads, page_size, page_shift, plane, owner, q_new, kv_new,
+                                 (int)threadIdx.x, kThreads);
         __syncthreads();
     }
-    // the group's query heads are rows 0 .. G-1 of the MMA tile; the other rows are zero
     uint32_t qa[D / 16][4];
-    const bf16* qrow0;
-    if constexpr (FUSED) qrow0 = q_new + g * D;
-    else qrow0 = q + (size_t)tok * q_stride + (size_t)(hk * G + g) * D;
-    const bf16* qrow1 = qrow0 + 8 * D;
-#pragma unroll
-    for (int kt = 0; kt < D / 16; ++kt) {
-        qa[kt][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + kt * 16 + 2 * t4) : 0u;
-        qa[kt][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + kt * 16 + 2 * t4) : 0u;
-        qa[kt][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow0 + kt * 16 + 8 + 2 * t4) : 0u;
-        qa[kt][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow1 + kt * 16 + 8 + 2 * t4) : 0u;
-    }
+    decode_query_fragments<D>(qa, FUSED ? q_new + g * D : q + (size_t)tok * q_stride + (size_t)(hk * G + g) * D, g, t4, G);
     float o[D / 8][4];
 #pragma unroll
     for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
@@ -476,66 +567,162 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
             __syncthreads();
         }
         const int k0 = c0 + it * kTile + warp * 16;               // this warp's 16 keys of the tile
-        if (k0 < c1) {
-            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-            qk_16keys<D>(s0, s1, qa, stage_k(it % kStages), warp * 16, lane);
-            if (k0 + 16 > c1 || k0 < lo) {
-                const int kb = k0 + 2 * t4;
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    if (kb + e >= c1 || kb + e < lo) s0[e] = s0[2 + e] = -INFINITY;
-                    if (kb + 8 + e >= c1 || kb + 8 + e < lo) s1[e] = s1[2 + e] = -INFINITY;
-                }
-            }
-            uint32_t pa[4];
-            softmax_16keys<D>(s0, s1, m, l, o, pa, sl);
-            pv_16keys<D>(o, pa, stage_v(it % kStages), warp * 16, lane);
-        }
+        if (k0 < c1)
+            decode_warp_tile<D, false>(qa, stage_k(it % kStages), stage_v(it % kStages), warp * 16, k0, lo, c1, sl, m, l, o, lane);
     }
     cp_async_wait<0>();
     __syncthreads();
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    decode_finish<D>(o, m, l, reinterpret_cast<float*>(smem_raw), warp, lane, (int)threadIdx.x, kThreads, G, hk, heads, tok,
+                     item, split, n_splits, max_splits, part_o, part_ml, out, out_stride, [] { __syncthreads(); });
+}
+
+// The same decode CTA with its keys and values brought in by TMA: the cache layer is one [rows, D] matrix to the
+// tensor map, a page's 64 dims of one key/value head are one box (page sizes 8 .. 64 that divide 64), and the boxes of
+// a tile of 64 keys land at their row offsets of 128-byte-swizzled [64 keys][64 dims] blocks.  Warp 4 fetches (lane p
+// page p of every tile: its block-table entry, then the boxes of K and V), warps 0-3 compute as above; stages change
+// hands over mbarriers (full: the bytes have landed; empty: the four computing warps are done), so no barrier of the
+// whole CTA sits in the loop, a thread issues no copy of its own, and the loading warp runs ahead of the others by
+// as many stages as there are.  Keys past the token's own are not read from the cache as they are there (the rows
+// are masked; a page past the token's is replaced by the token's page).  Bounded waits: a wait that runs out leaves
+// (7 << 16 | item) in g_decode_status and the CTA writes nothing.
+constexpr int kTmaThreads = 160;
+
+template <int D, bool FUSED>
+__global__ void __launch_bounds__(kTmaThreads)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, int q_stride,
+                       const int* __restrict__ block_table, int table_width, const int* __restrict__ items,
+                       const int* __restrict__ token_request, const int* __restrict__ positions,
+                       float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out, int out_stride,
+                       int heads, int kv_heads, int page_size, int page_shift, int window, float sl, int keys_per_split,
+                       int max_splits, const QkvParts f) {
+    pdl_trigger();
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(16) bf16 q_new[FUSED ? 16 * D : 8];
+    __shared__ __align__(16) bf16 kv_new[FUSED ? 2 * D : 8];
+    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
+    __shared__ volatile int failed;
+    constexpr int kPlaneBytes = kTile * D * 2;                    // one K or V tile
+    constexpr int kHalves = D / 64;
+    const int split = blockIdx.x, hk = blockIdx.y, item = blockIdx.z;
+    const int tok = items[item];
+    const int pos = positions[tok];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int k_begin = lo & ~(kTile - 1);
+    int n_splits = (pos - k_begin) / keys_per_split + 1;
+    if (n_splits > max_splits) {
+        if (split == 0 && hk == 0 && threadIdx.x == 0) atomicCAS(&g_decode_status, 0, (6 << 16) | (item & 0xffff));
+        n_splits = max_splits;
     }
-    // merge the four warps (each saw other keys) through shared memory: rows < G only
-    float* sm_o = reinterpret_cast<float*>(smem_raw);             // [4][16][D]
-    float* sm_m = sm_o + 4 * 16 * D;                              // [4][16]
-    float* sm_l = sm_m + 4 * 16;                                  // [4][16]
-#pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
-        const int col = n * 8 + 2 * t4;
-        if (g < G) { sm_o[(warp * 16 + g) * D + col] = o[n][0]; sm_o[(warp * 16 + g) * D + col + 1] = o[n][1]; }
-        if (g + 8 < G) { sm_o[(warp * 16 + g + 8) * D + col] = o[n][2]; sm_o[(warp * 16 + g + 8) * D + col + 1] = o[n][3]; }
-    }
-    if (t4 == 0) {
-        sm_m[warp * 16 + g] = m[0]; sm_l[warp * 16 + g] = l[0];
-        sm_m[warp * 16 + g + 8] = m[1]; sm_l[warp * 16 + g + 8] = l[1];
+    if (split >= n_splits) return;
+    const int c0 = k_begin + split * keys_per_split;
+    const int c1 = min(c0 + keys_per_split, pos + 1);
+    const int n_tiles = (c1 - c0 + kTile - 1) / kTile;
+    const int G = heads / kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    auto stage_k = [&](int s) { return reinterpret_cast<bf16*>(base + (size_t)s * 2 * kPlaneBytes); };
+    auto stage_v = [&](int s) { return reinterpret_cast<bf16*>(base + (size_t)s * 2 * kPlaneBytes + kPlaneBytes); };
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 4); }
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < G * D; i += kThreads) {
-        const int r = i / D, d = i % D;
-        float M = -INFINITY;
+
+    if (warp == 4) {
+        // ---- loads ------------------------------------------------------------------------------------------
+        const int* table = block_table + (size_t)token_request[tok] * table_width;
+        const int pages_per_tile = kTile >> page_shift;
+        // page of this lane's rows of tile `t` (a page past the token's own: the token's, see above)
+        auto page_of = [&](int t) { return table[min(c0 + t * kTile + (lane << page_shift), pos) >> page_shift]; };
+        int page = lane < pages_per_tile ? page_of(0) : 0;
+        bool waited = false;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int s = it % kStages;
+            // tiles that end before `pos` hold what earlier steps stored: they are requested ahead of the wait for the
+            // kernel before this one (which stores the token's own key and value in the form that is not FUSED)
+            if (!waited && c0 + (it + 1) * kTile > pos) { pdl_wait(); waited = true; }
+            int ok = 1;
+            if (lane == 0) {
+                if (it >= kStages && !mbar_wait(&empty_bar[s], ((it / kStages) - 1) & 1)) {
+                    atomicCAS(&g_decode_status, 0, (7 << 16) | (item & 0xffff));
+                    failed = 1;
+                    ok = 0;
+                } else {
+                    mbar_expect_tx(&full_bar[s], 2 * kPlaneBytes);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (lane < pages_per_tile) {
+                const int row = (page * 2 * kv_heads + hk) * page_size;         // K rows of this page; V rows kv_heads * page_size on
+                unsigned char* kd = reinterpret_cast<unsigned char*>(stage_k(s)) + (size_t)(lane << page_shift) * 128;
+                unsigned char* vd = reinterpret_cast<unsigned char*>(stage_v(s)) + (size_t)(lane << page_shift) * 128;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + r]);
-        float L = 0.f, O = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float mw = sm_m[w * 16 + r];
-            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
-            L += sm_l[w * 16 + r] * f;
-            O += sm_o[(w * 16 + r) * D + d] * f;
+                for (int h = 0; h < kHalves; ++h) {
+                    tma_load_2d(kd + h * (kTile * 128), &map_kv, &full_bar[s], 64 * h, row);
+                    tma_load_2d(vd + h * (kTile * 128), &map_kv, &full_bar[s], 64 * h, row + kv_heads * page_size);
+                }
+                if (it + 1 < n_tiles) page = page_of(it + 1);
+            }
         }
-        const int head = hk * G + r;
-        if (n_splits == 1) {
-            out[(size_t)tok * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(O / L);
-        } else {
-            const size_t base = ((size_t)item * heads + head) * max_splits + split;
-            part_o[base * D + d] = O;
-            if (d == 0) { part_ml[base * 2] = M; part_ml[base * 2 + 1] = L; }
-        }
+        return;
     }
+
+    // ---- the four computing warps ---------------------------------------------------------------------------
+    auto sync_compute = [] { asm volatile("bar.sync 1, 128;" ::: "memory"); };
+    pdl_wait();
+    const bool owner = FUSED && c1 == pos + 1;
+    if constexpr (FUSED) {
+        const size_t plane = (size_t)kv_heads * page_size * D;
+        decode_fused_prologue<D>(f, tok, hk, G, heads, kv_heads, page_size, page_shift, plane, owner, q_new, kv_new,
+                                 (int)threadIdx.x, 128);
+        sync_compute();
+    }
+    uint32_t qa[D / 16][4];
+    decode_query_fragments<D>(qa, FUSED ? q_new + g * D : q + (size_t)tok * q_stride + (size_t)(hk * G + g) * D, g, t4, G);
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    for (int it = 0; it < n_tiles; ++it) {
+        const int s = it % kStages;
+        if (!mbar_wait(&full_bar[s], (it / kStages) & 1)) {
+            atomicCAS(&g_decode_status, 0, (7 << 16) | (item & 0xffff));
+            failed = 1;
+            break;
+        }
+        const int k0 = c0 + it * kTile + warp * 16;               // this warp's 16 keys of the tile
+        if (k0 < c1) {
+            if constexpr (FUSED) {
+                // the box fetched the token's slot as it was before this step or as the prologue stored it, whichever
+                // came first: the warp that holds the token's row writes the key and value computed above over it
+                const int r_new = pos - (c0 + it * kTile);
+                if (owner && it == n_tiles - 1 && (r_new >> 4) == warp) {
+                    if (lane < D / 8) {
+                        *reinterpret_cast<uint4*>(stage_k(s) + tma_tile_off(r_new, lane)) = *reinterpret_cast<const uint4*>(kv_new + lane * 8);
+                        *reinterpret_cast<uint4*>(stage_v(s) + tma_tile_off(r_new, lane)) = *reinterpret_cast<const uint4*>(kv_new + D + lane * 8);
+                    }
+                    __syncwarp();
+                }
+            }
+            if (k0 + 16 > c1) {
+                // rows past the last key were read as they lie in the cache: P is 0 there, but 0 x a slot that was never
+                // written need not be, so their values are zeroed
+                const int first = c1 - k0;
+                for (int i = lane; i < (16 - first) * (D / 8); i += 32)
+                    *reinterpret_cast<uint4*>(stage_v(s) + tma_tile_off(warp * 16 + first + i / (D / 8), i % (D / 8))) = make_uint4(0u, 0u, 0u, 0u);
+                __syncwarp();
+            }
+            decode_warp_tile<D, true>(qa, stage_k(s), stage_v(s), warp * 16, k0, lo, c1, sl, m, l, o, lane);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+    sync_compute();                           // every warp is done with the stages: they become the merge's scratch
+    if (failed) return;
+    decode_finish<D>(o, m, l, reinterpret_cast<float*>(base), warp, lane, (int)threadIdx.x, 128, G, hk, heads, tok, item, split,
+                     n_splits, max_splits, part_o, part_ml, out, out_stride, sync_compute);
 }
 
 // All loads of a thread are asked for at once (the partial results of every possible split, and the position
@@ -680,10 +867,18 @@ LLM_API int llm_attention_prefill_bf16(const void* q, int q_stride, const void* 
 // items: [n_items] token rows of the decoded tokens.  part_o needs n_items*heads*max_splits*head_dim floats,
 // part_ml n_items*heads*max_splits*2 floats (both unused when max_splits == 1).
 namespace {
-int launch_decode(const void* q, int q_stride, const void* cache, const int* block_table, int table_width, const int* items,
-                  int n_items, const int* token_request, const int* positions, float* part_o, float* part_ml, void* out,
-                  int out_stride, int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
-                  int keys_per_split, int max_splits, const QkvParts* fused, cudaStream_t stream);
+int launch_decode(const void* q, int q_stride, const void* cache, long long cache_pages, const int* block_table,
+                  int table_width, const int* items, int n_items, const int* token_request, const int* positions,
+                  float* part_o, float* part_ml, void* out, int out_stride, int heads, int kv_heads, int head_dim,
+                  int page_size, int window, float scale, int keys_per_split, int max_splits, const QkvParts* fused,
+                  cudaStream_t stream);
+}
+
+// 1 if the decode kernel that fetches keys and values by TMA takes this shape (head sizes 64 and 128, pages of 8, 16,
+// 32 or 64 tokens), else 0: llm_attention_decode_bf16 and its fused form take the rest.
+LLM_API int llm_attention_decode_tma_supported(int heads, int kv_heads, int head_dim, int page_size) {
+    return llm_attention_bf16_supported(heads, kv_heads, head_dim) &&
+           (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
 }
 
 LLM_API int llm_attention_decode_bf16(const void* q, int q_stride, const void* cache, const int* block_table,
@@ -691,9 +886,24 @@ LLM_API int llm_attention_decode_bf16(const void* q, int q_stride, const void* c
                                       const int* positions, float* part_o, float* part_ml, void* out, int out_stride,
                                       int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
                                       int keys_per_split, int max_splits, cudaStream_t stream) {
-    return launch_decode(q, q_stride, cache, block_table, table_width, items, n_items, token_request, positions, part_o,
+    return launch_decode(q, q_stride, cache, 0, block_table, table_width, items, n_items, token_request, positions, part_o,
                          part_ml, out, out_stride, heads, kv_heads, head_dim, page_size, window, scale, keys_per_split,
                          max_splits, nullptr, stream);
+}
+
+// The same with keys and values fetched by TMA: `cache_pages` is the count of pages of the cache layer (its first
+// dimension), which the tensor map needs; shapes as llm_attention_decode_tma_supported says.
+LLM_API int llm_attention_decode_bf16_tma(const void* q, int q_stride, const void* cache, long long cache_pages,
+                                          const int* block_table, int table_width, const int* items, int n_items,
+                                          const int* token_request, const int* positions, float* part_o, float* part_ml,
+                                          void* out, int out_stride, int heads, int kv_heads, int head_dim, int page_size,
+                                          int window, float scale, int keys_per_split, int max_splits, cudaStream_t stream) {
+    if (cache_pages <= 0 || !llm_attention_decode_tma_supported(heads, kv_heads, head_dim, page_size))
+        LLM_FAIL(-1, "attention_decode_bf16_tma: heads %d / kv_heads %d / head_dim %d / page %d / %lld pages not supported",
+                 heads, kv_heads, head_dim, page_size, cache_pages);
+    return launch_decode(q, q_stride, cache, cache_pages, block_table, table_width, items, n_items, token_request, positions,
+                         part_o, part_ml, out, out_stride, heads, kv_heads, head_dim, page_size, window, scale,
+                         keys_per_split, max_splits, nullptr, stream);
 }
 
 // The same for single decoded tokens whose qkv product was left as k-split partial sums: `parts`
@@ -712,16 +922,38 @@ LLM_API int llm_attention_decode_bf16_fused(const float* parts, int splits, long
         LLM_FAIL(-1, "attention_decode_bf16_fused: 1 to %d splits with a stride that is a multiple of 4 (got %d, %lld)",
                  kMaxParts, splits, split_stride);
     QkvParts f{parts, splits, (size_t)split_stride, cos_table, sin_table, slots, (bf16*)cache};
-    return launch_decode(nullptr, 0, cache, block_table, table_width, items, n_items, token_request, positions, part_o,
+    return launch_decode(nullptr, 0, cache, 0, block_table, table_width, items, n_items, token_request, positions, part_o,
                          part_ml, out, out_stride, heads, kv_heads, head_dim, page_size, window, scale, keys_per_split,
                          max_splits, &f, stream);
 }
 
+// The fused form with keys and values fetched by TMA (`cache_pages` as in llm_attention_decode_bf16_tma).
+LLM_API int llm_attention_decode_bf16_fused_tma(const float* parts, int splits, long long split_stride, const float* cos_table,
+                                                const float* sin_table, const int* slots, void* cache, long long cache_pages,
+                                                const int* block_table, int table_width, const int* items, int n_items,
+                                                const int* token_request, const int* positions, float* part_o, float* part_ml,
+                                                void* out, int out_stride, int heads, int kv_heads, int head_dim,
+                                                int page_size, int window, float scale, int keys_per_split, int max_splits,
+                                                cudaStream_t stream) {
+    if (!parts || !cos_table || !sin_table || !slots) LLM_FAIL(-1, "attention_decode_bf16_fused_tma: parts, tables and slots are needed");
+    if (splits < 1 || splits > kMaxParts || split_stride % 4 || ((heads + 2 * kv_heads) * head_dim) % 4)
+        LLM_FAIL(-1, "attention_decode_bf16_fused_tma: 1 to %d splits with a stride that is a multiple of 4 (got %d, %lld)",
+                 kMaxParts, splits, split_stride);
+    if (cache_pages <= 0 || !llm_attention_decode_tma_supported(heads, kv_heads, head_dim, page_size))
+        LLM_FAIL(-1, "attention_decode_bf16_fused_tma: heads %d / kv_heads %d / head_dim %d / page %d / %lld pages not supported",
+                 heads, kv_heads, head_dim, page_size, cache_pages);
+    QkvParts f{parts, splits, (size_t)split_stride, cos_table, sin_table, slots, (bf16*)cache};
+    return launch_decode(nullptr, 0, cache, cache_pages, block_table, table_width, items, n_items, token_request, positions,
+                         part_o, part_ml, out, out_stride, heads, kv_heads, head_dim, page_size, window, scale,
+                         keys_per_split, max_splits, &f, stream);
+}
+
 namespace {
-int launch_decode(const void* q, int q_stride, const void* cache, const int* block_table, int table_width, const int* items,
-                  int n_items, const int* token_request, const int* positions, float* part_o, float* part_ml, void* out,
-                  int out_stride, int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
-                  int keys_per_split, int max_splits, const QkvParts* fused, cudaStream_t stream) {
+int launch_decode(const void* q, int q_stride, const void* cache, long long cache_pages, const int* block_table,
+                  int table_width, const int* items, int n_items, const int* token_request, const int* positions,
+                  float* part_o, float* part_ml, void* out, int out_stride, int heads, int kv_heads, int head_dim,
+                  int page_size, int window, float scale, int keys_per_split, int max_splits, const QkvParts* fused,
+                  cudaStream_t stream) {
     if (n_items == 0) return 0;
     if (!llm_attention_bf16_supported(heads, kv_heads, head_dim))
         LLM_FAIL(-1, "attention_decode_bf16: heads %d / kv_heads %d / head_dim %d not supported", heads, kv_heads, head_dim);
@@ -749,6 +981,35 @@ int launch_decode(const void* q, int q_stride, const void* cache, const int* blo
         }
         return 0;
     };
+    if (cache_pages > 0) {
+        // keys and values by TMA: the cache layer as a [pages * 2 * kv_heads * page_size, head_dim] matrix, one box per page and 64 dims
+        const uint64_t kv_rows = (uint64_t)cache_pages * 2 * kv_heads * page_size;
+        if (kv_rows > 0x7fffffffull) LLM_FAIL(-1, "attention_decode_bf16_tma: the cache layer has too many rows for 32-bit TMA coordinates");
+        CUtensorMap mkv;
+        if (int rc = llm_tensor_map_2d(cache, kv_rows, (uint64_t)head_dim, (uint32_t)page_size, 64, &mkv)) return rc;
+        auto launch_tma = [&](auto kern, auto merge, int D) {
+            size_t smem = (size_t)kStages * 2 * kTile * D * sizeof(bf16);
+            const size_t merge_smem = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
+            if (merge_smem > smem) smem = merge_smem;
+            smem += 1024;                          // the stages start at a multiple of 1024 bytes (128-byte swizzle)
+            if (set_smem(kern, smem, "attention_decode_bf16_tma")) return -2;
+            llm_launch(kern, grid, kTmaThreads, smem, stream, mkv, (const bf16*)q, q_stride, block_table, table_width, items,
+                       token_request, positions, part_o, part_ml, (bf16*)out, out_stride, heads, kv_heads, page_size,
+                       page_shift, window, sl, keys_per_split, max_splits, fused ? *fused : QkvParts{});
+            LLM_CHECK_LAUNCH("attention_decode_bf16_tma");
+            if (max_splits > 1) {
+                llm_launch(merge, dim3(n_items, heads), D, 0, stream, part_o, part_ml, items, positions, (bf16*)out, out_stride,
+                           heads, window, keys_per_split, max_splits);
+                LLM_CHECK_LAUNCH("attention_merge");
+            }
+            return 0;
+        };
+        if (fused)
+            return head_dim == 64 ? launch_tma(attn_decode_tma_kernel<64, true>, attn_merge_kernel<64>, 64)
+                                  : launch_tma(attn_decode_tma_kernel<128, true>, attn_merge_kernel<128>, 128);
+        return head_dim == 64 ? launch_tma(attn_decode_tma_kernel<64, false>, attn_merge_kernel<64>, 64)
+                              : launch_tma(attn_decode_tma_kernel<128, false>, attn_merge_kernel<128>, 128);
+    }
     if (fused)
         return head_dim == 64 ? launch(attn_decode_kernel<64, true>, attn_merge_kernel<64>, 64)
                               : launch(attn_decode_kernel<128, true>, attn_merge_kernel<128>, 128);

@@ -58,6 +58,14 @@ _SIGNATURES = {
     "llm_attention_decode_bf16_fused": [_c_void_p, _c_int, ctypes.c_longlong, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                         _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p],
+    "llm_attention_decode_tma_supported": [_c_int, _c_int, _c_int, _c_int],
+    "llm_attention_decode_bf16_tma": [_c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_int,
+                                      _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                                      _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p],
+    "llm_attention_decode_bf16_fused_tma": [_c_void_p, _c_int, ctypes.c_longlong, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                            ctypes.c_longlong, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                            _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                            _c_float, _c_int, _c_int, _c_void_p],
     "llm_attention_tcgen05_supported": [_c_int, _c_int, _c_int, _c_int],
     "llm_attention_prefill_tcgen05": [_c_void_p, _c_int, _c_int, _c_void_p, ctypes.c_longlong, _c_void_p, _c_int, _c_void_p,
                                       _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
@@ -86,7 +94,8 @@ HEALTH_WORDS = (
     ("CTA-pair matrix product", "a bounded wait ran out (1 producer, 2 MMA issuer, 3 epilogue, 4 drained accumulator, "
                                 "5 other clusters' partial sums)"),
     ("tcgen05 prefill attention", "a bounded wait ran out"),
-    ("decode attention", "keys_per_split * max_splits did not cover an item's keys (6)"),
+    ("decode attention", "keys_per_split * max_splits did not cover an item's keys (6), or a bounded wait for keys and "
+                         "values ran out (7)"),
 )
 
 
@@ -275,6 +284,7 @@ class Kernels:
         self.swiglu_half_tokens = int(os.environ.get("IITJ_SWIGLU_HALF_TOKENS", "64"))  # half-tile SwiGLU product up to here
         self.swiglu_half_smem_kb = int(os.environ.get("IITJ_SWIGLU_HALF_KB", "100"))
         self.fuse_decode = os.environ.get("IITJ_FUSE_DECODE", "1") != "0"   # rope + cache write inside decode attention
+        self.decode_tma = os.environ.get("IITJ_DECODE_TMA", "1") != "0"     # decode attention fetches keys and values by TMA
         self.attention_splits = os.environ.get("IITJ_ATTN_SPLITS")         # forces the key splits of prefill attention
         self.attention_tcgen05 = os.environ.get("IITJ_ATTN_TCGEN05", "1") == "1"
         if os.environ.get("IITJ_PDL", "1") == "0":
@@ -502,11 +512,18 @@ class Kernels:
                 if splits > 1:
                     part_o = self._scratch("attn.part_o", plan.n_items * heads * splits * head_dim, qkv.device)
                     part_ml = self._scratch("attn.part_ml", plan.n_items * heads * splits * 2, qkv.device)
-                self._call("llm_attention_decode_bf16", _ptr(qkv), qkv.shape[1], _ptr(cache_layer),
-                           _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.items), plan.n_items,
-                           _ptr(meta.token_request), _ptr(meta.positions), _ptr(part_o), _ptr(part_ml), _ptr(out),
-                           out.shape[1], heads, kv_heads, head_dim, page_size, int(window), float(scale), kps, splits,
-                           self._stream())
+                if self.decode_tma and self.lib.llm_attention_decode_tma_supported(heads, kv_heads, head_dim, page_size):
+                    self._call("llm_attention_decode_bf16_tma", _ptr(qkv), qkv.shape[1], _ptr(cache_layer), cache_layer.shape[0],
+                               _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.items), plan.n_items,
+                               _ptr(meta.token_request), _ptr(meta.positions), _ptr(part_o), _ptr(part_ml), _ptr(out),
+                               out.shape[1], heads, kv_heads, head_dim, page_size, int(window), float(scale), kps, splits,
+                               self._stream())
+                else:
+                    self._call("llm_attention_decode_bf16", _ptr(qkv), qkv.shape[1], _ptr(cache_layer),
+                               _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.items), plan.n_items,
+                               _ptr(meta.token_request), _ptr(meta.positions), _ptr(part_o), _ptr(part_ml), _ptr(out),
+                               out.shape[1], heads, kv_heads, head_dim, page_size, int(window), float(scale), kps, splits,
+                               self._stream())
                 if splits > 1:
                     self.launches += 1      # the merge kernel
             return out
@@ -558,10 +575,17 @@ class Kernels:
         if splits > 1:
             part_o = self._scratch("attn.part_o", plan.n_items * heads * splits * head_dim, out.device)
             part_ml = self._scratch("attn.part_ml", plan.n_items * heads * splits * 2, out.device)
-        self._call("llm_attention_decode_bf16_fused", _ptr(qkv.parts), qkv.splits, qkv.stride, _ptr(cos), _ptr(sin), _ptr(slots),
-                   _ptr(cache_layer), _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.items), plan.n_items,
-                   _ptr(meta.token_request), _ptr(meta.positions), _ptr(part_o), _ptr(part_ml), _ptr(out), out.shape[1],
-                   heads, kv_heads, head_dim, cache_layer.shape[3], int(window), float(scale), kps, splits, self._stream())
+        if self.decode_tma and self.lib.llm_attention_decode_tma_supported(heads, kv_heads, head_dim, cache_layer.shape[3]):
+            self._call("llm_attention_decode_bf16_fused_tma", _ptr(qkv.parts), qkv.splits, qkv.stride, _ptr(cos), _ptr(sin),
+                       _ptr(slots), _ptr(cache_layer), cache_layer.shape[0], _ptr(meta.block_table), meta.block_table.shape[1],
+                       _ptr(plan.items), plan.n_items, _ptr(meta.token_request), _ptr(meta.positions), _ptr(part_o),
+                       _ptr(part_ml), _ptr(out), out.shape[1], heads, kv_heads, head_dim, cache_layer.shape[3], int(window),
+                       float(scale), kps, splits, self._stream())
+        else:
+            self._call("llm_attention_decode_bf16_fused", _ptr(qkv.parts), qkv.splits, qkv.stride, _ptr(cos), _ptr(sin), _ptr(slots),
+                       _ptr(cache_layer), _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.items), plan.n_items,
+                       _ptr(meta.token_request), _ptr(meta.positions), _ptr(part_o), _ptr(part_ml), _ptr(out), out.shape[1],
+                       heads, kv_heads, head_dim, cache_layer.shape[3], int(window), float(scale), kps, splits, self._stream())
         if splits > 1:
             self.launches += 1      # the merge kernel
         return out

@@ -280,18 +280,45 @@ def test_sample_temperature_follows_softmax(K):
     assert (freq - want).abs().max() < 0.015, (freq, want)
 
 
+@pytest.fixture(params=["tma", "cp_async"])
+def decode_loads(K, request):
+    """Both decode attention kernels: keys and values fetched by TMA (pages of 8 to 64 tokens), or copied by the
+    threads themselves (any page size)."""
+    before = K.decode_tma
+    K.decode_tma = request.param == "tma"
+    yield request.param
+    K.decode_tma = before
+
+
+def _poison_unwritten_slots(cache, meta, lens, page):
+    """NaN in every slot after a request's last token (the rest of its last page) and in the pages no request
+    holds: nothing of them may reach a result."""
+    used = set()
+    for b, n in enumerate(lens):
+        for j in range(-(-n // page)):
+            used.add(int(meta.block_table[b, j]))
+        if n % page:
+            cache[int(meta.block_table[b, (n - 1) // page]), :, :, n % page:, :] = float("nan")
+    for pg in range(cache.shape[0]):
+        if pg not in used and pg != 0:                  # (page 0 pads the block table's rows)
+            cache[pg] = float("nan")
+
+
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page,window", [
     (8, 2, 128, 16, 0), (32, 8, 128, 16, 0), (16, 1, 64, 16, 0), (6, 2, 64, 8, 0), (4, 4, 128, 32, 0),
-    (8, 2, 128, 16, 300), (3, 1, 64, 4, 0)])
-def test_attention_bf16_decode_splits(K, heads, kv_heads, head_dim, page, window):
-    """Only single-token requests, contexts long enough to be cut into several splits."""
+    (8, 2, 128, 16, 300), (3, 1, 64, 4, 0), (2, 1, 128, 64, 0), (5, 1, 64, 64, 130), (12, 4, 128, 8, 0)])
+def test_attention_bf16_decode_splits(K, decode_loads, heads, kv_heads, head_dim, page, window):
+    """Only single-token requests, contexts long enough to be cut into several splits; what lies in the cache after
+    a request's last token is NaN."""
     lens = [700, 300, 1000, 257, 64, 65, 1, 1500]
     q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lens, [1] * len(lens), 70)
+    _poison_unwritten_slots(cache, meta, lens, page)
     out = torch.empty(q.shape[0], heads * head_dim, device="cuda", dtype=torch.bfloat16)
     K.attention(q, cache, meta, out, heads, kv_heads, head_dim, window=window)
     want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads,
                                  head_dim, window)
     close(out, want, torch.bfloat16)
+    assert K.decode_status() == 0
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page,window", [
@@ -307,7 +334,7 @@ def test_attention_bf16_prefill_tiles(K, heads, kv_heads, head_dim, page, window
     close(out, want, torch.bfloat16)
 
 
-def test_attention_bf16_same_result_in_any_batch(K):
+def test_attention_bf16_same_result_in_any_batch(K, decode_loads):
     """A decoded token's output is bitwise the same alone and beside other requests."""
     heads, kv_heads, head_dim, page = 8, 2, 128, 16
     lens, qlens = [500, 130, 77], [1, 40, 1]
@@ -552,8 +579,8 @@ def test_attention_tcgen05_far_key_and_page_edges(K, head_dim):
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page,window,splits", [
     (8, 2, 128, 16, 0, 3), (32, 8, 128, 16, 0, 6), (16, 1, 64, 16, 0, 1), (6, 2, 64, 8, 0, 8), (4, 4, 128, 32, 0, 2),
-    (8, 2, 128, 16, 300, 4), (3, 1, 64, 4, 0, 5)])
-def test_attention_decode_fused(K, heads, kv_heads, head_dim, page, window, splits):
+    (8, 2, 128, 16, 300, 4), (3, 1, 64, 4, 0, 5), (2, 1, 128, 64, 0, 2), (12, 4, 64, 32, 200, 3)])
+def test_attention_decode_fused(K, decode_loads, heads, kv_heads, head_dim, page, window, splits):
     """Decode attention that takes the qkv product's partial sums: adds them, rotates, stores the token's key and
     value and attends.  Against the plain rotation, store and attention; the slot of each token holds a
     huge stale value beforehand, which must neither be read nor survive."""
@@ -566,6 +593,7 @@ def test_attention_decode_fused(K, heads, kv_heads, head_dim, page, window, spli
     pos = meta.positions.long()
     slots = (meta.block_table[torch.arange(tokens, device="cuda"), pos // page].long() * page + pos % page).to(torch.int32)
     meta.slots = slots
+    _poison_unwritten_slots(cache, meta, lens, page)
     cache[(slots // page).long(), :, :, (slots % page).long(), :] = 3.0e4          # stale: would swamp everything
     want_cache = cache.clone()
     roped = R.ref_rope(parts.sum(0), meta.positions, inv_freq, heads, kv_heads, head_dim, head_dim).to(torch.bfloat16)
@@ -580,13 +608,15 @@ def test_attention_decode_fused(K, heads, kv_heads, head_dim, page, window, spli
     out = torch.empty(tokens, heads * head_dim, device="cuda", dtype=torch.bfloat16)
     K.attention_decode_fused(qkv, (cos, sin), slots, cache, meta, out, heads, kv_heads, head_dim, window=window)
     close(out, want, torch.bfloat16)
-    close(cache, want_cache, torch.bfloat16)
+    seen = lambda c: torch.nan_to_num(c, nan=7.0)                 # (the unwritten slots are NaN before and after)
+    close(seen(cache), seen(want_cache), torch.bfloat16)
     # the unfused route (rope_store, then attention) gives the same keys and values, bit for bit
     cache2 = want_cache.clone()
     cache2[(slots // page).long(), :, :, (slots % page).long(), :] = 3.0e4
     K.rope_store(PartialSums(K, parts, torch.zeros(tokens, width, device="cuda", dtype=torch.bfloat16)), meta.positions,
                  inv_freq, slots, cache2, heads, kv_heads, head_dim, head_dim, tables=(cos, sin))
-    assert torch.equal(cache2, cache)
+    assert torch.equal(seen(cache2), seen(cache))
+    assert K.decode_status() == 0
 
 
 def test_attention_decode_fused_is_refused_for_mixed_steps(K):
