@@ -586,6 +586,15 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
 // are masked; a page past the token's is replaced by the token's page).  Bounded waits: a wait that runs out leaves
 // (7 << 16 | item) in g_decode_status and the CTA writes nothing.
 constexpr int kTmaThreads = 160;
+// Stages of 64 keys: three at head size 128 (96 KiB, two CTAs per SM).  At head size 64 six (the same 96 KiB) measured
+// 1 to 2 % ahead of three and four in whole decode steps of a 16-layer model of width 2048.
+#ifndef LLM_TMA_STAGES_64
+#define LLM_TMA_STAGES_64 6
+#endif
+#ifndef LLM_TMA_STAGES_128
+#define LLM_TMA_STAGES_128 3
+#endif
+template <int D> constexpr int tma_stages() { return D == 64 ? LLM_TMA_STAGES_64 : LLM_TMA_STAGES_128; }
 
 template <int D, bool FUSED>
 __global__ void __launch_bounds__(kTmaThreads)
@@ -600,6 +609,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(16) bf16 q_new[FUSED ? 16 * D : 8];
     __shared__ __align__(16) bf16 kv_new[FUSED ? 2 * D : 8];
+    constexpr int kStages = tma_stages<D>();                      // (shadows the copying kernels' count)
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
     __shared__ volatile int failed;
     constexpr int kPlaneBytes = kTile * D * 2;                    // one K or V tile
@@ -988,7 +998,7 @@ int launch_decode(const void* q, int q_stride, const void* cache, long long cach
         CUtensorMap mkv;
         if (int rc = llm_tensor_map_2d(cache, kv_rows, (uint64_t)head_dim, (uint32_t)page_size, 64, &mkv)) return rc;
         auto launch_tma = [&](auto kern, auto merge, int D) {
-            size_t smem = (size_t)kStages * 2 * kTile * D * sizeof(bf16);
+            size_t smem = (size_t)(D == 64 ? tma_stages<64>() : tma_stages<128>()) * 2 * kTile * D * sizeof(bf16);
             const size_t merge_smem = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
             if (merge_smem > smem) smem = merge_smem;
             smem += 1024;                          // the stages start at a multiple of 1024 bytes (128-byte swizzle)
