@@ -594,7 +594,7 @@ constexpr int kTmaThreads = 160;
 #ifndef LLM_TMA_STAGES_128
 #define LLM_TMA_STAGES_128 3
 #endif
-template <int D> constexpr int tma_stages() { return D == 64 ? LLM_TMA_STAGES_64 : LLM_TMA_STAGES_128; }
+template <int D> __host__ __device__ constexpr int tma_stages() { return D == 64 ? LLM_TMA_STAGES_64 : LLM_TMA_STAGES_128; }
 
 template <int D, bool FUSED>
 __global__ void __launch_bounds__(kTmaThreads)
