@@ -35,3 +35,15 @@ def model_dirs(tmp_path_factory):
         write_model_dir(cfg, str(d), seed)
         out[name] = str(d)
     return out
+
+
+@pytest.fixture(params=["tma", "cp_async"])
+def decode_loads(request):
+    """Both decode attention kernels: keys and values fetched by TMA (pages of 8 to 64 tokens), or copied by the
+    threads themselves (any page size)."""
+    from iitj_llm_coopt_b200 import kernels
+    K = kernels.load()
+    before = K.decode_tma
+    K.decode_tma = request.param == "tma"
+    yield request.param
+    K.decode_tma = before

@@ -125,9 +125,10 @@ def _headline_case(lens, page, heads, kv_heads, head_dim, seed):
 
 @pytest.mark.parametrize("bound", [None, "graph"])
 @pytest.mark.parametrize("fused", [False, True])
-def test_decode_attention_at_the_headline_shape(fused, bound):
+def test_decode_attention_at_the_headline_shape(decode_loads, fused, bound):
     """Batch 64 of 32 heads / 8 key-value heads of 128, pages of 16, contexts of 8192 give or take a few and one of
-    16,400: the split chosen from the contexts themselves and, as a captured graph has it, from an upper bound.  In
+    16,400, with either kernel (TMA boxes, or copies by the threads): the split chosen from the contexts themselves and,
+    as a captured graph has it, from an upper bound.  In
     some requests one far key stands out (on the first and last key of a split and beside them), so that a
     split that is dropped, or merged with the wrong weight, changes the result from about 3 to about 0."""
     from iitj_llm_coopt_b200 import kernels

@@ -280,16 +280,6 @@ def test_sample_temperature_follows_softmax(K):
     assert (freq - want).abs().max() < 0.015, (freq, want)
 
 
-@pytest.fixture(params=["tma", "cp_async"])
-def decode_loads(K, request):
-    """Both decode attention kernels: keys and values fetched by TMA (pages of 8 to 64 tokens), or copied by the
-    threads themselves (any page size)."""
-    before = K.decode_tma
-    K.decode_tma = request.param == "tma"
-    yield request.param
-    K.decode_tma = before
-
-
 def _poison_unwritten_slots(cache, meta, lens, page):
     """NaN in every slot after a request's last token (the rest of its last page) and in the pages no request
     holds: nothing of them may reach a result."""
@@ -332,6 +322,32 @@ def test_attention_bf16_prefill_tiles(K, heads, kv_heads, head_dim, page, window
     want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads,
                                  head_dim, window)
     close(out, want, torch.bfloat16)
+
+
+@pytest.mark.parametrize("head_dim,context", [(128, 9000), (64, 5000), (128, 4500), (64, 20000)])
+def test_attention_bf16_one_long_request_has_many_splits(K, decode_loads, head_dim, context):
+    """One decoded token alone: its keys are cut into more splits than the merge kernel keeps in registers (17 to 31,
+    32 and more), and one key that stands out lies in the last but one."""
+    from iitj_llm_coopt_b200.kernels import AttentionPlan
+    heads, kv_heads, page = 8, 2, 16
+    q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, [context], [1], 95)
+    plan = AttentionPlan(meta.query_lens, meta.seq_lens_host, "cuda", total_tokens=1)
+    meta.attention_plan = plan
+    kps, splits = plan.split(kv_heads, 0, K.sm_count, head_dim, None)
+    assert splits > 16, (kps, splits)
+    far = (splits - 2) * kps + 5
+    direction = rnd((head_dim,), torch.float32, 96)
+    direction = direction / direction.norm()
+    pg, off = int(meta.block_table[0, far // page]), far % page
+    cache[pg, 0, :, off] = (direction * 30.0).to(torch.bfloat16)
+    cache[pg, 1, :, off] = 2.0
+    q[0, :heads * head_dim] = (direction * 12.0).repeat(heads).to(torch.bfloat16)
+    out = torch.empty(1, heads * head_dim, device="cuda", dtype=torch.bfloat16)
+    K.attention(q, cache, meta, out, heads, kv_heads, head_dim)
+    want = R.ref_paged_attention(q, cache, meta.block_table, meta.token_request, meta.positions, heads, kv_heads, head_dim)
+    close(out, want, torch.bfloat16)
+    assert (out.float() - 2.0).abs().max().item() < 0.1
+    assert K.decode_status() == 0
 
 
 def test_attention_bf16_same_result_in_any_batch(K, decode_loads):
