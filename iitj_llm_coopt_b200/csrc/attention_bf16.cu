@@ -740,14 +740,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
 constexpr int kMergeSplits = 16;
 constexpr int kMaxMergeSplits = 1024;          // most key splits of one item (the merge keeps their maxima and sums in shared memory)
 
+constexpr int kMergeGroups = 4;                // many splits: thread groups that share a (item, head)'s splits among them
+
 template <int D>
-__global__ void __launch_bounds__(D)
+__global__ void __launch_bounds__(D * kMergeGroups)
 attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ items,
                   const int* __restrict__ positions, bf16* __restrict__ out, int out_stride, int heads, int window,
                   int keys_per_split, int max_splits) {
     pdl_trigger();
     pdl_wait();
-    const int item = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    const int item = blockIdx.x, head = blockIdx.y, d = threadIdx.x;      // (blockDim.y > 1 only with many splits, see below)
     const size_t base = ((size_t)item * heads + head) * max_splits;
     float pm[kMergeSplits], pl[kMergeSplits], po[kMergeSplits];
     if (max_splits <= kMergeSplits) {
@@ -781,32 +783,41 @@ attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
         }
     } else {
         // Many splits (a single request with a long context): the splits' maxima and sums go through shared memory
-        // once (one split per thread), every thread then weighs its dim of the partial outputs, eight loads at a time.
+        // once, then blockDim.y groups of D threads share the splits among them (group g takes the splits g, g + groups,
+        // ...: eight loads at a time) and their sums meet in shared memory in group order.
         __shared__ float sm_w[kMaxMergeSplits], sm_l[kMaxMergeSplits];
-        float M_all = -INFINITY;
-        for (int s0 = 0; s0 < n_splits; s0 += D) {              // (n_splits <= kMaxMergeSplits, checked by the launcher)
-            const int sidx = s0 + d;
-            if (sidx < n_splits) { sm_w[sidx] = part_ml[(base + sidx) * 2]; sm_l[sidx] = part_ml[(base + sidx) * 2 + 1]; }
+        __shared__ float grp_o[kMergeGroups][D], grp_l[kMergeGroups];
+        const int grp = threadIdx.y, groups = blockDim.y;
+        for (int sidx = grp * D + d; sidx < n_splits; sidx += groups * D) {    // (n_splits <= kMaxMergeSplits, checked by the launcher)
+            sm_w[sidx] = part_ml[(base + sidx) * 2];
+            sm_l[sidx] = part_ml[(base + sidx) * 2 + 1];
         }
         __syncthreads();
-        for (int s = 0; s < n_splits; ++s) M_all = fmaxf(M_all, sm_w[s]);
-        M = M_all;
-        int s = 0;
-        for (; s + 8 <= n_splits; s += 8) {
+        for (int s = 0; s < n_splits; ++s) M = fmaxf(M, sm_w[s]);
+        int s = grp;
+        for (; s + 7 * groups < n_splits; s += 8 * groups) {
             float v[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = part_o[(base + s + i) * D + d];
+            for (int i = 0; i < 8; ++i) v[i] = part_o[(base + s + i * groups) * D + d];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const float f = exp2f(sm_w[s + i] - M);
-                L += sm_l[s + i] * f;
+                const float f = exp2f(sm_w[s + i * groups] - M);
+                L += sm_l[s + i * groups] * f;
                 O += v[i] * f;
             }
         }
-        for (; s < n_splits; ++s) {
+        for (; s < n_splits; s += groups) {
             const float f = exp2f(sm_w[s] - M);
             L += sm_l[s] * f;
             O += part_o[(base + s) * D + d] * f;
+        }
+        if (groups > 1) {
+            grp_o[grp][d] = O;
+            if (d == 0) grp_l[grp] = L;
+            __syncthreads();
+            if (grp > 0) return;
+            O = 0.f; L = 0.f;
+            for (int g = 0; g < groups; ++g) { O += grp_o[g][d]; L += grp_l[g]; }
         }
     }
     out[(size_t)tok * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(O / L);
@@ -985,7 +996,7 @@ int launch_decode(const void* q, int q_stride, const void* cache, long long cach
                                                fused ? *fused : QkvParts{});
         LLM_CHECK_LAUNCH("attention_decode_bf16");
         if (max_splits > 1) {
-            llm_launch(merge, dim3(n_items, heads), D, 0, stream, part_o, part_ml, items, positions, (bf16*)out, out_stride, heads,
+            llm_launch(merge, dim3(n_items, heads), dim3(D, max_splits > kMergeSplits ? kMergeGroups : 1), 0, stream, part_o, part_ml, items, positions, (bf16*)out, out_stride, heads,
                                                           window, keys_per_split, max_splits);
             LLM_CHECK_LAUNCH("attention_merge");
         }
@@ -1008,7 +1019,7 @@ int launch_decode(const void* q, int q_stride, const void* cache, long long cach
                        page_shift, window, sl, keys_per_split, max_splits, fused ? *fused : QkvParts{});
             LLM_CHECK_LAUNCH("attention_decode_bf16_tma");
             if (max_splits > 1) {
-                llm_launch(merge, dim3(n_items, heads), D, 0, stream, part_o, part_ml, items, positions, (bf16*)out, out_stride,
+                llm_launch(merge, dim3(n_items, heads), dim3(D, max_splits > kMergeSplits ? kMergeGroups : 1), 0, stream, part_o, part_ml, items, positions, (bf16*)out, out_stride,
                            heads, window, keys_per_split, max_splits);
                 LLM_CHECK_LAUNCH("attention_merge");
             }
