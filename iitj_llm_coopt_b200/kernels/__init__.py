@@ -487,7 +487,8 @@ class Kernels:
         if qkv.dtype == torch.bfloat16 and self.lib.llm_attention_bf16_supported(heads, kv_heads, head_dim):
             plan = attention_plan(meta, qkv.device)
             if plan.n_tiles and self.attention_tcgen05 and \
-                    self.lib.llm_attention_tcgen05_supported(heads, kv_heads, head_dim, page_size):
+                    cache_layer.shape[0] * 2 * kv_heads * page_size < (1 << 31) and \
+                    self.lib.llm_attention_tcgen05_supported(heads, kv_heads, head_dim, page_size):     # (TMA coordinates are 32-bit)
                 if plan.big_tiles is None:
                     plan.big_tiles = torch.tensor(plan.big_rows, dtype=torch.int32).to(qkv.device)
                 splits = self.prefill_key_splits(plan.big_rows, heads, kv_heads, int(window))
@@ -512,7 +513,7 @@ class Kernels:
                 if splits > 1:
                     part_o = self._scratch("attn.part_o", plan.n_items * heads * splits * head_dim, qkv.device)
                     part_ml = self._scratch("attn.part_ml", plan.n_items * heads * splits * 2, qkv.device)
-                if self.decode_tma and self.lib.llm_attention_decode_tma_supported(heads, kv_heads, head_dim, page_size):
+                if self._decode_by_tma(cache_layer, heads, kv_heads, head_dim):
                     self._call("llm_attention_decode_bf16_tma", _ptr(qkv), qkv.shape[1], _ptr(cache_layer), cache_layer.shape[0],
                                _ptr(meta.block_table), meta.block_table.shape[1], _ptr(plan.items), plan.n_items,
                                _ptr(meta.token_request), _ptr(meta.positions), _ptr(part_o), _ptr(part_ml), _ptr(out),
@@ -532,6 +533,13 @@ class Kernels:
                    out.shape[1], DTYPE_CODE[qkv.dtype], tokens, heads, kv_heads, head_dim, page_size,
                    int(window), float(scale), self._stream())
         return out
+
+    def _decode_by_tma(self, cache_layer, heads, kv_heads, head_dim) -> bool:
+        """True if decode attention fetches this cache layer's keys and values by TMA: a page size of 8 to 64 tokens, and
+        a layer whose rows (pages x 2 x kv_heads x page_size) fit TMA's 32-bit coordinates; else the copying kernel runs."""
+        pages, page_size = cache_layer.shape[0], cache_layer.shape[3]
+        return bool(self.decode_tma and pages * 2 * kv_heads * page_size < (1 << 31) and
+                    self.lib.llm_attention_decode_tma_supported(heads, kv_heads, head_dim, page_size))
 
     def can_fuse_decode(self, qkv, meta, cache_layer, heads, kv_heads, head_dim) -> bool:
         """True if `attention_decode_fused` takes this step: every token is a single decoded token, the qkv
@@ -575,7 +583,7 @@ class Kernels:
         if splits > 1:
             part_o = self._scratch("attn.part_o", plan.n_items * heads * splits * head_dim, out.device)
             part_ml = self._scratch("attn.part_ml", plan.n_items * heads * splits * 2, out.device)
-        if self.decode_tma and self.lib.llm_attention_decode_tma_supported(heads, kv_heads, head_dim, cache_layer.shape[3]):
+        if self._decode_by_tma(cache_layer, heads, kv_heads, head_dim):
             self._call("llm_attention_decode_bf16_fused_tma", _ptr(qkv.parts), qkv.splits, qkv.stride, _ptr(cos), _ptr(sin),
                        _ptr(slots), _ptr(cache_layer), cache_layer.shape[0], _ptr(meta.block_table), meta.block_table.shape[1],
                        _ptr(plan.items), plan.n_items, _ptr(meta.token_request), _ptr(meta.positions), _ptr(part_o),
