@@ -41,8 +41,14 @@ template <int D> __host__ __device__ constexpr int tile_bytes() { return (D / 64
 constexpr int kThreads = 320;     // warp 0: loads, warp 1: MMA + TMEM, warps 2-5: softmax of head A, warps 6-9: of head B
 constexpr int kGroupThreads = 128;
 constexpr uint32_t kTmemCols = 512;            // S_A | S_B | O_A | O_B, 128 float32 columns each (O uses the head's dims)
+constexpr int kVStages = 3;       // shared-memory stages of value tiles (the keys have two)
 constexpr int kMinSplitTiles = 16;              // key tiles per split, about (the count of splits is rounded)
 constexpr float kRescaleStep = 8.0f;           // in log2 units: P stays below 2^8
+constexpr float kOnePassLimit = 100.0f;        // a one-pass tile whose maximum is this far above the reference is void (status 9)
+#ifndef LLM_ATTN_ONE_PASS
+#define LLM_ATTN_ONE_PASS 1
+#endif
+constexpr bool kOnePass = LLM_ATTN_ONE_PASS != 0;
 
 __device__ int g_attn_status = 0;
 __device__ __forceinline__ void attn_give_up(int code) { atomicCAS(&g_attn_status, 0, (code << 16) | (int)(blockIdx.x & 0xffff)); }
@@ -194,8 +200,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_tile[2] = {base, base + kTileBytes};                          // head A, head B
     unsigned char* k_tile[2] = {base + 2 * kTileBytes, base + 3 * kTileBytes};
-    unsigned char* v_tile[2] = {base + 4 * kTileBytes, base + 5 * kTileBytes};
-    __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_done[2];
+    // Three stages for the values: a value tile is handed back only when both heads' P V of its keys are done, one
+    // tile's time after the keys' stage, and with two stages its successor's boxes came in about 300 clocks late every tile.
+    unsigned char* v_tile[kVStages] = {base + 4 * kTileBytes, base + 5 * kTileBytes, base + 6 * kTileBytes};
+    __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[kVStages], v_empty[kVStages], s_full[2], p_full[2], o_done[2];
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int failed;
 
@@ -229,9 +237,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
             mbar_init(&s_full[s], 1); mbar_init(&p_full[s], kGroupThreads / 32); mbar_init(&o_done[s], 1);
         }
+        for (int s = 0; s < kVStages; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -262,14 +271,15 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         int page = 0;
         if (lane < pages_per_tile) page = table[min(k_begin / ps + lane, a.table_width - 1)];
         for (int j = 0; j < n_tiles; ++j) {
-            const int s = j & 1;
+            const int s = j & 1, sv = j % kVStages;
             int ok = 1;
             if (lane == 0) {
-                if (j >= 2 && (!mbar_wait(&k_empty[s], ((j >> 1) - 1) & 1) || !mbar_wait(&v_empty[s], ((j >> 1) - 1) & 1))) {
+                if ((j >= 2 && !mbar_wait(&k_empty[s], ((j >> 1) - 1) & 1)) ||
+                    (j >= kVStages && !mbar_wait(&v_empty[sv], ((j / kVStages) - 1) & 1))) {
                     attn_give_up(1); failed = 1; ok = 0;
                 } else {
                     mbar_expect_tx(&k_full[s], kTileBytes);
-                    mbar_expect_tx(&v_full[s], kTileBytes);
+                    mbar_expect_tx(&v_full[sv], kTileBytes);
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -277,11 +287,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (lane < pages_per_tile) {
                 const int row = (page * 2 * a.kv_heads + hk) * ps;               // K rows of this page; V rows kv_heads * ps further
                 unsigned char* kd = k_tile[s] + lane * ps * 128;
-                unsigned char* vd = v_tile[s] + lane * ps * 128;
+                unsigned char* vd = v_tile[sv] + lane * ps * 128;
 #pragma unroll
                 for (int h = 0; h < kHalves; ++h) {
                     tma_load_2d(kd + h * kHalfBytes, &map_kv, &k_full[s], 64 * h, row);
-                    tma_load_2d(vd + h * kHalfBytes, &map_kv, &v_full[s], 64 * h, row + a.kv_heads * ps);
+                    tma_load_2d(vd + h * kHalfBytes, &map_kv, &v_full[sv], 64 * h, row + a.kv_heads * ps);
                 }
                 // the next tile's page id (keys past the request's end are masked: any valid page will do)
                 if (j + 1 < n_tiles) page = table[min((k_begin + (j + 1) * kKeys) / ps + lane, a.table_width - 1)];
@@ -298,7 +308,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // Descriptors are built once; inside the loops only constants are added.
         const uint64_t dq[2] = {umma_desc(q_tile[0]), umma_desc(q_tile[1])};
         const uint64_t dk[2] = {umma_desc(k_tile[0]), umma_desc(k_tile[1])};
-        const uint64_t dv[2] = {umma_desc_mn(v_tile[0], kHalfBytes), umma_desc_mn(v_tile[1], kHalfBytes)};
+        const uint64_t dv[kVStages] = {umma_desc_mn(v_tile[0], kHalfBytes), umma_desc_mn(v_tile[1], kHalfBytes), umma_desc_mn(v_tile[2], kHalfBytes)};
         auto issue_s = [&](int x, int j) {
             const uint64_t da = x ? dq[1] : dq[0], db = (j & 1) ? dk[1] : dk[0];
 #pragma unroll
@@ -311,12 +321,15 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         auto issue_pv = [&](int x, int j) {
             if (!mbar_wait(&p_full[x], j & 1)) { attn_give_up(3); failed = 1; return false; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t db = (j & 1) ? dv[1] : dv[0];
+            const int sv = j % kVStages;
+            const uint64_t db = sv == 0 ? dv[0] : sv == 1 ? dv[1] : dv[2];
 #pragma unroll
             for (int kk = 0; kk < kKeys / 16; ++kk)
                 umma_f16_ts(tmem + 256 + x * 128, tmem + x * 128 + kk * 8, db + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_o,
                             (j > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(&o_done[x]);
+            // The tensor core completes its instructions in the order of issue, so the scores of tile j + 1 being there
+            // (s_full) tell the softmax warps that O holds tile j too; only after the last tile nothing follows.
+            if (j == n_tiles - 1) umma_commit(&o_done[x]);
             return true;
         };
         if (ok) {
@@ -330,7 +343,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int s = j & 1, s1 = (j + 1) & 1;
             const bool more = j + 1 < n_tiles;
-            if (!mbar_wait(&v_full[s], (j >> 1) & 1)) { attn_give_up(5); failed = 1; ok = false; break; }
+            if (!mbar_wait(&v_full[j % kVStages], (j / kVStages) & 1)) { attn_give_up(5); failed = 1; ok = false; break; }
             if (!(ok = issue_pv(0, j))) break;
             if (more) {
                 if (!mbar_wait(&k_full[s1], ((j + 1) >> 1) & 1)) { attn_give_up(4); failed = 1; ok = false; break; }
@@ -341,7 +354,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (!(ok = issue_pv(1, j))) break;
                 if (more) issue_s(1, j + 1);
             }
-            umma_commit(&v_empty[s]);
+            umma_commit(&v_empty[j % kVStages]);
             if (more) umma_commit(&k_empty[s1]);
         }
     } else if (warp >= 2 && ((warp - 2) >> 2) < n_heads) {
@@ -360,9 +373,65 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int t0 = k_begin + j * kKeys;
             const bool need_mask = (t0 + kKeys - 1 > pos0) || (a.window > 0 && t0 < pos_last - a.window + 1);
+            uint32_t ca[32], cb[32];
+            float sums[4] = {0.f, 0.f, 0.f, 0.f};
+            // A tile without masked keys, after the first one, when every row of the warp has a reference already: ONE
+            // pass.  P is taken relative to the reference as it stands while the tile's maximum is taken on the way; only
+            // if that maximum turns out more than the step above some row's reference (rare after the first tiles) are
+            // the tile's P, the row's O and its sum scaled down afterwards, by a whole power of two (exact in bfloat16).
+            if (kOnePass && j > 0 && !need_mask && __all_sync(0xffffffffu, m != -INFINITY)) {
+                float mx = -INFINITY;
+                uint32_t packed[16];
+                tmem_ld32(s_addr, ca);
+#pragma unroll 1
+                for (int c0 = 0; c0 < kKeys; c0 += 64) {
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    tmem_ld32(s_addr + c0 + 32, cb);
+                    mx = chunk_max<false>(ca, t0 + c0, row_pos, row_lo, mx);
+                    chunk_exp<false>(ca, packed, a.sl, m, t0 + c0, row_pos, row_lo, sums);
+                    tmem_st16(s_addr + (c0 >> 1), packed);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (c0 + 64 < kKeys) tmem_ld32(s_addr + c0 + 64, ca);
+                    mx = chunk_max<false>(cb, t0 + c0 + 32, row_pos, row_lo, mx);
+                    chunk_exp<false>(cb, packed, a.sl, m, t0 + c0 + 32, row_pos, row_lo, sums);
+                    tmem_st16(s_addr + (c0 >> 1) + 16, packed);
+                }
+                float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+                const float grown = mx * a.sl - m;
+                if (__any_sync(0xffffffffu, grown > kRescaleStep)) {
+                    // beyond this the exponentials above may have left float32's range: the result is void, and said to be
+                    if (grown > kOnePassLimit) attn_give_up(9);
+                    const int k = grown > kRescaleStep ? (int)fminf(ceilf(grown), 126.f) : 0;
+                    const float f = __int_as_float((127 - k) << 23);            // 2^-k
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");   // P is read back below
+                    // (O of the tiles so far is complete: the scores of this tile were issued after their P V)
+#pragma unroll 1
+                    for (int c = 0; c < kDim; c += 16) {
+                        uint32_t o[16];
+                        tmem_ld16(o_addr + c, o);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                        tmem_st16(o_addr + c, o);
+                    }
+#pragma unroll 1
+                    for (int c = 0; c < kKeys / 2; c += 16) {
+                        uint32_t pp[16];
+                        tmem_ld16(s_addr + c, pp);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            pp[i] = pack2(__uint_as_float(pp[i] << 16) * f, __uint_as_float(pp[i] & 0xffff0000u) * f);
+                        tmem_st16(s_addr + c, pp);
+                    }
+                    l *= f;
+                    sum *= f;
+                    m += (float)k;
+                }
+                l += sum;
+            } else {
             // Two passes over the row of S in chunks of 32 columns, each chunk's load issued while the chunk
             // before it is worked on: pass 1 takes the maximum, pass 2 exponentiates and writes P.
-            uint32_t ca[32], cb[32];
             auto pass_max = [&](auto tag) {
                 constexpr bool MASK = decltype(tag)::value;
                 float mx = -INFINITY;
@@ -384,9 +453,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float m_tile = mx * a.sl;
             const bool move = m_tile > m + kRescaleStep || (m == -INFINITY && m_tile > -INFINITY);
             if (j > 0 && __any_sync(0xffffffffu, move)) {
-                // O of the tiles so far must be complete before its rows are scaled
-                if (!mbar_wait(&o_done[x], (j - 1) & 1)) { attn_give_up(7); failed = 1; ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // O of the tiles so far is complete (the scores of this tile were issued after their P V): its rows are scaled
                 const float f = move ? ex2(m - m_tile) : 1.0f;      // 0 when the row had no visible key so far
 #pragma unroll 1
                 for (int c = 0; c < kDim; c += 16) {
@@ -401,7 +468,6 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             if (move) m = m_tile;
             const float mu = m == -INFINITY ? 0.f : m;      // a row with no visible key yet
-            float sums[4] = {0.f, 0.f, 0.f, 0.f};
             auto pass_exp = [&](auto tag) {
                 constexpr bool MASK = decltype(tag)::value;
                 uint32_t packed[16];
@@ -420,12 +486,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (need_mask) pass_exp(std::true_type{}); else pass_exp(std::false_type{});
             const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
             l += sum;
+            }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[x]);              // one arrival per warp
         }
-        if (ok && !mbar_wait(&o_done[x], (n_tiles - 1) & 1)) { attn_give_up(8); failed = 1; ok = false; }
+        if (ok && !mbar_wait(&o_done[x], 0)) { attn_give_up(8); failed = 1; ok = false; }
         if (ok && !failed && eff_splits > 1) {
             // partial result of this split: O as it stands (relative to m), and (m, l) of the row
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -573,14 +640,14 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
     static const int forced = [] { const char* e = getenv("IITJ_ATTN_HEADS_PER_CTA"); return e ? atoi(e) : 0; }();   // measurements
     if (forced == 1 || (forced == 2 && group >= 2)) a.per_cta = forced;
     a.pairs = (group + a.per_cta - 1) / a.per_cta;
-    const size_t smem = 6 * (size_t)(head_dim == 64 ? tile_bytes<64>() : tile_bytes<128>()) + 1024;
+    const size_t smem = (4 + kVStages) * (size_t)(head_dim == 64 ? tile_bytes<64>() : tile_bytes<128>()) + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             6 * tile_bytes<128>() + 1024);
+                                             (4 + kVStages) * tile_bytes<128>() + 1024);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     6 * tile_bytes<64>() + 1024);
+                                     (4 + kVStages) * tile_bytes<64>() + 1024);
         if (e != cudaSuccess) LLM_FAIL(-2, "attention_prefill_tcgen05: %s", cudaGetErrorString(e));
         configured = true;
     }

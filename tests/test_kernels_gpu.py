@@ -593,6 +593,36 @@ def test_attention_tcgen05_far_key_and_page_edges(K, head_dim):
     assert K.attention_status() == 0
 
 
+def test_attention_tcgen05_says_when_scores_outgrow_its_one_pass_range(K):
+    """Tiles after a request's first are exponentiated against the reference of the tiles before them, in one pass.  A
+    key whose score lies more than 2^100 above everything before it is beyond what that pass can mend afterwards: the
+    kernel leaves code 9 in its status word (which the engine reads with every sampled token) instead of a silent
+    wrong result.  The same key in the first tile, where two passes run, is found as usual."""
+    from iitj_llm_coopt_b200.kernels import KernelError
+    heads, kv_heads, page, L, n, D = 2, 1, 16, 2000, 256, 128
+    key = rnd((D,), torch.float32, 141)
+    key = key / key.norm()
+    for far, flagged in ((1743, True), (5, False)):
+        q, cache, meta = _paged_case(torch.bfloat16, heads, kv_heads, D, page, [L], [n], 140 + far)
+        cache.mul_(0.05)
+        pg, off = int(meta.block_table[0, far // page]), far % page
+        cache[pg, 0, 0, off] = (key * 80.0).to(torch.bfloat16)          # 80 * 12 / sqrt(128) * log2(e) = 122 in the kernel's units
+        cache[pg, 1, 0, off] = 3.0
+        q[:, :heads * D] = (key * 12.0).to(torch.bfloat16).repeat(heads)
+        out = torch.zeros(n, heads * D, device="cuda", dtype=torch.bfloat16)
+        K.attention(q, cache, meta, out, heads, kv_heads, D)
+        torch.cuda.synchronize()
+        status = K.attention_status()
+        if flagged:
+            assert status >> 16 == 9, hex(status)
+            with pytest.raises(KernelError, match="prefill attention"):
+                K.check_health([0, 0, status, 0])
+        else:
+            assert status == 0
+            assert (out.float() - 3.0).abs().max() < 0.1
+    assert K.attention_status() == 0                                   # (reading clears the word)
+
+
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page,window,splits", [
     (8, 2, 128, 16, 0, 3), (32, 8, 128, 16, 0, 6), (16, 1, 64, 16, 0, 1), (6, 2, 64, 8, 0, 8), (4, 4, 128, 32, 0, 2),
     (8, 2, 128, 16, 300, 4), (3, 1, 64, 4, 0, 5), (2, 1, 128, 64, 0, 2), (12, 4, 64, 32, 200, 3)])
