@@ -41,7 +41,10 @@ template <int D> __host__ __device__ constexpr int tile_bytes() { return (D / 64
 constexpr int kThreads = 320;     // warp 0: loads, warp 1: MMA + TMEM, warps 2-5: softmax of head A, warps 6-9: of head B
 constexpr int kGroupThreads = 128;
 constexpr uint32_t kTmemCols = 512;            // S_A | S_B | O_A | O_B, 128 float32 columns each (O uses the head's dims)
-constexpr int kVStages = 3;       // shared-memory stages of value tiles (the keys have two)
+#ifndef LLM_ATTN_V_STAGES
+#define LLM_ATTN_V_STAGES 3
+#endif
+constexpr int kVStages = LLM_ATTN_V_STAGES;       // shared-memory stages of value tiles (the keys have two)
 constexpr int kMinSplitTiles = 16;              // key tiles per split, about (the count of splits is rounded)
 constexpr float kRescaleStep = 8.0f;           // in log2 units: P stays below 2^8
 constexpr float kOnePassLimit = 100.0f;        // a one-pass tile whose maximum is this far above the reference is void (status 9)
@@ -202,7 +205,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     unsigned char* k_tile[2] = {base + 2 * kTileBytes, base + 3 * kTileBytes};
     // Three stages for the values: a value tile is handed back only when both heads' P V of its keys are done, one
     // tile's time after the keys' stage, and with two stages its successor's boxes came in about 300 clocks late every tile.
-    unsigned char* v_tile[kVStages] = {base + 4 * kTileBytes, base + 5 * kTileBytes, base + 6 * kTileBytes};
+    unsigned char* v_tile[3] = {base + 4 * kTileBytes, base + 5 * kTileBytes, base + 6 * kTileBytes};   // (the last only with three stages)
     __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[kVStages], v_empty[kVStages], s_full[2], p_full[2], o_done[2];
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int failed;
@@ -308,7 +311,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // Descriptors are built once; inside the loops only constants are added.
         const uint64_t dq[2] = {umma_desc(q_tile[0]), umma_desc(q_tile[1])};
         const uint64_t dk[2] = {umma_desc(k_tile[0]), umma_desc(k_tile[1])};
-        const uint64_t dv[kVStages] = {umma_desc_mn(v_tile[0], kHalfBytes), umma_desc_mn(v_tile[1], kHalfBytes), umma_desc_mn(v_tile[2], kHalfBytes)};
+        const uint64_t dv[3] = {umma_desc_mn(v_tile[0], kHalfBytes), umma_desc_mn(v_tile[1], kHalfBytes), umma_desc_mn(v_tile[2], kHalfBytes)};
         auto issue_s = [&](int x, int j) {
             const uint64_t da = x ? dq[1] : dq[0], db = (j & 1) ? dk[1] : dk[0];
 #pragma unroll
