@@ -48,10 +48,6 @@ constexpr int kVStages = LLM_ATTN_V_STAGES;       // shared-memory stages of val
 constexpr int kMinSplitTiles = 16;              // key tiles per split, about (the count of splits is rounded)
 constexpr float kRescaleStep = 8.0f;           // in log2 units: P stays below 2^8
 constexpr float kOnePassLimit = 100.0f;        // a one-pass tile whose maximum is this far above the reference is void (status 9)
-#ifndef LLM_ATTN_ONE_PASS
-#define LLM_ATTN_ONE_PASS 1
-#endif
-constexpr bool kOnePass = LLM_ATTN_ONE_PASS != 0;
 
 __device__ int g_attn_status = 0;
 __device__ __forceinline__ void attn_give_up(int code) { atomicCAS(&g_attn_status, 0, (code << 16) | (int)(blockIdx.x & 0xffff)); }
@@ -191,6 +187,7 @@ struct AttnArgs {
     int per_cta;                  // query heads per CTA: 2 (ping-pong), or 1 when that fills more of the GPU
     int pairs;                    // CTAs per key/value group: ceil(heads per group / per_cta)
     float sl;                     // softmax scale * log2(e)
+    int one_pass;                 // tiles after a request's first: one softmax pass (see the kernel); 0: always two (IITJ_ATTN_ONE_PASS=0)
 };
 
 template <int D>
@@ -382,7 +379,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // pass.  P is taken relative to the reference as it stands while the tile's maximum is taken on the way; only
             // if that maximum turns out more than the step above some row's reference (rare after the first tiles) are
             // the tile's P, the row's O and its sum scaled down afterwards, by a whole power of two (exact in bfloat16).
-            if (kOnePass && j > 0 && !need_mask && __all_sync(0xffffffffu, m != -INFINITY)) {
+            if (a.one_pass && j > 0 && !need_mask && __all_sync(0xffffffffu, m != -INFINITY)) {
                 float mx = -INFINITY;
                 uint32_t packed[16];
                 tmem_ld32(s_addr, ca);
@@ -633,6 +630,8 @@ LLM_API int llm_attention_prefill_tcgen05(const void* q, int q_stride, int token
     a.page_size = page_size;
     a.window = window;
     a.sl = scale * 1.4426950408889634f;
+    static const int one_pass = [] { const char* e = getenv("IITJ_ATTN_ONE_PASS"); return (e && e[0] == '0') ? 0 : 1; }();
+    a.one_pass = one_pass;
     // Two heads per CTA share each key/value tile and keep the tensor core busier; with few CTAs one head per
     // CTA spreads the work over more SMs (512 queries over 8192 keys at 32 heads: 168 -> 125 us).
     int dev = 0, sms = 0;

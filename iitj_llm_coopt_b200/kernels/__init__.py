@@ -94,7 +94,8 @@ HEALTH_WORDS = (
     ("CTA-pair matrix product", "a bounded wait ran out (1 producer, 2 MMA issuer, 3 epilogue, 4 drained accumulator, "
                                 "5 other clusters' partial sums)"),
     ("tcgen05 prefill attention", "a bounded wait ran out (1 to 8), or a key's score lay more than 2^100 above all keys of "
-                                  "the tiles before it (9: beyond what the one-pass softmax can mend)"),
+                                  "the tiles before it (9: beyond what the one-pass softmax can mend; IITJ_ATTN_ONE_PASS=0 runs two passes "
+                                  "everywhere)"),
     ("decode attention", "keys_per_split * max_splits did not cover an item's keys (6), or a bounded wait for keys and "
                          "values ran out (7)"),
 )

@@ -597,8 +597,12 @@ def test_attention_tcgen05_says_when_scores_outgrow_its_one_pass_range(K):
     """Tiles after a request's first are exponentiated against the reference of the tiles before them, in one pass.  A
     key whose score lies more than 2^100 above everything before it is beyond what that pass can mend afterwards: the
     kernel leaves code 9 in its status word (which the engine reads with every sampled token) instead of a silent
-    wrong result.  The same key in the first tile, where two passes run, is found as usual."""
+    wrong result.  The same key in the first tile, where two passes run, is found as usual (with IITJ_ATTN_ONE_PASS=0 in
+    the environment two passes run everywhere and nothing is flagged)."""
+    import os
     from iitj_llm_coopt_b200.kernels import KernelError
+    if os.environ.get("IITJ_ATTN_ONE_PASS", "1")[:1] == "0":
+        pytest.skip("two passes everywhere: nothing to flag")
     heads, kv_heads, page, L, n, D = 2, 1, 16, 2000, 256, 128
     key = rnd((D,), torch.float32, 141)
     key = key / key.norm()
