@@ -152,9 +152,12 @@ __device__ __forceinline__ void softmax_16keys(float (&s0)[4], float (&s1)[4], f
     float p10 = exp2f(s1[0] * sl - mu0), p11 = exp2f(s1[1] * sl - mu0), p12 = exp2f(s1[2] * sl - mu1), p13 = exp2f(s1[3] * sl - mu1);
     l[0] = l[0] * c0 + (p00 + p01 + p10 + p11);
     l[1] = l[1] * c1 + (p02 + p03 + p12 + p13);
+    // (a factor of exactly 1 changes nothing: once the rows' maxima stand, which is most tiles, the warp skips the scaling)
+    if (__any_sync(0xffffffffu, c0 != 1.0f || c1 != 1.0f)) {
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
-        o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1;
+        for (int n = 0; n < D / 8; ++n) {
+            o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1;
+        }
     }
     pa[0] = pack_bf16(p00, p01);
     pa[1] = pack_bf16(p02, p03);
